@@ -1,0 +1,167 @@
+// Row-wise kernels of the decoder: embedding gather, residual add fused with RMSNorm, rotation
+// tables, SiLU-mul. All arithmetic is float32; only the stored activation may be bfloat16.
+//
+// What the reference computes: embed crates/kir/src/prims.rs:387, RMSNorm
+// crates/kir/tests/golden/rmsnorm_sm120.cu:19-29, swiglu crates/kir/tests/golden/swiglu_silu.cu:1-11.
+#include <stdarg.h>
+#include <stdio.h>
+
+#include "common.cuh"
+
+static thread_local char g_error[512] = "";
+extern "C" const char* ib_last_error() { return g_error; }
+int ib_set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+  return 1;
+}
+
+namespace {
+
+// ---------------------------------------------------------------- embedding
+template <typename W>
+__global__ void embed_kernel(const W* __restrict__ table, const int* __restrict__ tokens, float* __restrict__ x, int H, int V,
+                             unsigned* __restrict__ status) {
+  int t = blockIdx.y;
+  int tok = tokens[t];
+  if (tok < 0 || tok >= V) {
+    if (threadIdx.x == 0 && blockIdx.x == 0) atomicOr(status, IB_ERR_BAD_TOKEN);
+    tok = 0;
+  }
+  const W* src = table + (size_t)tok * H;
+  float* dst = x + (size_t)t * H;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < H; i += gridDim.x * blockDim.x) dst[i] = ib::to_f32<W>(src[i]);
+}
+
+// ---------------------------------------------------------------- residual add + RMSNorm
+// One block per output row r. Source row t = rows ? rows[r] : r.
+//   v = x[t] + sum_p delta[p][t]   (partials summed in order p = 0..P-1, then added to x)
+//   if write_x: x[t] = v
+//   out[r] = w * (v * rsqrt(mean(v^2) + eps))
+// The row lives in dynamic shared memory (H floats) between the two passes.
+template <typename O>
+__global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, int P, size_t delta_stride,
+                                   const float* __restrict__ w, O* __restrict__ out, const int* __restrict__ rows, int H, float eps,
+                                   int write_x) {
+  extern __shared__ float row[];
+  __shared__ float scratch[32];
+  int r = blockIdx.x;
+  int t = rows ? rows[r] : r;
+  float* xr = x + (size_t)t * H;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float v = xr[i];
+    if (P > 0) {
+      float d = delta[(size_t)t * H + i];
+      for (int p = 1; p < P; p++) d += delta[p * delta_stride + (size_t)t * H + i];
+      v += d;
+      if (write_x) xr[i] = v;
+    }
+    row[i] = v;
+    ss += v * v;
+  }
+  ss = ib::block_sum(ss, scratch);
+  float inv = rsqrtf(ss / (float)H + eps);
+  O* o = out + (size_t)r * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = ib::from_f32<O>(w[i] * (row[i] * inv));
+}
+
+// ---------------------------------------------------------------- rotation tables
+// cos/sin[t][i] of angle = float(position[t]) * inv_freq[i], float32 throughout
+// (crates/kir/tests/golden/attention/RopeKvWrite_bf16x2_sm120.cu:32-35).
+__global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq, float* __restrict__ cos_t,
+                                  float* __restrict__ sin_t, int T, int half) {
+  int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= T * half) return;
+  int t = idx / half, i = idx - t * half;
+  float ang = (float)positions[t] * inv_freq[i];
+  float s, c;
+  sincosf(ang, &s, &c);
+  cos_t[idx] = c;
+  sin_t[idx] = s;
+}
+
+// ---------------------------------------------------------------- SiLU-mul
+// gu[p][t][0:I] = gate, gu[p][t][I:2I] = up (partials summed first); act = g / (1 + exp(-g)) * u.
+template <typename O>
+__global__ void silu_mul_kernel(const float* __restrict__ gu, int P, size_t stride, O* __restrict__ act, int I) {
+  int t = blockIdx.y;
+  const float* row = gu + (size_t)t * 2 * I;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < I; i += gridDim.x * blockDim.x) {
+    float g = row[i], u = row[I + i];
+    for (int p = 1; p < P; p++) {
+      g += row[p * stride + i];
+      u += row[p * stride + I + i];
+    }
+    act[(size_t)t * I + i] = ib::from_f32<O>((g / (1.f + expf(-g))) * u);
+  }
+}
+
+}  // namespace
+
+extern "C" int ib_embed(const void* table, int table_dtype, const int* tokens, float* x, int T, int H, int V, unsigned* status,
+                        cudaStream_t stream) {
+  if (T == 0) return 0;
+  IB_CHECK_ARG(T > 0 && H > 0 && V > 0, "embed: bad sizes T=%d H=%d V=%d", T, H, V);
+  IB_CHECK_ARG(T <= 65535, "embed: T=%d rows exceed the grid limit 65535", T);
+  dim3 grid((H + 255) / 256, T);
+  if (table_dtype == IB_F32)
+    embed_kernel<float><<<grid, 256, 0, stream>>>((const float*)table, tokens, x, H, V, status);
+  else if (table_dtype == IB_BF16)
+    embed_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)table, tokens, x, H, V, status);
+  else
+    return ib_set_error("embed: unknown table dtype %d", table_dtype);
+  IB_CHECK_LAUNCH("embed");
+  return 0;
+}
+
+extern "C" int ib_add_rmsnorm(float* x, const float* delta, int P, long long delta_stride, const float* w, void* out, int out_dtype,
+                              const int* rows, int n_rows, int H, float eps, int write_x, cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  IB_CHECK_ARG(n_rows > 0 && H > 0 && P >= 0, "add_rmsnorm: bad sizes rows=%d H=%d P=%d", n_rows, H, P);
+  IB_CHECK_ARG(!(rows && write_x), "add_rmsnorm: a gathered call must not write x back");
+  size_t smem = (size_t)H * sizeof(float);
+  IB_CHECK_ARG(smem <= 200 * 1024, "add_rmsnorm: hidden size %d needs %zu bytes of shared memory, more than 200 KiB", H, smem);
+  int threads = H >= 4096 ? 1024 : (H >= 1024 ? 512 : 256);
+  if (out_dtype == IB_F32) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(add_rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    add_rmsnorm_kernel<float><<<n_rows, threads, smem, stream>>>(x, delta, P, (size_t)delta_stride, w, (float*)out, rows, H, eps, write_x);
+  } else if (out_dtype == IB_BF16) {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(add_rmsnorm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    add_rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, smem, stream>>>(x, delta, P, (size_t)delta_stride, w, (__nv_bfloat16*)out, rows, H,
+                                                                          eps, write_x);
+  } else {
+    return ib_set_error("add_rmsnorm: unknown output dtype %d", out_dtype);
+  }
+  IB_CHECK_LAUNCH("add_rmsnorm");
+  return 0;
+}
+
+extern "C" int ib_rope_table(const int* positions, const float* inv_freq, float* cos_t, float* sin_t, int T, int half,
+                             cudaStream_t stream) {
+  if (T == 0 || half == 0) return 0;
+  IB_CHECK_ARG(T > 0 && half > 0, "rope_table: bad sizes T=%d half=%d", T, half);
+  long long n = (long long)T * half;
+  rope_table_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(positions, inv_freq, cos_t, sin_t, T, half);
+  IB_CHECK_LAUNCH("rope_table");
+  return 0;
+}
+
+extern "C" int ib_silu_mul(const float* gu, int P, long long stride, void* act, int act_dtype, int T, int I, cudaStream_t stream) {
+  if (T == 0) return 0;
+  IB_CHECK_ARG(T > 0 && I > 0 && P >= 1, "silu_mul: bad sizes T=%d I=%d P=%d", T, I, P);
+  IB_CHECK_ARG(T <= 65535, "silu_mul: T=%d rows exceed the grid limit 65535", T);
+  dim3 grid((I + 255) / 256, T);
+  if (grid.x > 64) grid.x = 64;
+  if (act_dtype == IB_F32)
+    silu_mul_kernel<float><<<grid, 256, 0, stream>>>(gu, P, (size_t)stride, (float*)act, I);
+  else if (act_dtype == IB_BF16)
+    silu_mul_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(gu, P, (size_t)stride, (__nv_bfloat16*)act, I);
+  else
+    return ib_set_error("silu_mul: unknown output dtype %d", act_dtype);
+  IB_CHECK_LAUNCH("silu_mul");
+  return 0;
+}

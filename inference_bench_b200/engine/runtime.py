@@ -1,0 +1,99 @@
+"""The device-side environment parts run in: device, precision mode, matrix products, scratch.
+
+Two modes exist. "bfloat16" is what serving uses: bfloat16 weights, activations and cache,
+float32 residual stream, norms, softmax and accumulation, tcgen05 tensor-core products.
+"float32" is the true 32-bit path: every tensor and every product in IEEE float32 (FMA, no
+tensor-core mode of reduced precision). The reference has no such path; its closest is
+`gemm_fp32` with bfloat16 weights (crates/specrt/graphs/decoder.toml:174-278).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from ..kernels import lib as L
+from ..kernels import ops
+
+MODES = {"float32": torch.float32, "fp32": torch.float32, "bfloat16": torch.bfloat16, "bf16": torch.bfloat16}
+
+
+class DeviceStatusError(RuntimeError):
+    """A kernel reported a fault through the status word (bad page, bad token, a wait that ran out)."""
+
+
+@dataclass
+class LinearWeights:
+    """A [N, K] matrix prepared for the runtime's mode, plus whatever its kernel caches for it."""
+    weight: torch.Tensor
+    n: int
+    k: int
+    plan: Optional[object] = None  # kernel-side descriptor cache
+
+
+class Runtime:
+    def __init__(self, device="cuda:0", dtype: str = "bfloat16", gemm: str = "simt"):
+        if dtype not in MODES:
+            raise ValueError(f"dtype must be one of {sorted(set(MODES))}, got {dtype!r}")
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise L.KernelLibraryError("the engine runs on a CUDA device only; there is no CPU path")
+        if not torch.cuda.is_available():
+            raise L.KernelLibraryError("no CUDA device is visible; the engine has no CPU path")
+        L.load()
+        self.mode = "float32" if MODES[dtype] == torch.float32 else "bfloat16"
+        self.act_dtype = MODES[dtype]
+        self.gemm = gemm  # "auto" | "simt" | "tcgen05"
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+
+    # ---------------------------------------------------------------- memory
+    def empty(self, shape, dtype=None) -> torch.Tensor:
+        return torch.empty(shape, dtype=dtype or self.act_dtype, device=self.device)
+
+    def upload(self, t: torch.Tensor, dtype=None) -> torch.Tensor:
+        t = t.to(self.device, non_blocking=False)
+        if dtype is not None and t.dtype != dtype:
+            t = t.to(dtype)
+        return t.contiguous()
+
+    # ---------------------------------------------------------------- weights
+    def matrix(self, w: torch.Tensor) -> LinearWeights:
+        """Prepare a [N, K] matrix: float32 mode keeps every bit (bfloat16 widens exactly);
+        bfloat16 mode rounds a 32-bit matrix to bfloat16, as the reference does at load
+        (crates/specrt/src/weights.rs:388-396)."""
+        w = self.upload(w, self.act_dtype)
+        return LinearWeights(w, w.shape[0], w.shape[1])
+
+    def vector(self, w: torch.Tensor) -> torch.Tensor:
+        """Norm scales are used in float32 in both modes."""
+        return self.upload(w, torch.float32)
+
+    # ---------------------------------------------------------------- matrix product
+    def linear(self, x: torch.Tensor, lw: LinearWeights, allow_split: bool = True) -> torch.Tensor:
+        """x [T, K] in the activation dtype -> partial products float32 [P, T, N]; their sum over P,
+        taken in order, is x @ W^T."""
+        T = x.shape[0]
+        if x.shape[1] != lw.k:
+            raise L.KernelError(f"linear: x has {x.shape[1]} columns, the matrix has {lw.k}")
+        use_tc = self.mode == "bfloat16" and self.gemm != "simt"
+        if use_tc:
+            from ..kernels import gemm_tcgen05
+            if gemm_tcgen05.supports(lw.k):
+                return gemm_tcgen05.linear(self, x, lw, allow_split)
+            if self.gemm == "tcgen05":
+                raise L.KernelError(f"linear: K={lw.k} is not a multiple of 8, which the tcgen05 kernel needs")
+        out = self.empty((1, T, lw.n), torch.float32)
+        ops.gemm_simt(x, lw.weight, out[0])
+        return out
+
+    # ---------------------------------------------------------------- status word
+    def check_status(self) -> None:
+        """Read the status word (synchronises) and raise if a kernel reported a fault."""
+        bits = int(self.status.item())
+        if bits:
+            self.status.zero_()
+            what = [name for bit, name in ((L.ERR_BAD_PAGE, "a block table entry was missing or out of range"),
+                                           (L.ERR_BAD_TOKEN, "a token id was outside the vocabulary"),
+                                           (L.ERR_WAIT_TIMEOUT, "a bounded wait inside a kernel ran out")) if bits & bit]
+            raise DeviceStatusError("; ".join(what) or f"status bits {bits}")

@@ -1,0 +1,67 @@
+"""The engine against the plain implementation under every way of cutting the work, in true
+32-bit and in bfloat16, on all tiny configurations."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+import traces
+from plain_qwen3 import PlainModel
+from tiny_configs import CONFIGS
+
+pytestmark = pytest.mark.gpu
+
+# Largest |engine - plain| allowed, as a fraction of the largest |logit| of the sequence.
+# float32: the two differ only in summation order. bfloat16: activations and the cache are rounded
+# to 8 bits of mantissa (2^-9 relative per rounding) between float32 accumulations.
+TOLERANCE = {"float32": 1e-4, "bfloat16": 3e-2}
+LENGTHS = {"a": 7, "b": 19, "c": 33, "d": 70, "e": 45, "f": 100, "g": 2, "h": 64}
+
+
+def _requests(name):
+    vocab = CONFIGS[name]["config"]["vocab_size"]
+    return {r: traces.prompt(100 + i, n, vocab) for i, (r, n) in enumerate(LENGTHS.items())}
+
+
+@pytest.fixture(scope="module")
+def plain_logits(model_dirs):
+    out = {}
+    for name in CONFIGS:
+        m = PlainModel(model_dirs[name])
+        out[name] = {r: m.logits(t).numpy() for r, t in _requests(name).items()}
+    return out
+
+
+def _runner(model_dirs, name, dtype, max_tokens):
+    from inference_bench_b200.trace import build_runner
+    return build_runner(model_dirs[name], dtype, max_tokens, page_size=CONFIGS[name]["page_size"])
+
+
+def _compare(got, want_by_req, dtype, what):
+    worst = 0.0
+    for (r, pos), row in got.items():
+        want = want_by_req[r][pos]
+        scale = np.abs(want_by_req[r]).max()
+        err = np.abs(row - want).max() / scale
+        if err > TOLERANCE[dtype]:
+            raise AssertionError(f"{what}: request {r} position {pos}: |diff| = {err:.3e} of max|logit| (allowed {TOLERANCE[dtype]:.0e})")
+        worst = max(worst, err)
+    n_expected = sum(len(v) for v in want_by_req.values())
+    assert len(got) == n_expected, f"{what}: {len(got)} logits rows, expected {n_expected}"
+    return worst
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(CONFIGS))
+@pytest.mark.parametrize("cut", ["whole", "tail", "portions", "mixed"])
+def test_cut_matches_plain(model_dirs, plain_logits, name, dtype, cut):
+    reqs = _requests(name)
+    steps = {"whole": traces.whole, "tail": traces.tail_one_by_one, "portions": traces.portions, "mixed": traces.mixed}[cut](reqs)
+    max_tokens = traces.max_live_tokens(steps)
+    runner = _runner(model_dirs, name, dtype, max_tokens)
+    got = traces.run_steps(runner, steps)
+    worst = _compare(got, plain_logits[name], dtype, f"{name}/{dtype}/{cut}")
+    runner.cache.check()
+    assert runner.cache.used_pages() == [0] * len(runner.cache.groups)
+    print(f"{name}/{dtype}/{cut}: worst {worst:.3e} of max|logit|, pool {max_tokens} tokens")
