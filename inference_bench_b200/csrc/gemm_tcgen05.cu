@@ -1,0 +1,228 @@
+// out[p][t][n] = sum over split p's k-range of x[t][k] * w[n][k]: bfloat16 operands, float32
+// accumulation in tensor memory, on the sm_100a tensor cores (tcgen05.mma fed by TMA).
+//
+// The weight matrix sits in the MMA's M dimension (128 rows of W per CTA) and the tokens in its N
+// dimension (16 to 256 per CTA), so the same kernel streams weights at memory speed for a handful
+// of decoded tokens and runs full 128x256 tiles for a prompt. Both operands are K-major in
+// memory, which is how [rows, K] row-major tensors already are: no transposes anywhere.
+//
+// CTA = 6 warps: warp 0 issues TMA loads, warp 1 owns tensor memory and issues the MMAs, warps 2-5
+// read the accumulator back (tcgen05.ld: warp w may touch lanes 32*(w%4)..+31) and store it.
+// The reference's equivalent is its mma.sync tile kernel (crates/kir/src/cuda/gemm/core.rs:14-155).
+#include <cuda.h>
+
+#include "sm100.cuh"
+
+namespace {
+
+constexpr int BM = 128;     // weight rows per CTA (MMA M)
+constexpr int BK = 64;      // k per stage: 64 bfloat16 = one 128-byte swizzle row
+constexpr int UMMA_K = 16;  // k per tcgen05.mma of kind::f16
+constexpr int kThreads = 192;
+
+template <int BN>
+struct Tile {
+  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = BN >= 256 ? 4 : (BN >= 128 ? 6 : 8);
+  static constexpr int kTmemCols = BN < 32 ? 32 : BN;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+    gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, float* __restrict__ out, int T,
+                        int N, int K, int ktiles_per_split, unsigned* __restrict__ status) {
+  using TL = Tile<BN>;
+  constexpr int STAGES = TL::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = sm100::smem_u32(smem_raw);
+  uint8_t* tiles = smem_raw + (((raw + 1023u) & ~1023u) - raw);
+  uint64_t* full = (uint64_t*)(tiles + STAGES * TL::kStageBytes);
+  uint64_t* empty = full + STAGES;
+  uint64_t* acc_full = empty + STAGES;
+  uint32_t* tmem_slot = (uint32_t*)(acc_full + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BM, t0 = blockIdx.y * BN, split = blockIdx.z;
+  const int total_kt = (K + BK - 1) / BK;
+  const int kt_begin = split * ktiles_per_split;
+  const int kt_end = min(total_kt, kt_begin + ktiles_per_split);
+  const int nkt = max(0, kt_end - kt_begin);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; s++) {
+      sm100::mbar_init(&full[s], 1);
+      sm100::mbar_init(&empty[s], 1);
+    }
+    sm100::mbar_init(acc_full, 1);
+    sm100::fence_barrier_init();
+  }
+  if (warp == 1) {
+    sm100::tmem_alloc(tmem_slot, TL::kTmemCols);
+    sm100::tmem_relinquish();
+  }
+  sm100::tc_fence_before();
+  __syncthreads();
+  sm100::tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    if (sm100::elect_one()) {
+      sm100::prefetch_tensormap(&tmap_w);
+      sm100::prefetch_tensormap(&tmap_x);
+      for (int i = 0; i < nkt; i++) {
+        const int s = i % STAGES;
+        if (!sm100::mbar_wait(&empty[s], ((i / STAGES) & 1) ^ 1)) {
+          atomicOr(status, IB_ERR_WAIT_TIMEOUT);
+          break;
+        }
+        uint8_t* a = tiles + s * TL::kStageBytes;
+        sm100::mbar_arrive_expect_tx(&full[s], TL::kStageBytes);
+        sm100::tma_load_2d(a, &tmap_w, (kt_begin + i) * BK, n0, &full[s]);
+        sm100::tma_load_2d(a + TL::kABytes, &tmap_x, (kt_begin + i) * BK, t0, &full[s]);
+      }
+    }
+  } else if (warp == 1) {
+    if (sm100::elect_one()) {
+      constexpr uint32_t idesc = sm100::idesc_bf16_f32(BM, BN);
+      bool ok = true;
+      for (int i = 0; i < nkt && ok; i++) {
+        const int s = i % STAGES;
+        if (!sm100::mbar_wait(&full[s], (i / STAGES) & 1)) {
+          atomicOr(status, IB_ERR_WAIT_TIMEOUT);
+          ok = false;
+          break;
+        }
+        sm100::tc_fence_after();
+        const uint32_t a_addr = sm100::smem_u32(tiles + s * TL::kStageBytes);
+        const uint64_t da = sm100::smem_desc_sw128(a_addr), db = sm100::smem_desc_sw128(a_addr + TL::kABytes);
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; k++) {
+          // inside the 128-byte swizzle row the next 16 k-values are 32 bytes on: +2 in the >>4 address field
+          sm100::mma_bf16_ss(tmem, da + 2 * k, db + 2 * k, idesc, (i | k) != 0);
+        }
+        sm100::mma_commit(&empty[s]);
+      }
+      if (ok) sm100::mma_commit(acc_full);
+    }
+  } else {
+    // Epilogue: this warp's quarter of the 128 accumulator lanes.
+    const int q = warp & 3;
+    const int n = n0 + q * 32 + lane;
+    bool ok = true;
+    if (nkt > 0) {
+      ok = sm100::mbar_wait(acc_full, 0);
+      if (!ok && lane == 0) atomicOr(status, IB_ERR_WAIT_TIMEOUT);
+      sm100::tc_fence_after();
+    }
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+      float* dst = out + (size_t)split * T * N;
+      constexpr int CH = BN < 32 ? 16 : 32;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += CH) {
+        uint32_t r[CH];
+        if (nkt > 0) {
+          const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
+          if constexpr (CH == 32)
+            sm100::tmem_ld_32x32b_x32(taddr, r);
+          else
+            sm100::tmem_ld_32x32b_x16(taddr, r);
+          sm100::tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int c = 0; c < CH; c++) r[c] = 0u;
+        }
+        if (n < N) {
+#pragma unroll
+          for (int c = 0; c < CH; c++) {
+            const int t = t0 + c0 + c;
+            if (t < T) dst[(size_t)t * N + n] = __uint_as_float(r[c]);
+          }
+        }
+      }
+    }
+  }
+  sm100::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    sm100::tmem_dealloc(tmem, TL::kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// A [rows, K] row-major bfloat16 matrix read in boxes of [box_rows, 64] with the 128-byte swizzle;
+// out-of-range rows and columns read as zero.
+int make_tmap(CUtensorMap* m, const void* ptr, int rows, int K, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  IB_CHECK_ARG(fn, "gemm_tcgen05: the driver has no cuTensorMapEncodeTiled");
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  IB_CHECK_ARG(r == CUDA_SUCCESS, "gemm_tcgen05: cuTensorMapEncodeTiled failed with code %d (rows=%d K=%d box_rows=%d)", (int)r, rows, K, box_rows);
+  return 0;
+}
+
+template <int BN>
+int launch(const CUtensorMap& tw, const CUtensorMap& tx, float* out, int T, int N, int K, int splits, int kt_per_split, unsigned* status,
+           cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Tile<BN>::kSmemBytes);
+    IB_CHECK_ARG(e == cudaSuccess, "gemm_tcgen05: cannot reserve %d bytes of shared memory: %s", Tile<BN>::kSmemBytes, cudaGetErrorString(e));
+    configured = true;
+  }
+  dim3 grid((N + BM - 1) / BM, (T + BN - 1) / BN, splits);
+  gemm_tcgen05_kernel<BN><<<grid, kThreads, Tile<BN>::kSmemBytes, stream>>>(tw, tx, out, T, N, K, kt_per_split, status);
+  IB_CHECK_LAUNCH("gemm_tcgen05");
+  return 0;
+}
+
+}  // namespace
+
+// x [T, K] bfloat16, w [N, K] bfloat16 -> out [splits, T, N] float32. bn: tokens per CTA (16, 32, 64,
+// 128 or 256); splits: how many CTAs share one output tile's k-range (each writes its own partial).
+extern "C" int ib_gemm_tcgen05(const void* x, const void* w, float* out, int T, int N, int K, int bn, int splits, unsigned* status,
+                               cudaStream_t stream) {
+  if (T == 0 || N == 0) return 0;
+  IB_CHECK_ARG(T > 0 && N > 0 && K > 0, "gemm_tcgen05: bad sizes T=%d N=%d K=%d", T, N, K);
+  IB_CHECK_ARG(K % 8 == 0, "gemm_tcgen05: K=%d must be a multiple of 8 (TMA needs 16-byte row pitch)", K);
+  IB_CHECK_ARG(((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0, "gemm_tcgen05: operands must be 16-byte aligned");
+  const int total_kt = (K + BK - 1) / BK;
+  IB_CHECK_ARG(splits >= 1 && splits <= total_kt, "gemm_tcgen05: %d splits for %d k-tiles", splits, total_kt);
+  const int kt_per_split = (total_kt + splits - 1) / splits;
+  IB_CHECK_ARG((splits - 1) * kt_per_split < total_kt, "gemm_tcgen05: %d splits of %d k-tiles leave one empty (%d k-tiles)", splits, kt_per_split,
+               total_kt);
+  IB_CHECK_ARG((T + bn - 1) / bn <= 65535 && splits <= 65535, "gemm_tcgen05: grid too large");
+  CUtensorMap tw, tx;
+  if (make_tmap(&tw, w, N, K, BM)) return 1;
+  if (make_tmap(&tx, x, T, K, bn)) return 1;
+  switch (bn) {
+    case 16: return launch<16>(tw, tx, out, T, N, K, splits, kt_per_split, status, stream);
+    case 32: return launch<32>(tw, tx, out, T, N, K, splits, kt_per_split, status, stream);
+    case 64: return launch<64>(tw, tx, out, T, N, K, splits, kt_per_split, status, stream);
+    case 128: return launch<128>(tw, tx, out, T, N, K, splits, kt_per_split, status, stream);
+    case 256: return launch<256>(tw, tx, out, T, N, K, splits, kt_per_split, status, stream);
+    default: return ib_set_error("gemm_tcgen05: token tile %d is not one of 16, 32, 64, 128, 256", bn);
+  }
+}

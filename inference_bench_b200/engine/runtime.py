@@ -33,7 +33,7 @@ class LinearWeights:
 
 
 class Runtime:
-    def __init__(self, device="cuda:0", dtype: str = "bfloat16", gemm: str = "simt"):
+    def __init__(self, device="cuda:0", dtype: str = "bfloat16", gemm: str = "auto"):
         if dtype not in MODES:
             raise ValueError(f"dtype must be one of {sorted(set(MODES))}, got {dtype!r}")
         self.device = torch.device(device)
