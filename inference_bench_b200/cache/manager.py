@@ -91,11 +91,20 @@ class CacheManager:
             import torch
             for g in self.groups:
                 n = g.need
-                g.tensor = torch.zeros((g.pool.num_pages, len(g.entries), 2, n.kv_heads, page_size, n.head_dim), dtype=dtype, device=device)
+                # one page more than the pool hands out: the scratch page that padded rows of a fixed-size batch write to
+                g.tensor = torch.zeros((g.pool.num_pages + 1, len(g.entries), 2, n.kv_heads, page_size, n.head_dim), dtype=dtype, device=device)
             for i, n in self._fixed.items():
-                self.states[i].tensor = torch.zeros((max_requests, *n.shape), dtype=n.dtype, device=device)
+                # and one scratch slot more than requests can hold
+                self.states[i].tensor = torch.zeros((max_requests + 1, *n.shape), dtype=n.dtype, device=device)
         self._requests: dict[Hashable, _Request] = {}
         self._free_slots = list(range(max_requests - 1, -1, -1))
+
+    @property
+    def scratch_slot(self) -> int:
+        return self.max_requests
+
+    def scratch_page(self, group: int) -> int:
+        return self.groups[group].pool.num_pages
 
     # ------------------------------------------------------------------ requests
     def live(self) -> list[Hashable]:

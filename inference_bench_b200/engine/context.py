@@ -51,6 +51,9 @@ class StepContext:
     caches: list = field(default_factory=list)
     # parts may keep per-step results here (e.g. rotation tables shared by all layers)
     memo: dict = field(default_factory=dict)
+    # True when the step is being captured into (or replayed from) a CUDA graph: launch shapes must
+    # then depend on the batch's sizes only, never on the host copies of positions or tables
+    fixed_shape: bool = False
 
     @property
     def n_segments(self) -> int:

@@ -1,0 +1,146 @@
+"""Runs the scheduler's steps on the device: the step function, then sampling, tokens back to the host.
+
+Steps that hold only decoded tokens are the launch-bound inner loop of generation, so they are
+replayed as CUDA graphs, one per padded batch size (1, 2, 4, ... rows), like the reference's
+`Stepper` (crates/specrt/src/runtime/step.rs:8-20, 197-228): all inputs of such a step live in one
+static device buffer that a single copy fills, padded rows write to a scratch page and a scratch
+slot, and the graph holds the whole model, the sampling kernel included.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import numpy as np
+import torch
+
+from ..sampling.params import SamplingParams
+from ..sampling.sampler import Sampler
+from .context import Segment, StepContext
+from .step import ModelRunner, StepEntry
+
+
+class _DecodeGraph:
+    """The captured decode step for `rows` rows and the static buffers it reads and writes."""
+
+    def __init__(self, runner: ModelRunner, rows: int):
+        self.runner, self.rows = runner, rows
+        cache, rt = runner.cache, runner.rt
+        B, W = rows, cache.table_width
+        n_groups = len(cache.groups)
+        # layout of the int32 input block: tokens | positions | seg_pos0 | seg_slot | params[B,6] | tables[g][B,W]
+        self.n_ints = 4 * B + 6 * B + n_groups * B * W
+        self.host = torch.zeros(self.n_ints, dtype=torch.int32).pin_memory()
+        self.dev = torch.zeros(self.n_ints, dtype=torch.int32, device=rt.device)
+        h = self.host.numpy()
+        self.h_tokens, self.h_pos, self.h_pos0, self.h_slot = h[0:B], h[B:2 * B], h[2 * B:3 * B], h[3 * B:4 * B]
+        self.h_params = h[4 * B:10 * B].reshape(B, 6)
+        self.h_tables = [h[10 * B + g * B * W:10 * B + (g + 1) * B * W].reshape(B, W) for g in range(n_groups)]
+        d = self.dev
+        self.d_tables = [d[10 * B + g * B * W:10 * B + (g + 1) * B * W].view(B, W) for g in range(n_groups)]
+        const = torch.arange(B + 1, dtype=torch.int32, device=rt.device)
+        segs = [Segment(None, cache.scratch_slot, 0, [0], [0]) for _ in range(B)]
+        ar = np.arange(B, dtype=np.int32)
+        self.ctx = StepContext(
+            rt, segs, B, self.h_tokens, self.h_pos, ar, np.arange(B + 1, dtype=np.int32), self.h_pos0, self.h_slot, ar,
+            token_ids=d[0:B], positions=d[B:2 * B], seg_of_token=const[:B], seg_start=const, seg_pos0=d[2 * B:3 * B], seg_slot=d[3 * B:4 * B],
+            logit_rows=const[:B], caches=cache.views(self.d_tables))
+        self.ctx.fixed_shape = True
+        self.d_params = d[4 * B:10 * B].view(B, 6)
+        self.tokens = torch.zeros(B, dtype=torch.int32, device=rt.device)
+        self.h_out = torch.zeros(B, dtype=torch.int32).pin_memory()
+        self.logits: Optional[torch.Tensor] = None
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self._pad_all()
+
+    def _pad_all(self) -> None:
+        cache = self.runner.cache
+        self.h_tokens[:] = 0
+        self.h_pos[:] = 0
+        self.h_pos0[:] = 0
+        self.h_slot[:] = cache.scratch_slot
+        self.h_params[:] = 0
+        for g, t in enumerate(self.h_tables):
+            t[:] = cache.scratch_page(g)
+
+    def _forward(self) -> None:
+        from ..kernels import ops
+        self.ctx.memo = {}
+        self.logits = self.runner.decoder.forward(self.ctx)
+        ops.sample_rows(self.logits, self.d_params, self.tokens)
+
+    def capture(self) -> None:
+        self.dev.copy_(self.host, non_blocking=True)
+        stream = torch.cuda.Stream(device=self.runner.rt.device)
+        stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stream):
+            for _ in range(2):   # warm-up outside the capture: lazy kernel attributes, allocator
+                self._forward()
+        torch.cuda.current_stream().wait_stream(stream)
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self._forward()
+
+    def run(self, entries: list[StepEntry], sampling: list[tuple[SamplingParams, int]]) -> list[int]:
+        cache = self.runner.cache
+        n = len(entries)
+        if n < self.rows:
+            self._pad_all()
+        for i, e in enumerate(entries):
+            pos = cache.length(e.request)
+            self.h_tokens[i] = e.tokens[0]
+            self.h_pos[i] = pos
+            self.h_pos0[i] = pos
+            self.h_slot[i] = cache.slot(e.request)
+            self.h_params[i] = sampling[i][0].row(sampling[i][1])
+            for g, t in enumerate(self.h_tables):
+                t[i] = cache.table(g, e.request)
+        self.dev.copy_(self.host, non_blocking=True)
+        self.graph.replay()
+        self.h_out.copy_(self.tokens, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return self.h_out[:n].tolist()
+
+
+class GpuExecutor:
+    def __init__(self, runner: ModelRunner, use_graphs: bool = True, max_graph_rows: int = 256):
+        self.runner = runner
+        self.sampler = Sampler(runner.rt.device)
+        self.use_graphs, self.max_graph_rows = use_graphs, max_graph_rows
+        self._graphs: dict[int, _DecodeGraph] = {}
+        self.last_logits: Optional[torch.Tensor] = None
+        self.steps = 0
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+
+    def execute(self, entries: list[StepEntry], sampling: list[tuple[SamplingParams, int]]) -> list[int]:
+        self.steps += 1
+        cache = self.runner.cache
+        if self.use_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries) and len(entries) <= self.max_graph_rows:
+            rows = 1
+            while rows < len(entries):
+                rows *= 2
+            g = self._graphs.get(rows)
+            if g is None:
+                g = self._graphs[rows] = _DecodeGraph(self.runner, rows)
+                g.capture()
+            for e in entries:
+                tok = e.tokens[0]
+                if not 0 <= tok < self.runner.vocab:
+                    raise ValueError(f"request {e.request!r}: token id {tok} is outside the vocabulary of {self.runner.vocab}")
+                cache.extend(e.request, cache.length(e.request) + 1)
+            out = g.run(entries, sampling)
+            for e in entries:
+                cache.commit(e.request, cache.length(e.request) + 1)
+            self.last_logits = g.logits
+            self.h2d_bytes += g.n_ints * 4
+            self.d2h_bytes += g.rows * 4
+            return out
+        logits = self.runner.step(entries, check=False)
+        if logits is None:
+            return []
+        tokens = self.sampler.sample(logits, [p for p, _ in sampling], [s for _, s in sampling])
+        self.last_logits = logits
+        self.h2d_bytes += sum(len(e.tokens) for e in entries) * 12 + len(entries) * (12 + 4 * cache.table_width * len(cache.groups)) + len(sampling) * 28
+        self.d2h_bytes += len(sampling) * 4
+        return tokens.cpu().tolist()
