@@ -1,0 +1,268 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine at Qwen3-8B shape with random bfloat16 weights.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--batch B] [--impl ours|reference]
+
+A "step" is one decode step of a batch of 8 requests whose contexts start at 2,048 tokens (the
+context length of the benchmark is 4,096). `value` is decoded tokens per second with the steps
+enqueued back to back (sampled tokens fed back on the device) and timed with CUDA events; `e2e` is the
+same through the Python entry point (`Engine.submit` / `Engine.step`), every step taking its inputs
+from pinned host memory and handing its tokens back to the host. One JSON line is printed.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# Qwen3-8B layer sizes: the third configuration the baseline names.
+QWEN3_8B = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=151936, hidden_size=4096, intermediate_size=12288,
+    num_hidden_layers=36, num_attention_heads=32, num_key_value_heads=8, head_dim=128, rms_norm_eps=1e-6, rope_theta=1000000.0,
+    tie_word_embeddings=False, max_position_embeddings=40960, hidden_act="silu", attention_bias=False, torch_dtype="bfloat16")
+CONTEXT = 4096          # benchmark context length
+PROMPT = 2048           # prefill length, and the context each decode request starts from
+PAGE = 16
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def peaks() -> tuple[dict, str]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows: list[list[str]] = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        rows = [r for r in self.rows if len(r) >= 7]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[3 + i].lower().startswith("active") for r in rows)]
+        num = lambda s: float(s) if s.replace(".", "", 1).isdigit() else None
+        sm = [num(r[0]) for r in rows if num(r[0]) is not None]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": num(rows[0][1]), "reasons": reasons, "samples": len(rows)}
+
+
+def weight_bytes(cfg: dict, layers: int) -> int:
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    q = cfg["num_attention_heads"] * cfg["head_dim"]
+    kv = cfg["num_key_value_heads"] * cfg["head_dim"]
+    per_layer = (q + 2 * kv) * H + H * q + 2 * I * H + H * I
+    return 2 * (layers * per_layer + V * H)      # bfloat16; the lm_head is read once per step, the embedding rows are negligible
+
+
+def kv_bytes_per_token(cfg: dict, layers: int) -> int:
+    return 2 * 2 * cfg["num_key_value_heads"] * cfg["head_dim"] * layers
+
+
+def prefill_flops(cfg: dict, layers: int, T: int) -> float:
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    q = cfg["num_attention_heads"] * cfg["head_dim"]
+    kv = cfg["num_key_value_heads"] * cfg["head_dim"]
+    linear = 2.0 * T * layers * ((q + 2 * kv) * H + H * q + 2 * I * H + H * I)
+    attention = layers * 4.0 * (T * (T + 1) / 2) * q     # QK^T and PV over the causal half
+    return linear + attention + 2.0 * V * H
+
+
+def _prompt(seed: int, n: int, vocab: int) -> list[int]:
+    import numpy as np
+    return np.random.default_rng(seed).integers(0, vocab, size=n).tolist()
+
+
+def measure_prefill(engine, steps: int, warmup: int) -> float:
+    """Milliseconds for one step that prefills a PROMPT-token prompt and returns its last logits."""
+    import torch
+    from inference_bench_b200.engine.step import StepEntry
+    vocab = engine.decoder.plan.vocab_size
+    times = []
+    for i in range(warmup + steps):
+        rid = ("prefill", i)
+        toks = _prompt(1000 + i, PROMPT, vocab)
+        engine.cache.admit(rid)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        engine.runner.step([StepEntry(rid, toks, [PROMPT - 1])], check=False)
+        e1.record()
+        torch.cuda.synchronize()
+        engine.cache.release(rid)
+        if i >= warmup:
+            times.append(e0.elapsed_time(e1))
+    engine.rt.check_status()
+    return statistics.median(times)
+
+
+def measure_decode_device(engine, batch: int, steps: int, warmup: int) -> tuple[float, int]:
+    """Milliseconds per decode step of `batch` requests whose contexts start at PROMPT tokens, steps
+    enqueued back to back with tokens fed back on the device; and kernel launches per step."""
+    import torch
+    from inference_bench_b200.engine.executor import RUN_AHEAD_MAX
+    from inference_bench_b200.engine.step import StepEntry
+    from inference_bench_b200.sampling.params import GREEDY
+    vocab = engine.decoder.plan.vocab_size
+    ids = [("decode", batch, i) for i in range(batch)]
+    last = []
+    for i, rid in enumerate(ids):
+        engine.cache.admit(rid)
+        logits = engine.runner.step([StepEntry(rid, _prompt(2000 + i, PROMPT, vocab), [PROMPT - 1])], check=False)
+        last.append(int(engine.executor.sampler.sample(logits, [GREEDY], [0]).item()))
+    generated = 1
+
+    def run(n):
+        nonlocal last, generated
+        done = 0
+        while done < n:
+            k = min(RUN_AHEAD_MAX, n - done)
+            entries = [StepEntry(rid, [tok], [0]) for rid, tok in zip(ids, last)]
+            hist = engine.executor.decode_ahead(entries, [(GREEDY, generated)] * batch, k)
+            last = hist[-1]
+            generated += k
+            done += k
+
+    run(max(warmup, 1))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    run(steps)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    launches = engine.executor.graph_for(batch).launches
+    for rid in ids:
+        engine.cache.release(rid)
+    engine.rt.check_status()
+    return ms, launches
+
+
+def measure_decode_e2e(engine, batch: int, steps: int, warmup: int) -> tuple[float, float, float]:
+    """Milliseconds per decode step through Engine.submit / Engine.step: host token ids in (pinned
+    staging, copied every step) and sampled token ids back on the host every step."""
+    import torch
+    vocab = engine.decoder.plan.vocab_size
+    for i in range(batch):
+        engine.submit(_prompt(3000 + i, PROMPT, vocab), max_tokens=warmup + steps + 8)
+    while engine.scheduler.waiting or any(not s.decoding for s in engine.scheduler.running):
+        engine.step()
+    for _ in range(max(warmup, 1)):
+        engine.step()
+    ex = engine.executor
+    h0, d0 = ex.h2d_bytes, ex.d2h_bytes
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    emitted = 0
+    for _ in range(steps):
+        emitted += len(engine.step().emitted)
+    torch.cuda.synchronize()
+    t1 = time.perf_counter()
+    assert emitted == batch * steps, f"{emitted} tokens emitted in {steps} steps of {batch} requests"
+    h2d, d2h = (ex.h2d_bytes - h0) / steps, (ex.d2h_bytes - d0) / steps
+    for s in list(engine.scheduler.running):
+        engine.cancel(s.req.id)
+    engine.rt.check_status()
+    return (t1 - t0) * 1e3 / steps, h2d, d2h
+
+
+def run_ours(args) -> dict:
+    import torch
+    from inference_bench_b200 import Engine
+    pk, pk_src = peaks()
+    cfg = dict(QWEN3_8B)
+    full_layers = cfg["num_hidden_layers"]
+    cfg["num_hidden_layers"] = layers = args.layers or full_layers
+    big = max(args.batch, 64)
+    engine = Engine(cfg, dtype="bfloat16", max_ctx=CONTEXT, page_size=PAGE, num_pages=big * (CONTEXT // PAGE) + 64, max_num_seqs=big,
+                    max_batched_tokens=8192, prefill_chunk=PROMPT, random_weights_seed=0)
+    steps, warmup = args.steps, max(args.warmup, 3)
+
+    prefill_ms = measure_prefill(engine, 5, 3)
+    b1_ms, _ = measure_decode_device(engine, 1, steps, warmup)
+    b64_ms, _ = measure_decode_device(engine, 64, min(steps, 64), warmup)
+    clocks = ClockSampler()
+    clocks.start()
+    ms, launches = measure_decode_device(engine, args.batch, steps, warmup)
+    clock_report = clocks.stop()
+    e2e_ms, h2d, d2h = measure_decode_e2e(engine, args.batch, steps, warmup)
+
+    B = args.batch
+    avg_ctx = PROMPT + 1 + warmup + steps / 2
+    step_bytes = weight_bytes(cfg, layers) + B * avg_ctx * kv_bytes_per_token(cfg, layers)
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+    flops = prefill_flops(cfg, layers, PROMPT)
+    return {
+        "metric": "decode tok/s at batch 8 (Qwen3-8B shape, random bf16 weights, context 2048 growing toward 4096)",
+        "value": B * 1e3 / ms, "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"model": "Qwen3-8B shape", "layers": layers, "layers_full": full_layers, "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
+                   "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"],
+                   "vocab": cfg["vocab_size"], "global_batch": B, "seq_len": CONTEXT, "decode_context_start": PROMPT, "prefill_tokens": PROMPT,
+                   "page_size": PAGE, "weights": "random N(0,0.02) bf16 seed 0", "parallelism": "single_gpu",
+                   "l2": "inputs larger than L2 (weights read every step)", "peaks": pk_src},
+        "e2e": {"value": B * 1e3 / e2e_ms, "unit": "tok/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches * steps,
+        "prefill": {"value": PROMPT * 1e3 / prefill_ms, "tokens": PROMPT, "ms": prefill_ms, "frac": flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12)},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"]},
+        "points": {"decode_b1": 1e3 / b1_ms, "decode_b64": 64e3 / b64_ms},
+        "clocks": clock_report,
+    }
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (both numbers are reported)")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": "the reference is a Rust workspace (no setup.py/pyproject.toml): pip cannot install it and no Rust toolchain is present"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported, run with --gpus 1")
+        return 2
+    if args.steps + max(args.warmup, 3) + 8 > CONTEXT - PROMPT:
+        print(f"--steps + --warmup must stay below {CONTEXT - PROMPT - 8}: contexts start at {PROMPT} and end at {CONTEXT}")
+        return 2
+    print(json.dumps(run_ours(args)))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

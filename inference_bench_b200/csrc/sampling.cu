@@ -178,7 +178,38 @@ __global__ void __launch_bounds__(kThreads) sample_rows_kernel(const float* __re
   }
 }
 
+// After a decode step: feed every row's sampled token back as its next input, move its position on
+// by one, count its sampling step, and log the token. With this at the end of a captured decode
+// step the graph can be replayed many times with no host work in between; the host reads the log
+// afterwards (the reference's argmax_advance does the same for one row:
+// crates/kir/tests/golden/prims/prims_sm120.cu:252-294).
+__global__ void advance_rows_kernel(const int* __restrict__ sampled, int* __restrict__ token_in, int* __restrict__ positions,
+                                    int* __restrict__ pos0, RowParams* __restrict__ params, int* __restrict__ history, int* __restrict__ count,
+                                    int rows, int history_len) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  int c = count[0];
+  if (i < rows) {
+    int tok = sampled[i];
+    token_in[i] = tok;
+    positions[i] += 1;
+    pos0[i] += 1;
+    params[i].step += 1;
+    if (c < history_len) history[(size_t)c * rows + i] = tok;
+  }
+  __syncthreads();
+  if (i == 0) count[0] = c + 1;
+}
+
 }  // namespace
+
+extern "C" int ib_advance_rows(const int* sampled, int* token_in, int* positions, int* pos0, void* params, int* history, int* count, int rows,
+                               int history_len, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  IB_CHECK_ARG(rows > 0 && rows <= 1024 && history_len >= 0, "advance_rows: bad sizes rows=%d history=%d", rows, history_len);
+  advance_rows_kernel<<<1, 1024, 0, stream>>>(sampled, token_in, positions, pos0, (RowParams*)params, history, count, rows, history_len);
+  IB_CHECK_LAUNCH("advance_rows");
+  return 0;
+}
 
 extern "C" int ib_sample_rows(const float* logits, int rows, int V, const void* params, int* tokens, cudaStream_t stream) {
   if (rows == 0) return 0;

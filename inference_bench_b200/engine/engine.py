@@ -95,6 +95,21 @@ class Engine:
         self.tokens("")
         return self._tokenizer.decode(list(ids))
 
+    # ------------------------------------------------------------------ streaming interface
+    def submit(self, prompt: Sequence[int], max_tokens: int = 64, sampling: SamplingParams = GREEDY, stop_ids: Sequence[int] = ()) -> int:
+        """Queue one request; returns its id. Raises `Refused` for a request that can never run."""
+        rid = self._next_id
+        self._next_id += 1
+        self.scheduler.submit(Request(rid, list(prompt), max_tokens, sampling, tuple(stop_ids)))
+        return rid
+
+    def step(self):
+        """One scheduler step on the device; returns its StepReport (tokens emitted, requests finished)."""
+        return self.scheduler.step(self.executor)
+
+    def cancel(self, rid: int):
+        return self.scheduler.cancel(rid)
+
     # ------------------------------------------------------------------ generation
     def generate(self, prompt, max_tokens: int = 64, sampling: Union[SamplingParams, Sequence[SamplingParams]] = GREEDY,
                  stop_ids: Sequence[int] = ()) -> Union[Reply, list[Reply]]:

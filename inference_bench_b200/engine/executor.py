@@ -19,6 +19,9 @@ from .context import Segment, StepContext
 from .step import ModelRunner, StepEntry
 
 
+RUN_AHEAD_MAX = 64
+
+
 class _DecodeGraph:
     """The captured decode step for `rows` rows and the static buffers it reads and writes."""
 
@@ -27,8 +30,8 @@ class _DecodeGraph:
         cache, rt = runner.cache, runner.rt
         B, W = rows, cache.table_width
         n_groups = len(cache.groups)
-        # layout of the int32 input block: tokens | positions | seg_pos0 | seg_slot | params[B,6] | tables[g][B,W]
-        self.n_ints = 4 * B + 6 * B + n_groups * B * W
+        # layout of the int32 input block: tokens | positions | seg_pos0 | seg_slot | params[B,6] | tables[g][B,W] | count
+        self.n_ints = 4 * B + 6 * B + n_groups * B * W + 1
         self.host = torch.zeros(self.n_ints, dtype=torch.int32).pin_memory()
         self.dev = torch.zeros(self.n_ints, dtype=torch.int32, device=rt.device)
         h = self.host.numpy()
@@ -46,6 +49,9 @@ class _DecodeGraph:
             logit_rows=const[:B], caches=cache.views(self.d_tables))
         self.ctx.fixed_shape = True
         self.d_params = d[4 * B:10 * B].view(B, 6)
+        self.d_count = d[self.n_ints - 1:self.n_ints]
+        self.history = torch.zeros((RUN_AHEAD_MAX, B), dtype=torch.int32, device=rt.device)
+        self.h_history = torch.zeros((RUN_AHEAD_MAX, B), dtype=torch.int32).pin_memory()
         self.tokens = torch.zeros(B, dtype=torch.int32, device=rt.device)
         self.h_out = torch.zeros(B, dtype=torch.int32).pin_memory()
         self.logits: Optional[torch.Tensor] = None
@@ -67,6 +73,8 @@ class _DecodeGraph:
         self.ctx.memo = {}
         self.logits = self.runner.decoder.forward(self.ctx)
         ops.sample_rows(self.logits, self.d_params, self.tokens)
+        c = self.ctx
+        ops.advance_rows(self.tokens, c.token_ids, c.positions, c.seg_pos0, self.d_params, self.history, self.d_count)
 
     def capture(self) -> None:
         self.dev.copy_(self.host, non_blocking=True)
@@ -77,11 +85,37 @@ class _DecodeGraph:
                 self._forward()
         torch.cuda.current_stream().wait_stream(stream)
         torch.cuda.synchronize()
+        from ..kernels import lib
+        before = lib.launches
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph):
             self._forward()
+        self.launches = lib.launches - before    # kernels in one replay
+
+    def run_ahead(self, entries: list[StepEntry], sampling: list[tuple[SamplingParams, int]], steps: int) -> list[list[int]]:
+        """`steps` decode steps with no host work in between: every step's sampled tokens are the next
+        step's inputs on the device. The requests' pages for all `steps` positions must be allocated.
+        Returns the tokens of every step, [steps][rows]."""
+        if not 1 <= steps <= RUN_AHEAD_MAX:
+            raise ValueError(f"run_ahead takes 1 to {RUN_AHEAD_MAX} steps, got {steps}")
+        self._fill(entries, sampling)
+        self.dev.copy_(self.host, non_blocking=True)
+        for _ in range(steps):
+            self.graph.replay()
+        self.h_history.copy_(self.history, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return self.h_history[:steps, :len(entries)].tolist()
 
     def run(self, entries: list[StepEntry], sampling: list[tuple[SamplingParams, int]]) -> list[int]:
+        n = len(entries)
+        self._fill(entries, sampling)
+        self.dev.copy_(self.host, non_blocking=True)
+        self.graph.replay()
+        self.h_out.copy_(self.tokens, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return self.h_out[:n].tolist()
+
+    def _fill(self, entries: list[StepEntry], sampling: list[tuple[SamplingParams, int]]) -> None:
         cache = self.runner.cache
         n = len(entries)
         if n < self.rows:
@@ -95,11 +129,6 @@ class _DecodeGraph:
             self.h_params[i] = sampling[i][0].row(sampling[i][1])
             for g, t in enumerate(self.h_tables):
                 t[i] = cache.table(g, e.request)
-        self.dev.copy_(self.host, non_blocking=True)
-        self.graph.replay()
-        self.h_out.copy_(self.tokens, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        return self.h_out[:n].tolist()
 
 
 class GpuExecutor:
@@ -113,17 +142,35 @@ class GpuExecutor:
         self.h2d_bytes = 0
         self.d2h_bytes = 0
 
+    def graph_for(self, n_rows: int) -> _DecodeGraph:
+        rows = 1
+        while rows < n_rows:
+            rows *= 2
+        g = self._graphs.get(rows)
+        if g is None:
+            g = self._graphs[rows] = _DecodeGraph(self.runner, rows)
+            g.capture()
+        return g
+
+    def decode_ahead(self, entries: list[StepEntry], sampling: list[tuple[SamplingParams, int]], steps: int) -> list[list[int]]:
+        """Several decode steps of the same requests in a row, tokens fed back on the device."""
+        cache = self.runner.cache
+        g = self.graph_for(len(entries))
+        for e in entries:
+            cache.extend(e.request, cache.length(e.request) + steps)
+        out = g.run_ahead(entries, sampling, steps)
+        for e in entries:
+            cache.commit(e.request, cache.length(e.request) + steps)
+        self.steps += steps
+        self.h2d_bytes += g.n_ints * 4
+        self.d2h_bytes += steps * g.rows * 4
+        return out
+
     def execute(self, entries: list[StepEntry], sampling: list[tuple[SamplingParams, int]]) -> list[int]:
         self.steps += 1
         cache = self.runner.cache
         if self.use_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries) and len(entries) <= self.max_graph_rows:
-            rows = 1
-            while rows < len(entries):
-                rows *= 2
-            g = self._graphs.get(rows)
-            if g is None:
-                g = self._graphs[rows] = _DecodeGraph(self.runner, rows)
-                g.capture()
+            g = self.graph_for(len(entries))
             for e in entries:
                 tok = e.tokens[0]
                 if not 0 <= tok < self.runner.vocab:

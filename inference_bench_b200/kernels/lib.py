@@ -52,6 +52,7 @@ _SIGNATURES = {
     "ib_attention_generic": [_p, _i, C.POINTER(KvView), _p, _p, _i, _f, _p, _i, _i, _p, _p],
     "ib_gemm_simt": [_p, _i, _p, _i, _p, _i, _i, _i, _p],
     "ib_sample_rows": [_p, _i, _i, _p, _p, _p],
+    "ib_advance_rows": [_p, _p, _p, _p, _p, _p, _p, _i, _i, _p],
 }
 
 _lib: Optional[C.CDLL] = None
@@ -93,8 +94,13 @@ def register(name: str, argtypes: list) -> None:
         fn.restype = C.c_int
 
 
+launches = 0   # kernel entry points called so far (each launches one kernel)
+
+
 def call(name: str, *args) -> None:
+    global launches
     lib = load()
+    launches += 1
     rc = getattr(lib, name)(*args)
     if rc != 0:
         raise KernelError(lib.ib_last_error().decode(errors="replace"))

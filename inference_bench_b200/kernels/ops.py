@@ -173,3 +173,16 @@ def sample_rows(logits: torch.Tensor, params: torch.Tensor, tokens: torch.Tensor
     _check("params", params, torch.int32, (rows, 6))
     _check("tokens", tokens, torch.int32, (rows,))
     L.call("ib_sample_rows", logits.data_ptr(), rows, V, params.data_ptr(), tokens.data_ptr(), _stream())
+
+
+def advance_rows(sampled: torch.Tensor, token_in: torch.Tensor, positions: torch.Tensor, pos0: torch.Tensor, params: torch.Tensor,
+                 history: torch.Tensor, count: torch.Tensor) -> None:
+    """Feed sampled tokens back as the next inputs of a decode batch and log them: history[count, :] = sampled."""
+    rows = sampled.shape[0]
+    for name, t in (("sampled", sampled), ("token_in", token_in), ("positions", positions), ("pos0", pos0)):
+        _check(name, t, torch.int32, (rows,))
+    _check("params", params, torch.int32, (rows, 6))
+    _check("history", history, torch.int32)
+    _check("count", count, torch.int32, (1,))
+    L.call("ib_advance_rows", sampled.data_ptr(), token_in.data_ptr(), positions.data_ptr(), pos0.data_ptr(), params.data_ptr(), history.data_ptr(),
+           count.data_ptr(), rows, history.shape[0], _stream())
