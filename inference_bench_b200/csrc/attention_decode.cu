@@ -1,0 +1,237 @@
+// Decode attention over the paged cache, bfloat16, split over the context.
+//
+// One CTA = one decoded token's kv head and one 128-key slice of its context. The query heads that
+// share the kv head (the GQA group, up to 16) are the rows of a 16-row MMA tile, so keys and values
+// are read from memory once per group. Each of the 4 warps takes 32 keys of the slice:
+// S = Q K^T (m16n8k16 bfloat16 MMAs, float32 accumulators), softmax statistics in float32 base 2,
+// O = P V; the warps' partial results are merged in shared memory and written to scratch as an
+// unnormalised (max, sum, O) triple per (token, head, slice). A second kernel merges the slices.
+// Slices are cut at fixed absolute key positions, so a token's result does not depend on the batch.
+// Reference design: crates/kir/src/cuda/attention/decode.rs, combine.rs (split-KV with packed GQA rows).
+#include "kv_view.cuh"
+#include "mma_tiles.cuh"
+
+namespace {
+
+constexpr int kSlice = 128;  // keys per CTA
+constexpr int kWarps = 4;
+
+template <int HD>
+__global__ void __launch_bounds__(kWarps * 32)
+    decode_split_kernel(const __nv_bfloat16* __restrict__ q, IbKvView kv, const int* __restrict__ dec_tokens,
+                        const int* __restrict__ positions, const int* __restrict__ seg_of_token, int window, float scale_log2e,
+                        float* __restrict__ part_o, float* __restrict__ part_ml, int heads, int max_slices, unsigned* __restrict__ status) {
+  constexpr int CPR = HD / 8;  // 16-byte chunks per row
+  extern __shared__ __align__(128) uint8_t smem[];
+  // layout: Q tile [16][HD] | K tile [128][HD] | V tile [128][HD]; the merge buffers reuse K and V
+  const uint32_t q_s = mt::smem_u32(smem);
+  const uint32_t k_s = q_s + 16 * HD * 2;
+  const uint32_t v_s = k_s + kSlice * HD * 2;
+
+  const int kvh = blockIdx.x, item = blockIdx.y, slice = blockIdx.z;
+  const int t = dec_tokens[item];
+  const int pos = positions[t], seg = seg_of_token[t];
+  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int k0 = slice * kSlice;
+  const int k_begin = max(lo, k0), k_end = min(pos + 1, k0 + kSlice);
+  if (k_begin >= k_end) return;
+  const int group = heads / kv.kv_heads;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  // ---- stage Q (rows = the group's heads, zero rows above), K and V of the slice
+  for (int idx = tid; idx < 16 * CPR; idx += kWarps * 32) {
+    int row = idx / CPR, c = idx % CPR;
+    uint32_t dst = q_s + mt::tile_offset<HD>(row, c);
+    if (row < group)
+      mt::cp_async16(dst, q + ((size_t)t * heads + (size_t)kvh * group + row) * HD + c * 8);
+    else
+      mt::st_shared_zero16(dst);
+  }
+  const __nv_bfloat16* base = (const __nv_bfloat16*)kv.base;
+  bool bad_page = false;
+  for (int idx = tid; idx < kSlice * CPR; idx += kWarps * 32) {
+    int row = idx / CPR, c = idx % CPR;
+    int key = k0 + row;
+    long long off = (key >= k_begin && key < k_end) ? ib::kv_offset(kv, seg, key, kvh) : -2;
+    uint32_t kd = k_s + mt::tile_offset<HD>(row, c), vd = v_s + mt::tile_offset<HD>(row, c);
+    if (off >= 0) {
+      mt::cp_async16(kd, base + off + c * 8);
+      mt::cp_async16(vd, base + off + kv.v_offset + c * 8);
+    } else {
+      if (off == -1) bad_page = true;
+      mt::st_shared_zero16(kd);
+      mt::st_shared_zero16(vd);
+    }
+  }
+  if (bad_page) atomicOr(status, IB_ERR_BAD_PAGE);
+  mt::cp_async_commit();
+  mt::cp_async_wait<0>();
+  __syncthreads();
+
+  // ---- S = Q K^T for this warp's 32 keys
+  const int wkey = warp * 32;
+  float s[4][4];
+#pragma unroll
+  for (int j = 0; j < 4; j++)
+#pragma unroll
+    for (int e = 0; e < 4; e++) s[j][e] = 0.f;
+#pragma unroll
+  for (int kk = 0; kk < HD / 16; kk++) {
+    uint32_t a[4], b[4];
+    mt::load_a_frag<HD>(q_s, 0, kk, lane, a);
+#pragma unroll
+    for (int pr = 0; pr < 2; pr++) {
+      mt::load_k_frag<HD>(k_s, wkey + 16 * pr, kk, lane, b);
+      mt::mma_16816(s[2 * pr], a, b[0], b[1]);
+      mt::mma_16816(s[2 * pr + 1], a, b[2], b[3]);
+    }
+  }
+  // ---- mask, softmax statistics (rows g and g+8 of the tile; columns = keys)
+  const int g = lane >> 2, tq = lane & 3;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+#pragma unroll
+  for (int j = 0; j < 4; j++)
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+      int key = k0 + wkey + 8 * j + 2 * tq + (e & 1);
+      float v = (key >= k_begin && key < k_end) ? s[j][e] * scale_log2e : -INFINITY;
+      s[j][e] = v;
+      m[e >> 1] = fmaxf(m[e >> 1], v);
+    }
+#pragma unroll
+  for (int r = 0; r < 2; r++) {
+    m[r] = fmaxf(m[r], __shfl_xor_sync(0xffffffffu, m[r], 1));
+    m[r] = fmaxf(m[r], __shfl_xor_sync(0xffffffffu, m[r], 2));
+  }
+  const float mu[2] = {m[0] == -INFINITY ? 0.f : m[0], m[1] == -INFINITY ? 0.f : m[1]};
+  uint32_t p[2][4];  // A fragments of P for the two 16-key steps
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    float e0 = exp2f(s[j][0] - mu[0]), e1 = exp2f(s[j][1] - mu[0]), e2 = exp2f(s[j][2] - mu[1]), e3 = exp2f(s[j][3] - mu[1]);
+    l[0] += e0 + e1;
+    l[1] += e2 + e3;
+    p[j >> 1][(j & 1) * 2] = mt::pack_bf16(e0, e1);
+    p[j >> 1][(j & 1) * 2 + 1] = mt::pack_bf16(e2, e3);
+  }
+#pragma unroll
+  for (int r = 0; r < 2; r++) {
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+  }
+  // ---- O = P V over this warp's keys
+  float o[HD / 8][4];
+#pragma unroll
+  for (int n = 0; n < HD / 8; n++)
+#pragma unroll
+    for (int e = 0; e < 4; e++) o[n][e] = 0.f;
+#pragma unroll
+  for (int ks = 0; ks < 2; ks++)
+#pragma unroll
+    for (int dp = 0; dp < HD / 16; dp++) {
+      uint32_t b[4];
+      mt::load_v_frag<HD>(v_s, wkey + 16 * ks, dp, lane, b);
+      mt::mma_16816(o[2 * dp], p[ks], b[0], b[1]);
+      mt::mma_16816(o[2 * dp + 1], p[ks], b[2], b[3]);
+    }
+  // ---- merge the four warps through shared memory (K and V tiles are no longer needed)
+  __syncthreads();
+  float* ml_s = (float*)(smem + 16 * HD * 2);                  // [warps][16][2]
+  float* o_s = ml_s + kWarps * 16 * 2;                         // [warps][16][HD]
+  if (tq == 0) {
+    ml_s[(warp * 16 + g) * 2] = m[0];
+    ml_s[(warp * 16 + g) * 2 + 1] = l[0];
+    ml_s[(warp * 16 + g + 8) * 2] = m[1];
+    ml_s[(warp * 16 + g + 8) * 2 + 1] = l[1];
+  }
+#pragma unroll
+  for (int n = 0; n < HD / 8; n++) {
+    int d = 8 * n + 2 * tq;
+    *(float2*)&o_s[(warp * 16 + g) * HD + d] = make_float2(o[n][0], o[n][1]);
+    *(float2*)&o_s[(warp * 16 + g + 8) * HD + d] = make_float2(o[n][2], o[n][3]);
+  }
+  __syncthreads();
+  for (int idx = tid; idx < group * HD; idx += kWarps * 32) {
+    int row = idx / HD, d = idx % HD;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kWarps; w++) M = fmaxf(M, ml_s[(w * 16 + row) * 2]);
+    float L = 0.f, O = 0.f;
+#pragma unroll
+    for (int w = 0; w < kWarps; w++) {
+      float mw = ml_s[(w * 16 + row) * 2];
+      float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
+      L += ml_s[(w * 16 + row) * 2 + 1] * f;
+      O += o_s[(w * 16 + row) * HD + d] * f;
+    }
+    size_t slot = ((size_t)item * heads + (size_t)kvh * group + row) * max_slices + slice;
+    part_o[slot * HD + d] = O;
+    if (d == 0) {
+      part_ml[slot * 2] = M;
+      part_ml[slot * 2 + 1] = L;
+    }
+  }
+}
+
+// out[token][head] = sum over the slices that hold visible keys of O_s 2^(m_s - M) / sum of l_s 2^(m_s - M)
+template <int HD>
+__global__ void decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, const int* __restrict__ dec_tokens,
+                                      const int* __restrict__ positions, int window, __nv_bfloat16* __restrict__ out, int heads, int max_slices) {
+  const int h = blockIdx.x, item = blockIdx.y;
+  const int t = dec_tokens[item];
+  const int pos = positions[t];
+  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int s_begin = lo / kSlice, s_end = pos / kSlice + 1;
+  const size_t slot0 = ((size_t)item * heads + h) * max_slices;
+  float M = -INFINITY;
+  for (int s = s_begin; s < s_end; s++) M = fmaxf(M, part_ml[(slot0 + s) * 2]);
+  for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+    float L = 0.f, O = 0.f;
+    for (int s = s_begin; s < s_end; s++) {
+      float f = exp2f(part_ml[(slot0 + s) * 2] - M);
+      L += part_ml[(slot0 + s) * 2 + 1] * f;
+      O += part_o[(slot0 + s) * HD + d] * f;
+    }
+    out[((size_t)t * heads + h) * HD + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+  }
+}
+
+template <int HD>
+int launch(const void* q, const IbKvView* kv, const int* dec_tokens, int n_dec, const int* positions, const int* seg_of_token, int window,
+           float scale, float* part_o, float* part_ml, void* out, int heads, int max_slices, unsigned* status, cudaStream_t stream) {
+  constexpr int smem = (16 + 2 * kSlice) * HD * 2;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(decode_split_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    IB_CHECK_ARG(e == cudaSuccess, "attention_decode: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    configured = true;
+  }
+  dim3 grid(kv->kv_heads, n_dec, max_slices);
+  decode_split_kernel<HD><<<grid, kWarps * 32, smem, stream>>>((const __nv_bfloat16*)q, *kv, dec_tokens, positions, seg_of_token, window,
+                                                               scale * 1.4426950408889634f, part_o, part_ml, heads, max_slices, status);
+  IB_CHECK_LAUNCH("attention_decode split");
+  decode_combine_kernel<HD><<<dim3(heads, n_dec), HD, 0, stream>>>(part_o, part_ml, dec_tokens, positions, window, (__nv_bfloat16*)out, heads,
+                                                                   max_slices);
+  IB_CHECK_LAUNCH("attention_decode combine");
+  return 0;
+}
+
+}  // namespace
+
+// Attention for decoded tokens (one query position each). dec_tokens[i] is the flat row of the i-th
+// decoded token in q/out/positions/seg_of_token. Scratch: part_o float32 [n_dec * heads * max_slices * head_dim],
+// part_ml float32 [n_dec * heads * max_slices * 2]; max_slices * 128 must cover every position in use.
+extern "C" int ib_attention_decode(const void* q, const IbKvView* kv, const int* dec_tokens, int n_dec, const int* positions,
+                                   const int* seg_of_token, int window, float scale, float* part_o, float* part_ml, void* out, int heads,
+                                   int max_slices, unsigned* status, cudaStream_t stream) {
+  if (n_dec == 0) return 0;
+  IB_CHECK_ARG(kv && kv->base && kv->block_table, "attention_decode: the cache view has a null pointer");
+  IB_CHECK_ARG(kv->dtype == IB_BF16, "attention_decode: the cache must be bfloat16");
+  IB_CHECK_ARG(kv->kv_heads > 0 && heads % kv->kv_heads == 0 && heads / kv->kv_heads <= 16,
+               "attention_decode: %d query heads on %d kv heads (groups of up to 16 are supported)", heads, kv->kv_heads);
+  IB_CHECK_ARG(n_dec > 0 && n_dec <= 65535 && max_slices > 0 && max_slices <= 65535, "attention_decode: bad sizes n=%d slices=%d", n_dec, max_slices);
+  if (kv->head_dim == 128)
+    return launch<128>(q, kv, dec_tokens, n_dec, positions, seg_of_token, window, scale, part_o, part_ml, out, heads, max_slices, status, stream);
+  if (kv->head_dim == 64)
+    return launch<64>(q, kv, dec_tokens, n_dec, positions, seg_of_token, window, scale, part_o, part_ml, out, heads, max_slices, status, stream);
+  return ib_set_error("attention_decode: head_dim %d has no tensor-core kernel (64 and 128 have)", kv->head_dim);
+}

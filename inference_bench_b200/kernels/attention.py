@@ -1,17 +1,78 @@
-"""Chooses the attention kernel for a step: tensor-core kernels where a specialisation exists for
-the head size and precision, the generic kernel otherwise. All of them read keys and values
-through the block table and give the same result up to rounding."""
+"""Chooses the attention kernels for a step. bfloat16 with a head size of 64 or 128 runs on the
+tensor-core kernels: decoded tokens (segments of one token) on the split-context kernel, prompt
+portions on the flash kernel; everything else (float32, other head sizes, groups above 16) runs on
+the generic kernel. All of them read keys and values through the block table and agree up to rounding.
+"""
 from __future__ import annotations
 
+import ctypes as C
 from typing import Optional
 
+import numpy as np
 import torch
 
+from . import lib as L
 from . import ops
+
+SLICE = 128   # keys per CTA of the decode kernel (csrc/attention_decode.cu)
+QTILE = 64    # query rows per CTA of the prefill kernel (csrc/attention_prefill.cu)
+
+L.register("ib_attention_decode", [L._p, C.POINTER(L.KvView), L._p, L._i, L._p, L._p, L._i, L._f, L._p, L._p, L._p, L._i, L._i, L._p, L._p])
+L.register("ib_attention_prefill", [L._p, C.POINTER(L.KvView), L._p, L._p, L._i, L._p, L._p, L._i, L._f, L._p, L._i, L._p, L._p])
+
+
+def has_tensor_core_kernel(dtype: torch.dtype, head_dim: int, heads: int, kv_heads: int) -> bool:
+    return dtype == torch.bfloat16 and head_dim in (64, 128) and heads // kv_heads <= 16
+
+
+def _work_lists(ctx):
+    """Per step, shared by all layers: flat rows of decoded tokens, and 64-row query tiles of portions."""
+    key = "attention_work"
+    if key in ctx.memo:
+        return ctx.memo[key]
+    if ctx.fixed_shape:
+        work = dict(dec_tokens=ctx.seg_start[:ctx.n_tokens], n_dec=ctx.n_tokens, tile_seg=None, tile_row0=None, n_tiles=0, max_pos=None)
+    else:
+        lens = np.diff(ctx.h_seg_start)
+        dec = ctx.h_seg_start[:-1][lens == 1].astype(np.int32)
+        tile_seg, tile_row0 = [], []
+        for s in np.nonzero(lens > 1)[0]:
+            for r in range(0, int(lens[s]), QTILE):
+                tile_seg.append(s)
+                tile_row0.append(r)
+        flat = np.concatenate([dec, np.asarray(tile_seg, np.int32), np.asarray(tile_row0, np.int32)]).astype(np.int32)
+        dev = torch.from_numpy(flat).pin_memory().to(ctx.rt.device, non_blocking=True) if flat.size else None
+        nd, nt = dec.size, len(tile_seg)
+        work = dict(dec_tokens=dev[:nd] if nd else None, n_dec=nd, tile_seg=dev[nd:nd + nt] if nt else None,
+                    tile_row0=dev[nd + nt:] if nt else None, n_tiles=nt,
+                    max_pos=int(ctx.h_positions[dec].max()) if nd else None)
+    ctx.memo[key] = work
+    return work
 
 
 def paged_attention(ctx, q: torch.Tensor, cache: ops.KvLayerView, heads: int, window: Optional[int], scale: float) -> torch.Tensor:
     """q [T, heads*hd] (activation dtype) -> attention output of the same shape and dtype."""
-    out = ctx.rt.empty(tuple(q.shape), q.dtype)
-    ops.attention_generic(q, cache, ctx.positions, ctx.seg_of_token, window, scale, out, heads, ctx.rt.status)
+    rt = ctx.rt
+    out = rt.empty(tuple(q.shape), q.dtype)
+    view = cache.c_view()
+    if not has_tensor_core_kernel(q.dtype, view.head_dim, heads, view.kv_heads):
+        ops.attention_generic(q, cache, ctx.positions, ctx.seg_of_token, window, scale, out, heads, rt.status)
+        return out
+    work = _work_lists(ctx)
+    stream = ops._stream()
+    if work["n_dec"]:
+        limit = view.table_stride * view.page_size
+        max_slices = -(-limit // SLICE) if work["max_pos"] is None else work["max_pos"] // SLICE + 1
+        skey = ("decode_scratch", heads, view.head_dim, max_slices)
+        if skey not in ctx.memo:
+            n = work["n_dec"] * heads * max_slices
+            ctx.memo[skey] = (rt.empty((n * view.head_dim,), torch.float32), rt.empty((n * 2,), torch.float32))
+        part_o, part_ml = ctx.memo[skey]
+        L.call("ib_attention_decode", q.data_ptr(), C.byref(view), work["dec_tokens"].data_ptr(), work["n_dec"], ctx.positions.data_ptr(),
+               ctx.seg_of_token.data_ptr(), int(window or 0), float(scale), part_o.data_ptr(), part_ml.data_ptr(), out.data_ptr(), heads,
+               max_slices, rt.status.data_ptr(), stream)
+    if work["n_tiles"]:
+        L.call("ib_attention_prefill", q.data_ptr(), C.byref(view), work["tile_seg"].data_ptr(), work["tile_row0"].data_ptr(), work["n_tiles"],
+               ctx.seg_start.data_ptr(), ctx.seg_pos0.data_ptr(), int(window or 0), float(scale), out.data_ptr(), heads, rt.status.data_ptr(),
+               stream)
     return out

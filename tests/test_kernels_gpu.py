@@ -1,0 +1,286 @@
+"""Each CUDA kernel alone against its plain float32/float64 reference, at sizes other than the
+engine's tiny models: widths and vocabularies that are no powers of two, odd token counts, several
+head sizes and group sizes, shuffled pages, windows, and inputs built so that a fault shows."""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def status():
+    from inference_bench_b200.kernels import lib
+    lib.load()
+    return torch.zeros(1, dtype=torch.int32, device=DEV)
+
+
+def _g(seed):
+    return torch.Generator().manual_seed(seed)
+
+
+# ------------------------------------------------------------------------------------------ matrix products
+@pytest.mark.parametrize("T,N,K", [(1, 7, 5), (3, 70, 33), (65, 129, 100), (130, 64, 257)])
+def test_gemm_simt_float32(T, N, K):
+    from inference_bench_b200.kernels import ops
+    x = torch.randn(T, K, generator=_g(1)).to(DEV)
+    w = torch.randn(N, K, generator=_g(2)).to(DEV)
+    out = torch.empty(T, N, device=DEV)
+    ops.gemm_simt(x, w, out)
+    ref = (x.double() @ w.double().T)
+    assert (out.double() - ref).abs().max() <= 1e-5 * ref.abs().max()
+
+
+@pytest.mark.parametrize("T,N,K,bn,splits", [
+    (1, 128, 64, 16, 1), (5, 100, 96, 16, 1), (16, 136, 72, 16, 2), (17, 384, 1024, 32, 4), (33, 130, 520, 64, 3),
+    (100, 1000, 264, 128, 1), (300, 257, 2048, 256, 2), (513, 640, 4096, 256, 1), (8, 4096, 4096, None, None), (2048, 1536, 1024, None, None)])
+def test_gemm_tcgen05_bfloat16(status, T, N, K, bn, splits):
+    from inference_bench_b200.kernels import gemm_tcgen05 as G
+    x = (torch.randn(T, K, generator=_g(3)) * 0.5).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, K, generator=_g(4)) * 0.5).to(torch.bfloat16).to(DEV)
+    if bn is None:
+        bn, splits = G.choose(T, N, K)
+    out = torch.full((splits, T, N), float("nan"), device=DEV)
+    G.gemm(x, w, out, bn, splits, status)
+    ref = x.double() @ w.double().T
+    got = out.double().sum(0)
+    assert status.item() == 0
+    assert (got - ref).abs().max() <= 2e-5 * ref.abs().max() + 1e-6
+    # and it agrees with the plain-loop kernel on the same bfloat16 inputs
+    from inference_bench_b200.kernels import ops
+    simt = torch.empty(T, N, device=DEV)
+    ops.gemm_simt(x, w, simt)
+    assert (got - simt.double()).abs().max() <= 2e-5 * ref.abs().max() + 1e-6
+
+
+def test_gemm_tcgen05_refuses_bad_sizes(status):
+    from inference_bench_b200.kernels import gemm_tcgen05 as G, lib
+    x = torch.zeros(4, 100, dtype=torch.bfloat16, device=DEV)   # K = 100 is no multiple of 8
+    w = torch.zeros(8, 100, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(lib.KernelError, match="multiple of 8"):
+        G.gemm(x, w, torch.empty(1, 4, 8, device=DEV), 16, 1, status)
+    assert not G.supports(100)
+
+
+# ------------------------------------------------------------------------------------------ row-wise kernels
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,H,P_", [(1, 10, 0), (7, 100, 1), (33, 1000, 3), (4, 5120, 2)])
+def test_add_rmsnorm(dtype, T, H, P_):
+    from inference_bench_b200.kernels import ops
+    x = torch.randn(T, H, generator=_g(5)) * 3
+    delta = torch.randn(P_, T, H, generator=_g(6)) if P_ else None
+    w = 1 + 0.1 * torch.randn(H, generator=_g(7))
+    eps = 3e-5
+    xd = x.to(DEV)
+    out = torch.empty(T, H, dtype=dtype, device=DEV)
+    ops.add_rmsnorm(xd, delta.to(DEV) if P_ else None, w.to(DEV), out, eps)
+    x_ref = x.double() + (delta.double().sum(0) if P_ else 0)
+    ref = P.rmsnorm(x_ref, w.double(), eps)
+    assert (xd.cpu().double() - x_ref).abs().max() <= 1e-5
+    tol = 1e-5 if dtype == torch.float32 else 2.0 ** -8
+    assert ((out.cpu().double() - ref).abs() <= tol * ref.abs() + 1e-6).all()
+    # gathered rows leave x alone
+    rows = torch.tensor([T - 1, 0], dtype=torch.int32, device=DEV)
+    x2 = x.to(DEV)
+    out2 = torch.empty(2, H, dtype=dtype, device=DEV)
+    ops.add_rmsnorm(x2, delta.to(DEV) if P_ else None, w.to(DEV), out2, eps, rows)
+    assert torch.equal(x2.cpu(), x)
+    assert torch.equal(out2.cpu(), out.cpu()[[T - 1, 0]])
+
+
+def test_embed_and_bad_token(status):
+    from inference_bench_b200.kernels import ops
+    table = torch.randn(301, 70, generator=_g(8)).to(torch.bfloat16)
+    toks = torch.tensor([0, 300, 17, 17], dtype=torch.int32)
+    x = torch.empty(4, 70, device=DEV)
+    ops.embed(table.to(DEV), toks.to(DEV), x, status)
+    assert torch.equal(x.cpu(), P.embedding(table.float(), toks.tolist()))
+    assert status.item() == 0
+    ops.embed(table.to(DEV), torch.tensor([301], dtype=torch.int32, device=DEV), torch.empty(1, 70, device=DEV), status)
+    assert status.item() == 2   # a token outside the vocabulary is reported, never read
+    status.zero_()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_silu_mul(dtype):
+    from inference_bench_b200.kernels import ops
+    gu = torch.randn(2, 5, 2 * 37, generator=_g(9)) * 4
+    act = torch.empty(5, 37, dtype=dtype, device=DEV)
+    ops.silu_mul(gu.to(DEV), act)
+    s = gu.double().sum(0)
+    g, u = s[:, :37], s[:, 37:]
+    ref = g / (1 + torch.exp(-g)) * u
+    tol = 1e-5 if dtype == torch.float32 else 2.0 ** -8
+    assert ((act.cpu().double() - ref).abs() <= tol * ref.abs() + 1e-6).all()
+
+
+def test_rope_table():
+    from inference_bench_b200.kernels import ops
+    pos = torch.tensor([0, 1, 77, 4095, 40000], dtype=torch.int32)
+    inv = (1.0 / torch.pow(torch.tensor(1e6, dtype=torch.float64), torch.arange(0, 48, 2, dtype=torch.float64) / 48)).float()
+    cos = torch.empty(5, 24, device=DEV)
+    sin = torch.empty(5, 24, device=DEV)
+    ops.rope_table(pos.to(DEV), inv.to(DEV), cos, sin)
+    ang = pos.float()[:, None] * inv[None, :]     # float32 angles, as the reference computes them
+    assert (cos.cpu() - torch.cos(ang.double()).float()).abs().max() <= 2e-6
+    assert (sin.cpu() - torch.sin(ang.double()).float()).abs().max() <= 2e-6
+
+
+# ------------------------------------------------------------------------------------------ paged attention
+def _paged(contexts, page_size, dtype, seed, entries=2, entry=1):
+    """Scatter dense K, V ([L, kv_heads, hd] per request) into a pool with shuffled pages."""
+    from inference_bench_b200.kernels.ops import KvLayerView
+    kvh, hd = contexts[0][0].shape[1:]
+    need = [-(-k.shape[0] // page_size) for k, _ in contexts]
+    total = sum(need) + 5
+    order = np.random.default_rng(seed).permutation(total)
+    width = max(need) + 2
+    table = np.full((len(contexts), width), -1, dtype=np.int32)
+    pool = torch.zeros(total, entries, 2, kvh, page_size, hd, dtype=dtype)
+    at = 0
+    for s, (k, v) in enumerate(contexts):
+        for p in range(need[s]):
+            page = int(order[at]); at += 1
+            table[s, p] = page
+            rows = slice(p * page_size, min((p + 1) * page_size, k.shape[0]))
+            n = rows.stop - rows.start
+            pool[page, entry, 0, :, :n] = k[rows].transpose(0, 1).to(dtype)
+            pool[page, entry, 1, :, :n] = v[rows].transpose(0, 1).to(dtype)
+    return KvLayerView(pool.to(DEV), entry, torch.from_numpy(table).to(DEV)), table
+
+
+def _attention_case(dtype, heads, kvh, hd, page_size, window, shapes, seed, needle=False):
+    """shapes: (context length L, query tokens n) per segment; queries sit at the last n positions."""
+    g = _g(seed)
+    contexts, qs, refs, positions, seg_of = [], [], [], [], []
+    for s, (L, n) in enumerate(shapes):
+        k = torch.randn(L, kvh, hd, generator=g).to(dtype).float()
+        v = torch.randn(L, kvh, hd, generator=g).to(dtype).float()
+        q = torch.randn(n, heads, hd, generator=g).to(dtype).float()
+        if needle and L > 40:   # one far key that must dominate head 0 of the last query
+            k[3, 0] = 6.0 * q[-1, 0] / q[-1, 0].norm() * math.sqrt(hd) / math.sqrt(hd) * 1.0
+            k[3, 0] = k[3, 0].to(dtype).float()
+            v[3, 0] = 5.0
+        q_full = torch.zeros(L, heads, hd)
+        q_full[L - n:] = q
+        ref = P.attention_scores(q_full.double(), k.double(), v.double(), window)[L - n:]
+        contexts.append((k, v)); qs.append(q.reshape(n, heads * hd)); refs.append(ref)
+        positions += list(range(L - n, L)); seg_of += [s] * n
+    view, _ = _paged(contexts, page_size, dtype, seed)
+    return (torch.cat(qs).to(dtype).to(DEV), view, torch.tensor(positions, dtype=torch.int32, device=DEV),
+            torch.tensor(seg_of, dtype=torch.int32, device=DEV), torch.cat(refs), shapes)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window", [None, 10])
+def test_attention_generic(status, dtype, window):
+    from inference_bench_b200.kernels import ops
+    heads, kvh, hd = 6, 3, 24
+    q, view, pos, seg, ref, _ = _attention_case(dtype, heads, kvh, hd, 8, window, [(50, 50), (37, 1), (20, 3), (200, 2)], 11, needle=True)
+    out = torch.empty_like(q)
+    ops.attention_generic(q, view, pos, seg, window, 1 / math.sqrt(hd), out, heads, status)
+    assert status.item() == 0
+    tol = 1e-5 if dtype == torch.float32 else 1.5e-2
+    assert (out.cpu().double() - ref).abs().max() <= tol * ref.abs().max()
+
+
+@pytest.mark.parametrize("hd,heads,kvh,page", [(128, 8, 2, 16), (64, 5, 1, 32), (128, 16, 1, 16), (64, 4, 4, 8)])
+@pytest.mark.parametrize("window", [None, 100])
+def test_attention_tensor_core_kernels(status, hd, heads, kvh, page, window):
+    """Decode slices and prefill tiles through the engine's dispatch, against the plain reference."""
+    from inference_bench_b200.engine.context import Segment, build_context
+    from inference_bench_b200.engine.runtime import Runtime
+    from inference_bench_b200.kernels import attention
+    shapes = [(300, 300), (500, 70), (1000, 1), (129, 1), (128, 1), (5, 2), (260, 1), (64, 64), (65, 65)]
+    q, view, pos, seg, ref, _ = _attention_case(torch.bfloat16, heads, kvh, hd, page, window, shapes, 12, needle=True)
+    rt = Runtime(DEV, "bfloat16")
+    segs = [Segment(i, i, L - n, [0] * n) for i, (L, n) in enumerate(shapes)]
+    ctx = build_context(rt, segs)
+    assert torch.equal(ctx.positions, pos) and torch.equal(ctx.seg_of_token, seg)
+    assert attention.has_tensor_core_kernel(q.dtype, hd, heads, kvh)
+    out = attention.paged_attention(ctx, q, view, heads, window, 1 / math.sqrt(hd))
+    rt.check_status()
+    err = (out.cpu().double() - ref).abs()
+    assert err.max() <= 1.5e-2 * ref.abs().max(), f"row {int(err.max(dim=1).values.argmax())} is off by {err.max():.3e}"
+    # the generic kernel gives the same up to rounding
+    from inference_bench_b200.kernels import ops
+    out2 = torch.empty_like(q)
+    ops.attention_generic(q, view, pos, seg, window, 1 / math.sqrt(hd), out2, heads, status)
+    assert (out2.float() - out.float()).abs().max() <= 2e-2 * ref.abs().max()
+
+
+def test_attention_reports_missing_page(status):
+    from inference_bench_b200.kernels import ops
+    q, view, pos, seg, ref, _ = _attention_case(torch.float32, 2, 1, 16, 8, None, [(30, 1)], 13)
+    view.block_table[0, 1] = -1
+    out = torch.empty_like(q)
+    ops.attention_generic(q, view, pos, seg, None, 0.25, out, 2, status)
+    assert status.item() == 1
+    status.zero_()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("hd,rot", [(24, 24), (64, 32), (16, 0)])
+def test_qk_norm_rope_kv(status, dtype, hd, rot):
+    from inference_bench_b200.kernels import ops
+    heads, kvh, page, T = 4, 2, 8, 21
+    R = (heads + 2 * kvh) * hd
+    qkv = torch.randn(2, T, R, generator=_g(14))
+    qw = 1 + 0.1 * torch.randn(hd, generator=_g(15))
+    kw = 1 + 0.1 * torch.randn(hd, generator=_g(16))
+    eps, theta, pos0 = 1e-5, 1e4, 13
+    positions = torch.arange(pos0, pos0 + T, dtype=torch.int32)
+    view, table = _paged([(torch.zeros(pos0 + T, kvh, hd), torch.zeros(pos0 + T, kvh, hd))], page, dtype, 17)
+    cos = sin = None
+    if rot:
+        inv = (1.0 / torch.pow(torch.tensor(theta, dtype=torch.float64), torch.arange(0, rot, 2, dtype=torch.float64) / rot)).float().to(DEV)
+        cos = torch.empty(T, rot // 2, device=DEV)
+        sin = torch.empty(T, rot // 2, device=DEV)
+        ops.rope_table(positions.to(DEV), inv, cos, sin)
+    q_out = torch.empty(T, heads * hd, dtype=dtype, device=DEV)
+    ops.qk_norm_rope_kv(qkv.to(DEV), qw.to(DEV), kw.to(DEV), eps, cos, sin, positions.to(DEV), torch.zeros(T, dtype=torch.int32, device=DEV), q_out,
+                        view, heads, status)
+    assert status.item() == 0
+    s = qkv.double().sum(0)
+    q = P.rmsnorm(s[:, :heads * hd].reshape(T, heads, hd), qw.double(), eps)
+    k = P.rmsnorm(s[:, heads * hd:(heads + kvh) * hd].reshape(T, kvh, hd), kw.double(), eps)
+    v = s[:, (heads + kvh) * hd:].reshape(T, kvh, hd)
+    if rot:
+        q = torch.cat([P.rope_neox(q[..., :rot], positions, theta), q[..., rot:]], -1)
+        k = torch.cat([P.rope_neox(k[..., :rot], positions, theta), k[..., rot:]], -1)
+    tol = 2e-5 if dtype == torch.float32 else 2.0 ** -7
+    assert (q_out.cpu().double().reshape(T, heads, hd) - q).abs().max() <= tol * q.abs().max()
+    pool = view.pool.cpu().double()
+    for t in range(T):
+        p = pos0 + t
+        pg = table[0, p // page]
+        assert (pool[pg, 1, 0, :, p % page] - k[t]).abs().max() <= tol * k.abs().max()
+        assert (pool[pg, 1, 1, :, p % page] - v[t]).abs().max() <= tol * v.abs().max()
+    assert pool[:, 0].abs().max() == 0   # the other layer's place in the pages is untouched
+
+
+# ------------------------------------------------------------------------------------------ sampling
+def test_sample_rows_matches_plain():
+    from inference_bench_b200.kernels import ops
+    from inference_bench_b200.sampling.params import SamplingParams
+    V = 1003
+    logits = torch.randn(8, V, generator=_g(18)) * 3
+    logits[0, 17] = logits[0, 900] = logits[0].max() + 1     # a tie: the lowest index wins
+    params = [SamplingParams(), SamplingParams(temperature=0.7, seed=1), SamplingParams(temperature=1.5, seed=2, top_k=5),
+              SamplingParams(temperature=1.0, seed=3, top_p=0.6), SamplingParams(temperature=1.0, seed=4, min_p=0.1),
+              SamplingParams(temperature=2.0, seed=5, top_k=50, top_p=0.9, min_p=0.01), SamplingParams(temperature=0.3, seed=2**31 + 5),
+              SamplingParams(temperature=1.0, seed=7, top_k=1)]
+    steps = [0, 3, 1, 9, 2, 100, 5, 0]
+    rows = torch.tensor([p.row(s) for p, s in zip(params, steps)], dtype=torch.int32, device=DEV)
+    toks = torch.empty(8, dtype=torch.int32, device=DEV)
+    ops.sample_rows(logits.to(DEV), rows, toks)
+    want = [P.sample_token(logits[i], p.temperature, p.seed, steps[i], p.top_k, p.top_p, p.min_p) for i, p in enumerate(params)]
+    assert toks.cpu().tolist() == want
+    assert want[0] == 17 and want[7] == int(logits[7].argmax())

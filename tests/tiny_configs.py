@@ -23,6 +23,17 @@ CONFIGS = {
         num_hidden_layers=4, num_attention_heads=5, num_key_value_heads=1, head_dim=32, rms_norm_eps=3e-6, rope_theta=500000.0,
         tie_word_embeddings=False, max_position_embeddings=512, hidden_act="silu", attention_bias=False, torch_dtype="bfloat16",
         sliding_window=24, layer_types=["sliding_attention", "full_attention", "sliding_attention", "full_attention"])),
+    # head 64 with a window on layer 1: the tensor-core attention kernels in bfloat16
+    "D": dict(seed=3, page_size=16, std=0.05, config=dict(
+        architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=500, hidden_size=128, intermediate_size=200,
+        num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=64, rms_norm_eps=1e-6, rope_theta=10000.0,
+        tie_word_embeddings=False, max_position_embeddings=512, hidden_act="silu", attention_bias=False, torch_dtype="bfloat16",
+        sliding_window=40, layer_types=["full_attention", "sliding_attention"])),
+    # head 128, group 4 on one kv head, larger pages
+    "E": dict(seed=4, page_size=32, std=0.05, config=dict(
+        architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=320, hidden_size=72, intermediate_size=136,
+        num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=1, head_dim=128, rms_norm_eps=1e-6, rope_theta=1000000.0,
+        tie_word_embeddings=True, max_position_embeddings=512, hidden_act="silu", attention_bias=False, torch_dtype="bfloat16")),
 }
 
 
