@@ -209,6 +209,11 @@ def run_ours(args) -> dict:
     engine = Engine(cfg, dtype="bfloat16", max_ctx=CONTEXT, page_size=PAGE, num_pages=big * (CONTEXT // PAGE) + 64, max_num_seqs=big,
                     max_batched_tokens=8192, prefill_chunk=PROMPT, random_weights_seed=0)
     steps, warmup = args.steps, max(args.warmup, 3)
+    if args.only == "prefill":   # one part alone, for profiling: a short report, not the benchmark line
+        return {"only": "prefill", "layers": layers, "ms": measure_prefill(engine, args.steps, 1)}
+    if args.only == "decode":
+        ms, launches = measure_decode_device(engine, args.batch, steps, warmup)
+        return {"only": "decode", "layers": layers, "batch": args.batch, "ms_per_step": ms, "launches_per_step": launches}
 
     prefill_ms = measure_prefill(engine, 5, 3)
     b1_ms, _ = measure_decode_device(engine, 1, steps, warmup)
@@ -250,6 +255,7 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (both numbers are reported)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--only", default="", choices=["", "prefill", "decode"], help="run one part alone (for profiling); prints a short report")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "the reference is a Rust workspace (no setup.py/pyproject.toml): pip cannot install it and no Rust toolchain is present"}))
