@@ -1,0 +1,241 @@
+"""The scheduler's decisions on the CPU, with a fake executor in place of the device.
+
+The fake keeps a paged "memory" of its own: every token of a step is written to the page and slot
+the request's block table names, and before a request's next token is computed its whole history is
+read back through the table and compared with what the request really holds. A page handed to two
+requests, a stale table, or a portion that starts at the wrong position fails that check. The next
+token is a hash of the history, so outputs are comparable with a request run alone
+(the reference tests its scheduler the same way: crates/specrt/src/sched.rs:1591-1760)."""
+import numpy as np
+import pytest
+
+from inference_bench_b200.cache.manager import CacheManager
+from inference_bench_b200.engine.scheduler import Refused, Request, Scheduler, SchedulerConfig
+from inference_bench_b200.parts.base import PagedKV
+from inference_bench_b200.sampling.params import SamplingParams
+
+VOCAB = 1000
+
+
+def next_token(history) -> int:
+    h = 1469598103
+    for t in history:
+        h = (h * 1099511 + int(t) + 7) % 2147483647
+    return h % VOCAB
+
+
+def alone(prompt, n, stop=()):
+    seq = list(prompt)
+    out = []
+    for _ in range(n):
+        t = next_token(seq)
+        if t in stop:
+            break
+        seq.append(t)
+        out.append(t)
+    return out
+
+
+class FakeExecutor:
+    def __init__(self, cache: CacheManager, truth: dict):
+        self.cache, self.truth = cache, truth
+        self.memory = np.full((cache.groups[0].pool.num_pages, cache.page_size), -1, dtype=np.int64)
+        self.steps = []
+
+    def execute(self, entries, sampling):
+        out = []
+        self.steps.append([(e.request, len(e.tokens)) for e in entries])
+        for e in entries:
+            self.cache.extend(e.request, self.cache.length(e.request) + len(e.tokens))
+        for e in entries:
+            start = self.cache.length(e.request)
+            table = self.cache.table(0, e.request)
+            for i, tok in enumerate(e.tokens):
+                p = start + i
+                assert table[p // self.cache.page_size] >= 0
+                self.memory[table[p // self.cache.page_size], p % self.cache.page_size] = tok
+            n = start + len(e.tokens)
+            seen = [self.memory[table[p // self.cache.page_size], p % self.cache.page_size] for p in range(n)]
+            assert seen == list(self.truth[e.request].tokens[:n]), f"request {e.request}: the cache does not hold its history"
+            self.cache.commit(e.request, n)
+            if e.want:
+                out.append(next_token(seen))
+        assert len(out) == len(sampling)
+        return out
+
+
+def make(pages=64, page=4, slots=8, **cfg):
+    cache = CacheManager([PagedKV(1, 8, None)], page, pages, slots, cfg.get("max_ctx", 256))
+    sched = Scheduler(cache, SchedulerConfig(**{"max_num_seqs": slots, "max_batched_tokens": 64, "prefill_chunk": 16, "max_ctx": 256, **cfg}))
+    truth = {}
+    ex = FakeExecutor(cache, truth)
+
+    def submit(rid, prompt, n, **kw):
+        sched.submit(Request(rid, prompt, n, **kw))
+        truth[rid] = next(s for s in sched.waiting if s.req.id == rid)
+    return cache, sched, ex, submit
+
+
+def run(sched, ex, limit=10000):
+    done, reports = {}, []
+    for _ in range(limit):
+        if sched.idle():
+            break
+        rep = sched.step(ex)
+        reports.append(rep)
+        for f in rep.finished:
+            done[f.id] = f
+        sched.cache.check()
+    assert sched.idle()
+    return done, reports
+
+
+def prompt(seed, n):
+    return np.random.default_rng(seed).integers(0, VOCAB, n).tolist()
+
+
+def test_outputs_equal_requests_run_alone_and_everything_is_freed():
+    cache, sched, ex, submit = make()
+    reqs = {i: (prompt(i, n), k) for i, (n, k) in enumerate([(5, 9), (40, 3), (17, 20), (1, 12), (33, 1)])}
+    for i, (p, k) in reqs.items():
+        submit(i, p, k)
+    done, _ = run(sched, ex)
+    for i, (p, k) in reqs.items():
+        assert done[i].tokens == alone(p, k) and done[i].finish == "length"
+        assert done[i].prompt_tokens == len(p) and done[i].completion_tokens == k
+    assert cache.used_pages() == [0] and cache.free_slots() == 8
+
+
+def test_budget_chunks_and_decoders_never_skipped():
+    cache, sched, ex, submit = make(max_batched_tokens=24, prefill_chunk=10)
+    submit("short", prompt(1, 3), 30)
+    done = {}
+    rep = sched.step(ex)                       # prefill of the short prompt samples its first token
+    assert rep.prefill_tokens == 3 and len(rep.emitted) == 1
+    submit("long", prompt(2, 95), 2)
+    while not sched.idle():
+        rep = sched.step(ex)
+        step = dict(ex.steps[-1])
+        assert sum(step.values()) <= 24                                    # the token budget holds, decode rows included
+        if "short" in step or any(s.req.id == "short" for s in sched.running):
+            assert step.get("short", 1) == 1                               # the decoder gets its row every step
+        if "long" in step and step["long"] > 1:
+            assert step["long"] <= 10                                      # no portion beyond prefill_chunk
+        for f in rep.finished:
+            done[f.id] = f
+    assert done["short"].tokens == alone(prompt(1, 3), 30) and done["long"].tokens == alone(prompt(2, 95), 2)
+    long_portions = [dict(s)["long"] for s in ex.steps if "long" in dict(s) and dict(s)["long"] > 1]
+    assert sum(long_portions) == 95 and len(long_portions) == 10
+
+
+def test_shortest_remaining_prompt_goes_first_and_admission_is_fifo():
+    cache, sched, ex, submit = make(max_batched_tokens=40, prefill_chunk=20, slots=2)
+    submit("a", prompt(1, 30), 1)
+    submit("b", prompt(2, 6), 1)
+    submit("c", prompt(3, 2), 1)               # has to wait for a slot although it is the shortest
+    sched.step(ex)
+    first = dict(ex.steps[0])
+    assert first == {"b": 6, "a": 20}          # both admitted in order; the shorter prompt is served first, a gets one full portion
+    assert [s.req.id for s in sched.waiting] == ["c"]
+    done, _ = run(sched, ex)
+    assert set(done) | {"b"} == {"a", "b", "c"}
+
+
+def test_preemption_recomputes_and_outputs_do_not_change():
+    cache, sched, ex, submit = make(pages=10, page=4, slots=4, max_batched_tokens=32, prefill_chunk=8)
+    reqs = {i: (prompt(10 + i, n), k) for i, (n, k) in enumerate([(6, 20), (9, 14), (3, 25), (12, 8), (5, 18), (7, 11)])}
+    for i, (p, k) in reqs.items():
+        submit(i, p, k)
+    done, reports = run(sched, ex)
+    assert sum(r.preemptions for r in reports) > 0 and sched.total_preemptions > 0
+    for i, (p, k) in reqs.items():
+        assert done[i].tokens == alone(p, k), f"request {i}"
+    emitted = {}
+    for r in reports:
+        for rid, tok in r.emitted:
+            emitted.setdefault(rid, []).append(tok)
+    assert all(emitted[i] == done[i].tokens for i in reqs)        # a preempted request never emits a token twice
+    assert cache.used_pages() == [0]
+
+
+def test_preempted_request_is_the_newest_and_returns_to_the_front():
+    cache, sched, ex, submit = make(pages=6, page=4, slots=3, max_batched_tokens=64, prefill_chunk=64)
+    submit("old", prompt(1, 7), 16)
+    submit("new", prompt(2, 7), 16)
+    submit("later", prompt(3, 2), 2)
+    preempted = None
+    for _ in range(40):
+        rep = sched.step(ex)
+        if rep.preemptions:
+            preempted = [s.req.id for s in sched.waiting]
+            break
+    assert preempted is not None and preempted[0] == "new" and "old" in [s.req.id for s in sched.running]
+
+
+def test_stop_token_cancel_and_context_limit():
+    cache, sched, ex, submit = make(max_ctx=40)
+    p = prompt(5, 8)
+    full = alone(p, 12)
+    stop = full[5]
+    submit("s", p, 12, stop_ids=(stop,))
+    submit("c", prompt(6, 9), 50 - 19)
+    submit("l", prompt(7, 30), 10)             # 30 + 10 = the context limit exactly
+    done = {}
+    for i in range(200):
+        if sched.idle():
+            break
+        if i == 3:
+            f = sched.cancel("c")
+            assert f.finish == "cancelled" and cache.has("c") is False
+        for f in sched.step(ex).finished:
+            done[f.id] = f
+    assert done["s"].finish == "stop" and done["s"].tokens == full[:full.index(stop)]
+    assert done["l"].finish == "length" and len(done["l"].tokens) == 10
+    assert sched.cancel("nobody") is None and cache.used_pages() == [0]
+
+
+def test_refusals():
+    cache, sched, ex, submit = make(pages=8, page=4, max_ctx=64)
+    with pytest.raises(Refused, match="empty"):
+        sched.submit(Request(1, [], 4))
+    with pytest.raises(Refused, match="max_tokens"):
+        sched.submit(Request(2, [1], 0))
+    with pytest.raises(Refused, match="context limit"):
+        sched.submit(Request(3, [1] * 60, 5))
+    with pytest.raises(Refused, match="pages"):
+        sched.submit(Request(4, [1] * 30, 10))    # 40 tokens need 10 pages, the pool has 8
+    sched.submit(Request(5, [1, 2], 2))
+    with pytest.raises(Refused, match="already"):
+        sched.submit(Request(5, [1, 2], 2))
+
+
+def test_sampling_rows_carry_the_request_step():
+    cache, sched, _, submit = make()
+    seen = []
+
+    class Ex(FakeExecutor):
+        def execute(self, entries, sampling):
+            seen.extend((p.seed, step) for p, step in sampling)
+            return super().execute(entries, sampling)
+    truth = {}
+    ex = Ex(cache, truth)
+    sched.submit(Request("a", prompt(1, 4), 3, SamplingParams(temperature=0.5, seed=11)))
+    truth["a"] = sched.waiting[0]
+    run(sched, ex)
+    assert seen == [(11, 0), (11, 1), (11, 2)]
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_random_load_under_page_pressure(seed):
+    """Many requests, few slots and pages (cf. crates/specrt/tests/serving.rs:240-281)."""
+    rng = np.random.default_rng(seed)
+    cache, sched, ex, submit = make(pages=30, page=4, slots=5, max_batched_tokens=48, prefill_chunk=16, max_ctx=100)
+    reqs = {}
+    for i in range(24):
+        n, k = int(rng.integers(1, 60)), int(rng.integers(1, 40))
+        reqs[i] = (prompt(100 * seed + i, n), k)
+        submit(i, *reqs[i])
+    done, _ = run(sched, ex)
+    for i, (p, k) in reqs.items():
+        assert done[i].tokens == alone(p, k), f"request {i}"
+    assert cache.used_pages() == [0] and cache.free_slots() == 5
