@@ -1,0 +1,262 @@
+"""Each part of the decoder alone against the plain implementation, and the extension points:
+a toy mixer with state of its own, a layer that runs twice, and a layer that reads another
+layer's cache, registered and stepped from this file without touching the framework."""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as P
+import traces
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _rt(dtype):
+    from inference_bench_b200.engine.runtime import Runtime
+    return Runtime(DEV, dtype)
+
+
+def _ctx(rt, segments, caches=None):
+    from inference_bench_b200.engine.context import Segment, build_context
+    return build_context(rt, [Segment(i, i, pos0, toks) for i, (pos0, toks) in enumerate(segments)], caches)
+
+
+def _weights(part, seed, std=0.1):
+    from inference_bench_b200.weights.random_init import random_weights
+    return random_weights(part.weight_specs(), seed, std=std)
+
+
+TOL = {"float32": 2e-5, "bfloat16": 2e-2}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_norm_embedding_and_head_alone(dtype):
+    from inference_bench_b200.parts.standard import LinearHead, RMSNorm, TokenEmbedding
+    rt = _rt(dtype)
+    emb, norm, head = TokenEmbedding("e.weight", 301, 72), RMSNorm("n.weight", 72, 2e-5), LinearHead("h.weight", 301, 72)
+    w = {**_weights(emb, 1, 1.0), **_weights(norm, 2), **_weights(head, 3)}
+    for p in (emb, norm, head):
+        p.bind({k: v.to(DEV) for k, v in w.items()}, rt)
+    toks = [5, 300, 0, 17, 17, 211]
+    ctx = _ctx(rt, [(0, toks[:4]), (9, toks[4:])])
+    x = emb.forward(ctx)
+    wf = {k: v.float() for k, v in w.items()}
+    x_ref = P.embedding(wf["e.weight"], toks)
+    assert torch.equal(x.cpu(), x_ref)
+    delta = torch.randn(2, 6, 72, generator=torch.Generator().manual_seed(4))
+    h = norm.forward(ctx, x, delta.to(DEV))
+    x_ref = x_ref + delta.sum(0)
+    h_ref = P.rmsnorm(x_ref, wf["n.weight"], 2e-5)
+    assert (x.cpu() - x_ref).abs().max() < 1e-5
+    assert (h.float().cpu() - h_ref).abs().max() <= TOL[dtype] * h_ref.abs().max()
+    logits = head.forward(ctx, h)
+    ref = h.float().cpu() @ wf["h.weight"].T
+    assert logits.dtype == torch.float32 and (logits.cpu() - ref).abs().max() <= 1e-4 * ref.abs().max()
+    # tied head reads the embedding table
+    tied = LinearHead("unused", 301, 72, tied_to="e.weight")
+    assert tied.weight_specs() == []
+    tied.bind({k: v.to(DEV) for k, v in w.items()}, rt)
+    ref = h.float().cpu() @ wf["e.weight"].T
+    assert (tied.forward(ctx, h).cpu() - ref).abs().max() <= 1e-4 * ref.abs().max()
+
+
+def test_position_encodings_alone():
+    from inference_bench_b200.parts.standard import NoPositionEncoding, RotaryEmbedding
+    rt = _rt("float32")
+    rope = RotaryEmbedding(24, 5e5)
+    rope.bind({}, rt)
+    ctx = _ctx(rt, [(100, [1, 2, 3]), (0, [4])])
+    cos, sin = rope.tables(ctx)
+    assert rope.tables(ctx)[0] is cos                                   # one table per step, shared by the layers
+    pos = torch.tensor([100, 101, 102, 0], dtype=torch.float64)
+    inv = 1.0 / torch.pow(torch.tensor(5e5, dtype=torch.float64), torch.arange(0, 24, 2, dtype=torch.float64) / 24)
+    assert (cos.cpu().double() - torch.cos(pos[:, None] * inv)).abs().max() < 1e-5
+    assert (sin.cpu().double() - torch.sin(pos[:, None] * inv)).abs().max() < 1e-5
+    assert NoPositionEncoding().tables(ctx) == (None, None)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_swiglu_alone(dtype):
+    from inference_bench_b200.parts.standard import SwiGLU
+    rt = _rt(dtype)
+    ff = SwiGLU("m", 72, 104)
+    w = _weights(ff, 5, 0.2)
+    ff.bind({k: v.to(DEV) for k, v in w.items()}, rt)
+    ctx = _ctx(rt, [(0, [0] * 5)])
+    h = torch.randn(5, 72, generator=torch.Generator().manual_seed(6)).to(rt.act_dtype)
+    out = ff.forward(ctx, h.to(DEV)).sum(0)
+    ref = P.swiglu(h.float(), {k.replace("m.", "m."): v.float() for k, v in w.items()}, "m.")
+    assert (out.cpu() - ref).abs().max() <= TOL[dtype] * ref.abs().max()
+
+
+@pytest.mark.parametrize("dtype,hd,window", [("float32", 24, None), ("float32", 16, 7), ("bfloat16", 24, 7), ("bfloat16", 64, None), ("bfloat16", 128, 20)])
+def test_attention_alone_in_portions(dtype, hd, window):
+    """The attention part on a prompt cut in three portions, against the plain block on the whole prompt."""
+    from inference_bench_b200.cache.manager import CacheManager
+    from inference_bench_b200.parts.standard import Attention, RotaryEmbedding
+    rt = _rt(dtype)
+    hidden, heads, kvh, n = 80, 6, 2, 45
+    att = Attention("a", hidden, heads, kvh, hd, True, 1e-5, RotaryEmbedding(hd, 1e4), window)
+    w = _weights(att, 7, 0.15)
+    att.bind({k: v.to(DEV) for k, v in w.items()}, rt)
+    cache = CacheManager([att.cache_need()], 8, 8, 2, 64, device=rt.device, dtype=rt.act_dtype)
+    cache.admit("r")
+    h = torch.randn(n, hidden, generator=torch.Generator().manual_seed(8)).to(rt.act_dtype)
+    outs = []
+    for a, b in ((0, 20), (20, 43), (43, 45)):
+        cache.extend("r", b)
+        table = torch.from_numpy(cache.step_tables(["r"])[0]).to(DEV)
+        ctx = _ctx(rt, [(a, [0] * (b - a))], cache.views([table]))
+        outs.append(att.forward(ctx, h[a:b].to(DEV), ctx.caches[0]).sum(0).cpu())
+        cache.commit("r", b)
+    rt.check_status()
+    cfg = {"heads": heads, "kv_heads": kvh, "head_dim": hd, "eps": 1e-5, "theta": 1e4}
+    ref = P.attention_block(h.float(), {k.replace("a.", "a."): v.float() for k, v in w.items()}, "a.", cfg, window)
+    assert (torch.cat(outs) - ref).abs().max() <= TOL[dtype] * ref.abs().max()
+
+
+# ------------------------------------------------------------------------------------------ extension points
+# A toy architecture made only for this test: a mixer with fixed-size state of its own (a running
+# mean of everything the request has seen), a layer that runs twice with a cache for each run, and
+# a layer without keys of its own that reads the cache of the first run.
+def _register_toy():
+    from inference_bench_b200.parts import base
+    from inference_bench_b200.parts.base import FixedState, WeightSpec
+    from inference_bench_b200.parts.plan import LayerPlan, ModelPlan, PartSpec, ScheduleEntry
+    from inference_bench_b200.registry import register_architecture
+
+    if "running_mean" in base.MIXERS:
+        return
+
+    @base.register_mixer("running_mean")
+    class RunningMean(base.Mixer):
+        """out_t = W mean(h_0..h_t) over the whole request; state per request: the sum and the count."""
+
+        def __init__(self, prefix, hidden):
+            self.prefix, self.hidden = prefix, hidden
+
+        def cache_need(self):
+            return FixedState((self.hidden + 1,), torch.float32)
+
+        def weight_specs(self):
+            return [WeightSpec(f"{self.prefix}.mix.weight", (self.hidden, self.hidden))]
+
+        def bind(self, weights, rt):
+            self.w = weights[f"{self.prefix}.mix.weight"].to(rt.device).float()
+
+        def forward(self, ctx, h, cache):
+            H = self.hidden
+            out = torch.empty(ctx.n_tokens, H, dtype=torch.float32, device=h.device)
+            for i, seg in enumerate(ctx.segments):
+                a, b = int(ctx.h_seg_start[i]), int(ctx.h_seg_start[i + 1])
+                state = cache.tensor[seg.slot]
+                sums = state[:H] + torch.cumsum(h[a:b].float(), dim=0)
+                counts = state[H] + torch.arange(1, b - a + 1, device=h.device, dtype=torch.float32)
+                out[a:b] = (sums / counts[:, None]) @ self.w.T
+                state[:H] = sums[-1]
+                state[H] = counts[-1]
+            return out.unsqueeze(0)
+
+    @dataclass(frozen=True)
+    class ToyConfig:
+        vocab_size: int
+        hidden_size: int
+        heads: int
+        kv_heads: int
+        head_dim: int
+        intermediate_size: int
+        eps: float
+
+        def to_dict(self):
+            return {"architectures": ["ToyForCausalLM"], **self.__dict__}
+
+    def from_dict(raw):
+        return ToyConfig(**{k: raw[k] for k in ToyConfig.__dataclass_fields__})
+
+    def plan(c: ToyConfig) -> ModelPlan:
+        rope = PartSpec("rope", {"rotary_dim": c.head_dim, "theta": 10000.0})
+
+        def norm(name):
+            return PartSpec("rmsnorm", {"name": name, "size": c.hidden_size, "eps": c.eps})
+
+        def attn(p, own_kv):
+            return PartSpec("attention", {"prefix": f"{p}.self_attn", "hidden": c.hidden_size, "heads": c.heads, "kv_heads": c.kv_heads,
+                                          "head_dim": c.head_dim, "qk_norm": True, "norm_eps": c.eps, "position": rope, "own_kv": own_kv})
+
+        def layer(i, mixer):
+            p = f"model.layers.{i}"
+            return LayerPlan(p, "prenorm", mixer, PartSpec("swiglu", {"prefix": f"{p}.mlp", "hidden": c.hidden_size, "intermediate": c.intermediate_size}),
+                             norm(f"{p}.input_layernorm.weight"), norm(f"{p}.post_attention_layernorm.weight"))
+
+        layers = (layer(0, attn("model.layers.0", True)),
+                  layer(1, PartSpec("running_mean", {"prefix": "model.layers.1.mixer", "hidden": c.hidden_size})),
+                  layer(2, attn("model.layers.2", False)))
+        return ModelPlan("ToyForCausalLM", c.vocab_size, c.hidden_size, 512,
+                         PartSpec("table", {"name": "model.embed_tokens.weight", "vocab": c.vocab_size, "hidden": c.hidden_size}), layers,
+                         (ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(0), ScheduleEntry(2, cache_of=0)),
+                         norm("model.norm.weight"),
+                         PartSpec("linear", {"name": "lm_head.weight", "vocab": c.vocab_size, "hidden": c.hidden_size}))
+
+    register_architecture(["ToyForCausalLM"], from_dict, plan)
+
+
+TOY = dict(architectures=["ToyForCausalLM"], vocab_size=130, hidden_size=48, heads=4, kv_heads=2, head_dim=16, intermediate_size=56, eps=1e-5)
+
+
+def _toy_plain_logits(folder, tokens):
+    """The toy model evaluated whole with the plain functions."""
+    w = {k: v.double() for k, v in P.read_safetensors(folder / "model.safetensors").items()}
+    cfg = {"heads": 4, "kv_heads": 2, "head_dim": 16, "eps": 1e-5, "theta": 1e4}
+    n = len(tokens)
+    pos = torch.arange(n)
+    x = P.embedding(w["model.embed_tokens.weight"], tokens)
+
+    def mlp(i, x):
+        return x + P.swiglu(P.rmsnorm(x, w[f"model.layers.{i}.post_attention_layernorm.weight"], 1e-5), w, f"model.layers.{i}.mlp.")
+
+    first_kv = None
+    for run in range(2):                                                    # layer 0 runs twice, the toy layer between the runs
+        h = P.rmsnorm(x, w["model.layers.0.input_layernorm.weight"], 1e-5)
+        if first_kv is None:
+            p = "model.layers.0.self_attn."
+            k = P.rope_neox(P.rmsnorm((h @ w[p + "k_proj.weight"].T).reshape(n, 2, 16), w[p + "k_norm.weight"], 1e-5), pos, 1e4)
+            first_kv = (k, (h @ w[p + "v_proj.weight"].T).reshape(n, 2, 16))
+        x = mlp(0, x + P.attention_block(h, w, "model.layers.0.self_attn.", cfg, None))
+        if run == 0:
+            h = P.rmsnorm(x, w["model.layers.1.input_layernorm.weight"], 1e-5)
+            mean = torch.cumsum(h, 0) / torch.arange(1, n + 1, dtype=h.dtype)[:, None]
+            x = mlp(1, x + mean @ w["model.layers.1.mixer.mix.weight"].T)
+    h = P.rmsnorm(x, w["model.layers.2.input_layernorm.weight"], 1e-5)      # queries of its own, keys and values of the first run
+    p = "model.layers.2.self_attn."
+    q = P.rope_neox(P.rmsnorm((h @ w[p + "q_proj.weight"].T).reshape(n, 4, 16), w[p + "q_norm.weight"], 1e-5), pos, 1e4)
+    x = mlp(2, x + P.attention_scores(q, *first_kv) @ w[p + "o_proj.weight"].T)
+    return (P.rmsnorm(x, w["model.norm.weight"], 1e-5) @ w["lm_head.weight"].T).float().numpy()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_mixer_with_state_layer_run_twice_and_shared_cache(tmp_path, dtype):
+    from inference_bench_b200.trace import build_runner
+    from inference_bench_b200.weights.random_init import write_random_model
+    _register_toy()
+    folder = write_random_model(TOY, 5, tmp_path / "toy", std=0.08)
+    runner = build_runner(folder, dtype, 512, page_size=8)
+    cache = runner.cache
+    assert len(cache.groups) == 1 and cache.groups[0].entries == [0, 2]       # two caches for the layer that runs twice
+    assert cache.sources == [0, 1, 2, 0] and list(cache.states) == [1]        # entry 3 reads entry 0's cache; entry 1 has state
+    reqs = {r: traces.prompt(300 + i, n, 130) for i, (r, n) in enumerate({"a": 23, "b": 5, "c": 41, "d": 12, "e": 30}.items())}
+    want = {r: _toy_plain_logits(folder, t) for r, t in reqs.items()}
+    tol = {"float32": 1e-4, "bfloat16": 3e-2}[dtype]
+    for cut in (traces.whole, traces.portions, traces.mixed):
+        got = traces.run_steps(runner, cut(reqs))
+        assert len(got) == sum(len(t) for t in reqs.values())
+        for (r, pos), row in got.items():
+            err = np.abs(row - want[r][pos]).max() / np.abs(want[r]).max()
+            assert err <= tol, f"{cut.__name__}: request {r} position {pos}: {err:.3e}"
+        cache.check()
+        assert cache.used_pages() == [0] and cache.free_slots() == cache.max_requests
