@@ -235,3 +235,56 @@ extern "C" int ib_attention_decode(const void* q, const IbKvView* kv, const int*
     return launch<64>(q, kv, dec_tokens, n_dec, positions, seg_of_token, window, scale, part_o, part_ml, out, heads, max_slices, status, stream);
   return ib_set_error("attention_decode: head_dim %d has no tensor-core kernel (64 and 128 have)", kv->head_dim);
 }
+
+// ---------------------------------------------------------------- the variant that allocates nothing
+#include <mutex>
+
+#include "attention_decode_noalloc.h"
+
+// Scratch of the no-allocation entry point: [part_o | part_ml] of one call. In host code this name
+// is only a handle for cudaGetSymbolAddress, never a pointer a kernel may be given.
+static __device__ __align__(256) float g_decode_noalloc_scratch[IB_DECODE_NOALLOC_MAX_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_noalloc_ptr[kMaxDevices] = {nullptr};
+std::mutex g_noalloc_mutex;
+
+// Device address of the scratch array on the current device, looked up once per device.
+int noalloc_scratch(float** ptr) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  IB_CHECK_ARG(e == cudaSuccess, "attention_decode_noalloc: cudaGetDevice failed: %s", cudaGetErrorString(e));
+  IB_CHECK_ARG(dev >= 0 && dev < kMaxDevices, "attention_decode_noalloc: device %d is beyond the %d this library tracks", dev, kMaxDevices);
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (!g_noalloc_ptr[dev]) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_decode_noalloc_scratch);
+    IB_CHECK_ARG(e == cudaSuccess && p, "attention_decode_noalloc: cudaGetSymbolAddress failed on device %d: %s", dev, cudaGetErrorString(e));
+    g_noalloc_ptr[dev] = p;
+  }
+  *ptr = g_noalloc_ptr[dev];
+  return 0;
+}
+}  // namespace
+
+extern "C" int ib_attention_decode_noalloc(const void* q, const IbKvView* kv, const int* dec_tokens, int n_dec, const int* positions,
+                                           const int* seg_of_token, int window, float scale, void* out, int heads, int max_slices,
+                                           unsigned* status, cudaStream_t stream) {
+  if (n_dec == 0) return 0;
+  IB_CHECK_ARG(kv, "attention_decode_noalloc: the cache view is null");
+  IB_CHECK_ARG(n_dec > 0 && heads > 0 && max_slices > 0 && kv->head_dim > 0, "attention_decode_noalloc: bad sizes n=%d heads=%d slices=%d", n_dec,
+               heads, max_slices);
+  const unsigned long long slots = (unsigned long long)n_dec * heads * max_slices;
+  const unsigned long long need = slots * (unsigned long long)(kv->head_dim + 2);
+  IB_CHECK_ARG(need <= IB_DECODE_NOALLOC_MAX_FLOATS,
+               "attention_decode_noalloc: %d tokens x %d heads x %d slices x (head_dim %d + 2) = %llu float32 values, more than the fixed scratch of %u; "
+               "use ib_attention_decode with scratch of your own",
+               n_dec, heads, max_slices, kv->head_dim, need, IB_DECODE_NOALLOC_MAX_FLOATS);
+  float* scratch = nullptr;
+  if (noalloc_scratch(&scratch)) return 1;
+  float* part_o = scratch;
+  float* part_ml = scratch + slots * kv->head_dim;
+  return ib_attention_decode(q, kv, dec_tokens, n_dec, positions, seg_of_token, window, scale, part_o, part_ml, out, heads, max_slices, status,
+                             stream);
+}

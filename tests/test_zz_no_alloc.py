@@ -1,0 +1,91 @@
+"""The decode-attention entry point that allocates nothing, called through its exported C symbol.
+
+Some hosts of this library cannot allocate device memory while they run (they gave the device to
+an arena of their own, or their serving loop forbids calls that may synchronise the device), so
+`ib_attention_decode_noalloc` keeps the kernel's scratch in a fixed array inside the library. This
+test checks it against the ordinary entry point, which takes scratch from the caller, on two calls
+in a row (the second call finds the first call's leftovers in the shared array), and checks that a
+call too large for the fixed array is refused. It sits in a file that pytest collects last."""
+from __future__ import annotations
+
+import ctypes as C
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+SLICE = 128
+MAX_FLOATS = 2 * 1024 * 1024
+
+
+def _case(seed, heads, kvh, hd, page, lengths):
+    """Decoded tokens at the last position of requests with the given context lengths."""
+    from inference_bench_b200.kernels.ops import KvLayerView
+    g = torch.Generator().manual_seed(seed)
+    n = len(lengths)
+    need = [-(-L // page) for L in lengths]
+    total = sum(need) + 3
+    order = np.random.default_rng(seed).permutation(total)
+    pool = (torch.randn(total, 1, 2, kvh, page, hd, generator=g)).to(torch.bfloat16)
+    table = np.full((n, max(need) + 1), -1, dtype=np.int32)
+    at = 0
+    for s in range(n):
+        for p in range(need[s]):
+            table[s, p] = order[at]
+            at += 1
+    q = torch.randn(n, heads * hd, generator=g).to(torch.bfloat16)
+    view = KvLayerView(pool.to(DEV), 0, torch.from_numpy(table).to(DEV))
+    positions = torch.tensor([L - 1 for L in lengths], dtype=torch.int32, device=DEV)
+    seg = torch.arange(n, dtype=torch.int32, device=DEV)
+    return q.to(DEV), view, positions, seg
+
+
+def test_no_alloc_entry_point_matches_the_ordinary_one():
+    from inference_bench_b200.kernels import lib as L
+    lib = L.load()
+    fn = lib.ib_attention_decode_noalloc
+    fn.restype = C.c_int
+    fn.argtypes = [C.c_void_p, C.POINTER(L.KvView), C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_float, C.c_void_p, C.c_int, C.c_int,
+                   C.c_void_p, C.c_void_p]
+    ref_fn = lib.ib_attention_decode
+    ref_fn.restype = C.c_int
+    ref_fn.argtypes = [C.c_void_p, C.POINTER(L.KvView), C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_float, C.c_void_p, C.c_void_p,
+                       C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    stream = torch.cuda.current_stream().cuda_stream
+    for seed, (heads, kvh, hd, page, lengths, window) in enumerate([(8, 2, 128, 16, [700, 129, 5, 1024], 0), (4, 1, 64, 32, [300, 64, 2000], 150)]):
+        q, view, positions, seg = _case(seed, heads, kvh, hd, page, lengths)
+        n = len(lengths)
+        max_slices = max(lengths) // SLICE + 1
+        cview = view.c_view()
+        scale = 1 / math.sqrt(hd)
+        part_o = torch.empty(n * heads * max_slices * hd, device=DEV)
+        part_ml = torch.empty(n * heads * max_slices * 2, device=DEV)
+        want = torch.empty_like(q)
+        rc = ref_fn(q.data_ptr(), C.byref(cview), seg.data_ptr(), n, positions.data_ptr(), seg.data_ptr(), window, scale, part_o.data_ptr(),
+                    part_ml.data_ptr(), want.data_ptr(), heads, max_slices, status.data_ptr(), stream)
+        assert rc == 0, lib.ib_last_error()
+        for call in range(2):
+            got = torch.full_like(q, float("nan"))
+            before = torch.cuda.memory_allocated(DEV)
+            rc = fn(q.data_ptr(), C.byref(cview), seg.data_ptr(), n, positions.data_ptr(), seg.data_ptr(), window, scale, got.data_ptr(), heads,
+                    max_slices, status.data_ptr(), stream)
+            assert rc == 0, lib.ib_last_error()
+            torch.cuda.synchronize()
+            assert torch.cuda.memory_allocated(DEV) == before
+            assert status.item() == 0
+            diff = (got.float() - want.float()).abs().max().item()
+            assert diff <= 1.5e-2 * want.float().abs().max().item(), f"case {seed}, call {call}: differs by {diff}"
+    # a call beyond the fixed scratch is refused with a message, and nothing runs
+    q, view, positions, seg = _case(9, 32, 8, 128, 16, [100] * 8)
+    cview = view.c_view()
+    out = torch.zeros_like(q)
+    too_many = MAX_FLOATS // (8 * 32 * 130) + 1
+    rc = fn(q.data_ptr(), C.byref(cview), seg.data_ptr(), 8, positions.data_ptr(), seg.data_ptr(), 0, 0.1, out.data_ptr(), 32, too_many,
+            status.data_ptr(), stream)
+    torch.cuda.synchronize()
+    assert rc != 0 and b"more than the fixed scratch" in lib.ib_last_error()
+    assert out.abs().max().item() == 0
