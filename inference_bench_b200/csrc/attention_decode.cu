@@ -1,8 +1,8 @@
 // Decode attention over the paged cache, bfloat16, split over the context.
 //
-// One CTA = one decoded token's kv head and one 128-key slice of its context. The query heads that
+// One CTA = one decoded token's kv head and one 64-key slice of its context. The query heads that
 // share the kv head (the GQA group, up to 16) are the rows of a 16-row MMA tile, so keys and values
-// are read from memory once per group. Each of the 4 warps takes 32 keys of the slice:
+// are read from memory once per group. Each of the 4 warps takes 16 keys of the slice:
 // S = Q K^T (m16n8k16 bfloat16 MMAs, float32 accumulators), softmax statistics in float32 base 2,
 // O = P V; the warps' partial results are merged in shared memory and written to scratch as an
 // unnormalised (max, sum, O) triple per (token, head, slice). A second kernel merges the slices.
@@ -13,8 +13,11 @@
 
 namespace {
 
-constexpr int kSlice = 128;  // keys per CTA
 constexpr int kWarps = 4;
+constexpr int kKeysPerWarp = 16;                 // 16 or 32
+constexpr int kSlice = kWarps * kKeysPerWarp;    // keys per CTA
+constexpr int kNT = kKeysPerWarp / 8;            // 8-key MMA column tiles per warp
+constexpr int kKS = kKeysPerWarp / 16;           // 16-key MMA steps per warp
 
 template <int HD>
 __global__ void __launch_bounds__(kWarps * 32)
@@ -23,11 +26,13 @@ __global__ void __launch_bounds__(kWarps * 32)
                         float* __restrict__ part_o, float* __restrict__ part_ml, int heads, int max_slices, unsigned* __restrict__ status) {
   constexpr int CPR = HD / 8;  // 16-byte chunks per row
   extern __shared__ __align__(128) uint8_t smem[];
-  // layout: Q tile [16][HD] | K tile [128][HD] | V tile [128][HD]; the merge buffers reuse K and V
+  // layout: Q tile [16][HD] | K tile [slice][HD] | V tile [slice][HD]; the merge buffers reuse all three
   const uint32_t q_s = mt::smem_u32(smem);
   const uint32_t k_s = q_s + 16 * HD * 2;
   const uint32_t v_s = k_s + kSlice * HD * 2;
 
+  ib::pdl_launch_dependents();
+  ib::pdl_wait();
   const int kvh = blockIdx.x, item = blockIdx.y, slice = blockIdx.z;
   const int t = dec_tokens[item];
   const int pos = positions[t], seg = seg_of_token[t];
@@ -68,11 +73,11 @@ __global__ void __launch_bounds__(kWarps * 32)
   mt::cp_async_wait<0>();
   __syncthreads();
 
-  // ---- S = Q K^T for this warp's 32 keys
-  const int wkey = warp * 32;
-  float s[4][4];
+  // ---- S = Q K^T for this warp's keys
+  const int wkey = warp * kKeysPerWarp;
+  float s[kNT][4];
 #pragma unroll
-  for (int j = 0; j < 4; j++)
+  for (int j = 0; j < kNT; j++)
 #pragma unroll
     for (int e = 0; e < 4; e++) s[j][e] = 0.f;
 #pragma unroll
@@ -80,7 +85,7 @@ __global__ void __launch_bounds__(kWarps * 32)
     uint32_t a[4], b[4];
     mt::load_a_frag<HD>(q_s, 0, kk, lane, a);
 #pragma unroll
-    for (int pr = 0; pr < 2; pr++) {
+    for (int pr = 0; pr < kKS; pr++) {
       mt::load_k_frag<HD>(k_s, wkey + 16 * pr, kk, lane, b);
       mt::mma_16816(s[2 * pr], a, b[0], b[1]);
       mt::mma_16816(s[2 * pr + 1], a, b[2], b[3]);
@@ -90,7 +95,7 @@ __global__ void __launch_bounds__(kWarps * 32)
   const int g = lane >> 2, tq = lane & 3;
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 #pragma unroll
-  for (int j = 0; j < 4; j++)
+  for (int j = 0; j < kNT; j++)
 #pragma unroll
     for (int e = 0; e < 4; e++) {
       int key = k0 + wkey + 8 * j + 2 * tq + (e & 1);
@@ -104,9 +109,9 @@ __global__ void __launch_bounds__(kWarps * 32)
     m[r] = fmaxf(m[r], __shfl_xor_sync(0xffffffffu, m[r], 2));
   }
   const float mu[2] = {m[0] == -INFINITY ? 0.f : m[0], m[1] == -INFINITY ? 0.f : m[1]};
-  uint32_t p[2][4];  // A fragments of P for the two 16-key steps
+  uint32_t p[kKS][4];  // A fragments of P, one per 16-key step
 #pragma unroll
-  for (int j = 0; j < 4; j++) {
+  for (int j = 0; j < kNT; j++) {
     float e0 = exp2f(s[j][0] - mu[0]), e1 = exp2f(s[j][1] - mu[0]), e2 = exp2f(s[j][2] - mu[1]), e3 = exp2f(s[j][3] - mu[1]);
     l[0] += e0 + e1;
     l[1] += e2 + e3;
@@ -125,7 +130,7 @@ __global__ void __launch_bounds__(kWarps * 32)
 #pragma unroll
     for (int e = 0; e < 4; e++) o[n][e] = 0.f;
 #pragma unroll
-  for (int ks = 0; ks < 2; ks++)
+  for (int ks = 0; ks < kKS; ks++)
 #pragma unroll
     for (int dp = 0; dp < HD / 16; dp++) {
       uint32_t b[4];
@@ -133,10 +138,10 @@ __global__ void __launch_bounds__(kWarps * 32)
       mt::mma_16816(o[2 * dp], p[ks], b[0], b[1]);
       mt::mma_16816(o[2 * dp + 1], p[ks], b[2], b[3]);
     }
-  // ---- merge the four warps through shared memory (K and V tiles are no longer needed)
+  // ---- merge the four warps through shared memory (the tiles are no longer needed)
   __syncthreads();
-  float* ml_s = (float*)(smem + 16 * HD * 2);                  // [warps][16][2]
-  float* o_s = ml_s + kWarps * 16 * 2;                         // [warps][16][HD]
+  float* ml_s = (float*)smem;                                  // [warps][16][2], in the Q tile
+  float* o_s = (float*)(smem + 16 * HD * 2);                   // [warps][16][HD], in the K and V tiles
   if (tq == 0) {
     ml_s[(warp * 16 + g) * 2] = m[0];
     ml_s[(warp * 16 + g) * 2 + 1] = l[0];
@@ -176,6 +181,8 @@ __global__ void __launch_bounds__(kWarps * 32)
 template <int HD>
 __global__ void decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, const int* __restrict__ dec_tokens,
                                       const int* __restrict__ positions, int window, __nv_bfloat16* __restrict__ out, int heads, int max_slices) {
+  ib::pdl_launch_dependents();
+  ib::pdl_wait();
   const int h = blockIdx.x, item = blockIdx.y;
   const int t = dec_tokens[item];
   const int pos = positions[t];
@@ -198,7 +205,8 @@ __global__ void decode_combine_kernel(const float* __restrict__ part_o, const fl
 template <int HD>
 int launch(const void* q, const IbKvView* kv, const int* dec_tokens, int n_dec, const int* positions, const int* seg_of_token, int window,
            float scale, float* part_o, float* part_ml, void* out, int heads, int max_slices, unsigned* status, cudaStream_t stream) {
-  constexpr int smem = (16 + 2 * kSlice) * HD * 2;
+  constexpr int tiles = (16 + 2 * kSlice) * HD * 2, merge = 16 * HD * 2 + kWarps * 16 * HD * 4;
+  constexpr int smem = tiles > merge ? tiles : merge;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(decode_split_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -206,10 +214,10 @@ int launch(const void* q, const IbKvView* kv, const int* dec_tokens, int n_dec, 
     configured = true;
   }
   dim3 grid(kv->kv_heads, n_dec, max_slices);
-  decode_split_kernel<HD><<<grid, kWarps * 32, smem, stream>>>((const __nv_bfloat16*)q, *kv, dec_tokens, positions, seg_of_token, window,
+  ib::launch(decode_split_kernel<HD>, grid, kWarps * 32, smem, stream, (const __nv_bfloat16*)q, *kv, dec_tokens, positions, seg_of_token, window,
                                                                scale * 1.4426950408889634f, part_o, part_ml, heads, max_slices, status);
   IB_CHECK_LAUNCH("attention_decode split");
-  decode_combine_kernel<HD><<<dim3(heads, n_dec), HD, 0, stream>>>(part_o, part_ml, dec_tokens, positions, window, (__nv_bfloat16*)out, heads,
+  ib::launch(decode_combine_kernel<HD>, dim3(heads, n_dec), HD, 0, stream, part_o, part_ml, dec_tokens, positions, window, (__nv_bfloat16*)out, heads,
                                                                    max_slices);
   IB_CHECK_LAUNCH("attention_decode combine");
   return 0;
@@ -219,7 +227,9 @@ int launch(const void* q, const IbKvView* kv, const int* dec_tokens, int n_dec, 
 
 // Attention for decoded tokens (one query position each). dec_tokens[i] is the flat row of the i-th
 // decoded token in q/out/positions/seg_of_token. Scratch: part_o float32 [n_dec * heads * max_slices * head_dim],
-// part_ml float32 [n_dec * heads * max_slices * 2]; max_slices * 128 must cover every position in use.
+// part_ml float32 [n_dec * heads * max_slices * 2]; max_slices * ib_attention_decode_slice() must cover every position in use.
+extern "C" int ib_attention_decode_slice() { return kSlice; }
+
 extern "C" int ib_attention_decode(const void* q, const IbKvView* kv, const int* dec_tokens, int n_dec, const int* positions,
                                    const int* seg_of_token, int window, float scale, float* part_o, float* part_ml, void* out, int heads,
                                    int max_slices, unsigned* status, cudaStream_t stream) {

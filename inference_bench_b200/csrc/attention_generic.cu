@@ -23,6 +23,8 @@ __global__ void qk_norm_rope_kv_kernel(const float* __restrict__ qkv, int P, siz
                                        const int* __restrict__ seg_of_token, A* __restrict__ q_out, IbKvView kv, int write_kv, int T,
                                        int heads, unsigned* __restrict__ status) {
   __shared__ float vec[kWarps][kMaxHeadDim];
+  ib::pdl_launch_dependents();
+  ib::pdl_wait();
   const int hd = kv.head_dim, kvh = kv.kv_heads;
   const int slots = heads + 2 * kvh;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -80,6 +82,8 @@ __global__ void attention_generic_kernel(const A* __restrict__ q, IbKvView kv, c
                                          const int* __restrict__ seg_of_token, int window, float scale, A* __restrict__ out, int T,
                                          int heads, unsigned* __restrict__ status) {
   __shared__ float qs[kWarps][kMaxHeadDim];
+  ib::pdl_launch_dependents();
+  ib::pdl_wait();
   const int hd = kv.head_dim;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   long long item = (long long)blockIdx.x * kWarps + warp;
@@ -168,11 +172,11 @@ extern "C" int ib_qk_norm_rope_kv(const float* qkv, int P, long long stride_p, c
   long long items = (long long)T * (heads + 2 * kv->kv_heads);
   unsigned blocks = (unsigned)((items + kWarps - 1) / kWarps);
   if (act_dtype == IB_F32)
-    qk_norm_rope_kv_kernel<float, float><<<blocks, kWarps * 32, 0, stream>>>(qkv, P, (size_t)stride_p, q_norm_w, k_norm_w, eps, cos_t, sin_t,
+    ib::launch(qk_norm_rope_kv_kernel<float, float>, blocks, kWarps * 32, 0, stream, qkv, P, (size_t)stride_p, q_norm_w, k_norm_w, eps, cos_t, sin_t,
                                                                             rot_half, positions, seg_of_token, (float*)q_out, *kv, write_kv,
                                                                             T, heads, status);
   else
-    qk_norm_rope_kv_kernel<__nv_bfloat16, __nv_bfloat16><<<blocks, kWarps * 32, 0, stream>>>(
+    ib::launch(qk_norm_rope_kv_kernel<__nv_bfloat16, __nv_bfloat16>, blocks, kWarps * 32, 0, stream, 
         qkv, P, (size_t)stride_p, q_norm_w, k_norm_w, eps, cos_t, sin_t, rot_half, positions, seg_of_token, (__nv_bfloat16*)q_out, *kv,
         write_kv, T, heads, status);
   IB_CHECK_LAUNCH("qk_norm_rope_kv");
@@ -188,10 +192,10 @@ extern "C" int ib_attention_generic(const void* q, int act_dtype, const IbKvView
   long long items = (long long)T * heads;
   unsigned blocks = (unsigned)((items + kWarps - 1) / kWarps);
   if (act_dtype == IB_F32)
-    attention_generic_kernel<float, float><<<blocks, kWarps * 32, 0, stream>>>((const float*)q, *kv, positions, seg_of_token, window, scale,
+    ib::launch(attention_generic_kernel<float, float>, blocks, kWarps * 32, 0, stream, (const float*)q, *kv, positions, seg_of_token, window, scale,
                                                                               (float*)out, T, heads, status);
   else
-    attention_generic_kernel<__nv_bfloat16, __nv_bfloat16><<<blocks, kWarps * 32, 0, stream>>>(
+    ib::launch(attention_generic_kernel<__nv_bfloat16, __nv_bfloat16>, blocks, kWarps * 32, 0, stream, 
         (const __nv_bfloat16*)q, *kv, positions, seg_of_token, window, scale, (__nv_bfloat16*)out, T, heads, status);
   IB_CHECK_LAUNCH("attention_generic");
   return 0;

@@ -45,6 +45,8 @@ __global__ void __launch_bounds__(kWarps * 32)
   const uint32_t q_s = mt::smem_u32(smem);                // [64][HD]
   const uint32_t kv_s = q_s + BM * HD * 2;                // 2 stages x (K tile, V tile)
 
+  ib::pdl_launch_dependents();
+  ib::pdl_wait();
   const int tile = blockIdx.x, h = blockIdx.y;
   const int seg = tile_seg[tile], row0 = tile_row0[tile];
   const int n = seg_start[seg + 1] - seg_start[seg];
@@ -192,7 +194,7 @@ int launch(const void* q, const IbKvView* kv, const int* tile_seg, const int* ti
     IB_CHECK_ARG(e == cudaSuccess, "attention_prefill: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
-  prefill_kernel<HD><<<dim3(n_tiles, heads), kWarps * 32, smem, stream>>>((const __nv_bfloat16*)q, *kv, tile_seg, tile_row0, seg_start, seg_pos0,
+  ib::launch(prefill_kernel<HD>, dim3(n_tiles, heads), kWarps * 32, smem, stream, (const __nv_bfloat16*)q, *kv, tile_seg, tile_row0, seg_start, seg_pos0,
                                                                          window, scale * 1.4426950408889634f, (__nv_bfloat16*)out, heads, status);
   IB_CHECK_LAUNCH("attention_prefill");
   return 0;

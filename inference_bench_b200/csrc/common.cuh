@@ -30,7 +30,32 @@ int ib_set_error(const char* fmt, ...);
 #define IB_ERR_BAD_TOKEN 2u     // a token id outside the vocabulary
 #define IB_ERR_WAIT_TIMEOUT 4u  // a bounded wait on an mbarrier ran out
 
+// Programmatic dependent launch: a kernel may be scheduled while the kernel before it in the stream
+// is still running; it runs its own set-up, and ib::pdl_wait() then blocks until everything earlier
+// in the stream has finished and its writes are visible. Nothing before pdl_wait() may read memory
+// that an earlier kernel writes, nor write memory at all.
+extern "C" int ib_pdl_enabled();
+extern "C" void ib_set_pdl(int on);
+
 namespace ib {
+
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... Exp, typename... Act>
+inline cudaError_t launch(void (*kernel)(Exp...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Act&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = ib_pdl_enabled();
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<Exp>(args)...);
+}
 
 template <typename T>
 __device__ __forceinline__ float to_f32(T v);

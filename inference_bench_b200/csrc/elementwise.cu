@@ -18,12 +18,18 @@ int ib_set_error(const char* fmt, ...) {
   return 1;
 }
 
+static int g_pdl = 1;
+extern "C" int ib_pdl_enabled() { return g_pdl; }
+extern "C" void ib_set_pdl(int on) { g_pdl = on ? 1 : 0; }
+
 namespace {
 
 // ---------------------------------------------------------------- embedding
 template <typename W>
 __global__ void embed_kernel(const W* __restrict__ table, const int* __restrict__ tokens, float* __restrict__ x, int H, int V,
                              unsigned* __restrict__ status) {
+  ib::pdl_launch_dependents();
+  ib::pdl_wait();
   int t = blockIdx.y;
   int tok = tokens[t];
   if (tok < 0 || tok >= V) {
@@ -47,6 +53,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restric
                                    int write_x) {
   extern __shared__ float row[];
   __shared__ float scratch[32];
+  ib::pdl_launch_dependents();
+  ib::pdl_wait();
   int r = blockIdx.x;
   int t = rows ? rows[r] : r;
   float* xr = x + (size_t)t * H;
@@ -73,6 +81,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restric
 // (crates/kir/tests/golden/attention/RopeKvWrite_bf16x2_sm120.cu:32-35).
 __global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq, float* __restrict__ cos_t,
                                   float* __restrict__ sin_t, int T, int half) {
+  ib::pdl_launch_dependents();
+  ib::pdl_wait();
   int idx = blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= T * half) return;
   int t = idx / half, i = idx - t * half;
@@ -87,6 +97,8 @@ __global__ void rope_table_kernel(const int* __restrict__ positions, const float
 // gu[p][t][0:I] = gate, gu[p][t][I:2I] = up (partials summed first); act = g / (1 + exp(-g)) * u.
 template <typename O>
 __global__ void silu_mul_kernel(const float* __restrict__ gu, int P, size_t stride, O* __restrict__ act, int I) {
+  ib::pdl_launch_dependents();
+  ib::pdl_wait();
   int t = blockIdx.y;
   const float* row = gu + (size_t)t * 2 * I;
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < I; i += gridDim.x * blockDim.x) {
@@ -108,9 +120,9 @@ extern "C" int ib_embed(const void* table, int table_dtype, const int* tokens, f
   IB_CHECK_ARG(T <= 65535, "embed: T=%d rows exceed the grid limit 65535", T);
   dim3 grid((H + 255) / 256, T);
   if (table_dtype == IB_F32)
-    embed_kernel<float><<<grid, 256, 0, stream>>>((const float*)table, tokens, x, H, V, status);
+    ib::launch(embed_kernel<float>, grid, 256, 0, stream, (const float*)table, tokens, x, H, V, status);
   else if (table_dtype == IB_BF16)
-    embed_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)table, tokens, x, H, V, status);
+    ib::launch(embed_kernel<__nv_bfloat16>, grid, 256, 0, stream, (const __nv_bfloat16*)table, tokens, x, H, V, status);
   else
     return ib_set_error("embed: unknown table dtype %d", table_dtype);
   IB_CHECK_LAUNCH("embed");
@@ -127,11 +139,11 @@ extern "C" int ib_add_rmsnorm(float* x, const float* delta, int P, long long del
   int threads = H >= 4096 ? 1024 : (H >= 1024 ? 512 : 256);
   if (out_dtype == IB_F32) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(add_rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    add_rmsnorm_kernel<float><<<n_rows, threads, smem, stream>>>(x, delta, P, (size_t)delta_stride, w, (float*)out, rows, H, eps, write_x);
+    ib::launch(add_rmsnorm_kernel<float>, n_rows, threads, smem, stream, x, delta, P, (size_t)delta_stride, w, (float*)out, rows, H, eps, write_x);
   } else if (out_dtype == IB_BF16) {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(add_rmsnorm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    add_rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, smem, stream>>>(x, delta, P, (size_t)delta_stride, w, (__nv_bfloat16*)out, rows, H,
+    ib::launch(add_rmsnorm_kernel<__nv_bfloat16>, n_rows, threads, smem, stream, x, delta, P, (size_t)delta_stride, w, (__nv_bfloat16*)out, rows, H,
                                                                           eps, write_x);
   } else {
     return ib_set_error("add_rmsnorm: unknown output dtype %d", out_dtype);
@@ -145,7 +157,7 @@ extern "C" int ib_rope_table(const int* positions, const float* inv_freq, float*
   if (T == 0 || half == 0) return 0;
   IB_CHECK_ARG(T > 0 && half > 0, "rope_table: bad sizes T=%d half=%d", T, half);
   long long n = (long long)T * half;
-  rope_table_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(positions, inv_freq, cos_t, sin_t, T, half);
+  ib::launch(rope_table_kernel, (unsigned)((n + 255) / 256), 256, 0, stream, positions, inv_freq, cos_t, sin_t, T, half);
   IB_CHECK_LAUNCH("rope_table");
   return 0;
 }
@@ -157,9 +169,9 @@ extern "C" int ib_silu_mul(const float* gu, int P, long long stride, void* act, 
   dim3 grid((I + 255) / 256, T);
   if (grid.x > 64) grid.x = 64;
   if (act_dtype == IB_F32)
-    silu_mul_kernel<float><<<grid, 256, 0, stream>>>(gu, P, (size_t)stride, (float*)act, I);
+    ib::launch(silu_mul_kernel<float>, grid, 256, 0, stream, gu, P, (size_t)stride, (float*)act, I);
   else if (act_dtype == IB_BF16)
-    silu_mul_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(gu, P, (size_t)stride, (__nv_bfloat16*)act, I);
+    ib::launch(silu_mul_kernel<__nv_bfloat16>, grid, 256, 0, stream, gu, P, (size_t)stride, (__nv_bfloat16*)act, I);
   else
     return ib_set_error("silu_mul: unknown output dtype %d", act_dtype);
   IB_CHECK_LAUNCH("silu_mul");

@@ -15,6 +15,8 @@ template <typename X, typename W>
 __global__ void __launch_bounds__(256) gemm_simt_kernel(const X* __restrict__ x, const W* __restrict__ w, float* __restrict__ out, int T,
                                                         int N, int K) {
   __shared__ float xs[BK][BM + 1];
+  ib::pdl_launch_dependents();
+  ib::pdl_wait();
   __shared__ float ws[BK][BN + 1];
   const int t0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
   const int tid = threadIdx.x;
@@ -71,11 +73,11 @@ extern "C" int ib_gemm_simt(const void* x, int x_dtype, const void* w, int w_dty
   dim3 grid((N + BN - 1) / BN, (T + BM - 1) / BM);
   IB_CHECK_ARG(grid.y <= 65535, "gemm_simt: T=%d rows exceed the grid limit", T);
   if (x_dtype == IB_F32 && w_dtype == IB_F32)
-    gemm_simt_kernel<float, float><<<grid, 256, 0, stream>>>((const float*)x, (const float*)w, out, T, N, K);
+    ib::launch(gemm_simt_kernel<float, float>, grid, 256, 0, stream, (const float*)x, (const float*)w, out, T, N, K);
   else if (x_dtype == IB_BF16 && w_dtype == IB_BF16)
-    gemm_simt_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, out, T, N, K);
+    ib::launch(gemm_simt_kernel<__nv_bfloat16, __nv_bfloat16>, grid, 256, 0, stream, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, out, T, N, K);
   else if (x_dtype == IB_F32 && w_dtype == IB_BF16)
-    gemm_simt_kernel<float, __nv_bfloat16><<<grid, 256, 0, stream>>>((const float*)x, (const __nv_bfloat16*)w, out, T, N, K);
+    ib::launch(gemm_simt_kernel<float, __nv_bfloat16>, grid, 256, 0, stream, (const float*)x, (const __nv_bfloat16*)w, out, T, N, K);
   else
     return ib_set_error("gemm_simt: unsupported dtypes x=%d w=%d", x_dtype, w_dtype);
   IB_CHECK_LAUNCH("gemm_simt");

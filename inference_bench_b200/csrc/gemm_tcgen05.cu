@@ -25,7 +25,8 @@ struct Tile {
   static constexpr int kABytes = BM * BK * 2;
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = BN >= 256 ? 4 : (BN >= 128 ? 6 : 8);
+  // few tokens: shallower pipelines so that two CTAs share an SM and more loads are in flight
+  static constexpr int kStages = BN >= 256 ? 4 : (BN >= 128 ? 6 : (BN >= 64 ? 8 : (BN >= 32 ? 5 : 6)));
   static constexpr int kTmemCols = BN < 32 ? 32 : BN;
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
 };
@@ -51,6 +52,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int kt_end = min(total_kt, kt_begin + ktiles_per_split);
   const int nkt = max(0, kt_end - kt_begin);
 
+  ib::pdl_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) {
       sm100::mbar_init(&full[s], 1);
@@ -72,7 +74,17 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (sm100::elect_one()) {
       sm100::prefetch_tensormap(&tmap_w);
       sm100::prefetch_tensormap(&tmap_x);
-      for (int i = 0; i < nkt; i++) {
+      // The weights do not depend on earlier kernels: fill the pipeline with them before waiting
+      // for the kernel that produces x, then send the x tiles after.
+      const int first = min(nkt, STAGES);
+      for (int i = 0; i < first; i++) {
+        sm100::mbar_arrive_expect_tx(&full[i], TL::kStageBytes);
+        sm100::tma_load_2d(tiles + i * TL::kStageBytes, &tmap_w, (kt_begin + i) * BK, n0, &full[i]);
+      }
+      ib::pdl_wait();
+      for (int i = 0; i < first; i++)
+        sm100::tma_load_2d(tiles + i * TL::kStageBytes + TL::kABytes, &tmap_x, (kt_begin + i) * BK, t0, &full[i]);
+      for (int i = first; i < nkt; i++) {
         const int s = i % STAGES;
         if (!sm100::mbar_wait(&empty[s], ((i / STAGES) & 1) ^ 1)) {
           atomicOr(status, IB_ERR_WAIT_TIMEOUT);
@@ -111,6 +123,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     // Epilogue: this warp's quarter of the 128 accumulator lanes.
     const int q = warp & 3;
     const int n = n0 + q * 32 + lane;
+    ib::pdl_wait();   // the output buffer may still be in use by an earlier kernel
     bool ok = true;
     if (nkt > 0) {
       ok = sm100::mbar_wait(acc_full, 0);
@@ -193,7 +206,7 @@ int launch(const CUtensorMap& tw, const CUtensorMap& tx, float* out, int T, int 
     configured = true;
   }
   dim3 grid((N + BM - 1) / BM, (T + BN - 1) / BN, splits);
-  gemm_tcgen05_kernel<BN><<<grid, kThreads, Tile<BN>::kSmemBytes, stream>>>(tw, tx, out, T, N, K, kt_per_split, status);
+  ib::launch(gemm_tcgen05_kernel<BN>, grid, kThreads, Tile<BN>::kSmemBytes, stream, tw, tx, out, T, N, K, kt_per_split, status);
   IB_CHECK_LAUNCH("gemm_tcgen05");
   return 0;
 }

@@ -92,90 +92,121 @@ __device__ float mass_at_least(const float* row, int V, float inv_temp, float m,
   return ib::block_sum(z, scratch);
 }
 
-__global__ void __launch_bounds__(kThreads) sample_rows_kernel(const float* __restrict__ logits, int V, const RowParams* __restrict__ params,
-                                                               int* __restrict__ tokens) {
+// Stage 1, one block per row: the candidate threshold on v = logit / T. Rows that are greedy or
+// have no filter leave at once with -inf.
+__global__ void __launch_bounds__(kThreads) sample_threshold_kernel(const float* __restrict__ logits, int V, const RowParams* __restrict__ params,
+                                                                    float* __restrict__ threshold) {
   __shared__ float scratch[32];
-  __shared__ float best_v[kThreads / 32];
-  __shared__ int best_i[kThreads / 32];
+  ib::pdl_launch_dependents();
+  ib::pdl_wait();
   const float* row = logits + (size_t)blockIdx.x * V;
   const RowParams p = params[blockIdx.x];
-  const bool sampling = p.inv_temp > 0.f;
-  float thr = -INFINITY;
-  if (sampling) {
-    float m = -INFINITY;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) m = fmaxf(m, row[i] * p.inv_temp);
-    m = block_max(m, scratch);
-    if (p.top_k > 0 && p.top_k < V) thr = kth_largest(row, V, p.inv_temp, p.top_k);
-    if (p.top_p < 1.f) {
-      // Largest threshold whose candidates (also above the top-k threshold) hold mass >= top_p * total.
-      float z = mass_at_least(row, V, p.inv_temp, m, thr, scratch);
-      float target = fmaxf(p.top_p, 1e-9f) * z;
-      float lo = thr > -INFINITY ? thr : m - 88.f;
-      float hi = nextafterf(m, INFINITY);
-      for (int it = 0; it < 64; it++) {
-        float mid = 0.5f * (lo + hi);
-        if (mid <= lo || mid >= hi) break;
-        if (mass_at_least(row, V, p.inv_temp, m, mid, scratch) >= target)
-          lo = mid;
-        else
-          hi = mid;
-      }
-      // Snap to the smallest candidate value >= lo.
-      float low = INFINITY;
-      for (int i = threadIdx.x; i < V; i += blockDim.x) {
-        float v = row[i] * p.inv_temp;
-        if (v >= lo) low = fminf(low, v);
-      }
-      low = -block_max(-low, scratch);
-      thr = fmaxf(thr, low);
-    }
-    if (p.min_p > 0.f) thr = fmaxf(thr, m + logf(p.min_p));
+  const bool use_k = p.top_k > 0 && p.top_k < V, use_p = p.top_p < 1.f, use_m = p.min_p > 0.f;
+  if (!(p.inv_temp > 0.f) || !(use_k || use_p || use_m)) {
+    if (threadIdx.x == 0) threshold[blockIdx.x] = -INFINITY;
+    return;
   }
+  float thr = -INFINITY;
+  float m = -INFINITY;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) m = fmaxf(m, row[i] * p.inv_temp);
+  m = block_max(m, scratch);
+  if (use_k) thr = kth_largest(row, V, p.inv_temp, p.top_k);
+  if (use_p) {
+    // Largest threshold whose candidates (also above the top-k threshold) hold mass >= top_p * total.
+    float z = mass_at_least(row, V, p.inv_temp, m, thr, scratch);
+    float target = fmaxf(p.top_p, 1e-9f) * z;
+    float lo = thr > -INFINITY ? thr : m - 88.f;
+    float hi = nextafterf(m, INFINITY);
+    for (int it = 0; it < 64; it++) {
+      float mid = 0.5f * (lo + hi);
+      if (mid <= lo || mid >= hi) break;
+      if (mass_at_least(row, V, p.inv_temp, m, mid, scratch) >= target)
+        lo = mid;
+      else
+        hi = mid;
+    }
+    // Snap to the smallest candidate value >= lo.
+    float low = INFINITY;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      float v = row[i] * p.inv_temp;
+      if (v >= lo) low = fminf(low, v);
+    }
+    low = -block_max(-low, scratch);
+    thr = fmaxf(thr, low);
+  }
+  if (use_m) thr = fmaxf(thr, m + logf(p.min_p));
+  if (threadIdx.x == 0) threshold[blockIdx.x] = thr;
+}
+
+__device__ __forceinline__ void better(float& bv, int& bi, float ov, int oi) {  // the lowest index wins ties
+  if (ov > bv || (ov == bv && oi < bi)) {
+    bv = ov;
+    bi = oi;
+  }
+}
+
+// Best (value, index) of a block of kPickThreads threads; valid in thread 0.
+constexpr int kPickThreads = 256;
+__device__ void block_best(float& bv, int& bi) {
+  __shared__ float sv[kPickThreads / 32];
+  __shared__ int si[kPickThreads / 32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) better(bv, bi, __shfl_xor_sync(0xffffffffu, bv, o), __shfl_xor_sync(0xffffffffu, bi, o));
+  if (lane == 0) {
+    sv[warp] = bv;
+    si[warp] = bi;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    bv = lane < kPickThreads / 32 ? sv[lane] : -INFINITY;
+    bi = lane < kPickThreads / 32 ? si[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) better(bv, bi, __shfl_xor_sync(0xffffffffu, bv, o), __shfl_xor_sync(0xffffffffu, bi, o));
+  }
+}
+
+// Stage 2, grid (chunks, rows): the best candidate of one chunk of the vocabulary.
+__global__ void __launch_bounds__(kPickThreads) sample_pick_kernel(const float* __restrict__ logits, int V, const RowParams* __restrict__ params,
+                                                                   const float* __restrict__ threshold, float* __restrict__ part_v,
+                                                                   int* __restrict__ part_i, int chunk) {
+  ib::pdl_launch_dependents();
+  ib::pdl_wait();
+  const int r = blockIdx.y;
+  const float* row = logits + (size_t)r * V;
+  const RowParams p = params[r];
+  const bool sampling = p.inv_temp > 0.f;
+  const float thr = threshold[r];
+  const int begin = blockIdx.x * chunk, end = min(V, begin + chunk);
   float bv = -INFINITY;
   int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+  for (int i = begin + threadIdx.x; i < end; i += kPickThreads) {
     float v = row[i];
     if (sampling) {
       v *= p.inv_temp;
       if (v < thr) continue;
       v += gumbel(p.seed, p.step, (unsigned)i);
     }
-    if (v > bv || (v == bv && i < bi)) {
-      bv = v;
-      bi = i;
-    }
+    better(bv, bi, v, i);
   }
-  // Reduce (value, index) with the lowest index winning ties.
-  int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  block_best(bv, bi);
+  if (threadIdx.x == 0) {
+    part_v[r * gridDim.x + blockIdx.x] = bv;
+    part_i[r * gridDim.x + blockIdx.x] = bi;
+  }
+}
+
+// Stage 3, one warp per row: the best of the chunks.
+__global__ void sample_final_kernel(const float* __restrict__ part_v, const int* __restrict__ part_i, int chunks, int* __restrict__ tokens) {
+  ib::pdl_launch_dependents();
+  ib::pdl_wait();
+  const int r = blockIdx.x;
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int c = threadIdx.x; c < chunks; c += 32) better(bv, bi, part_v[r * chunks + c], part_i[r * chunks + c]);
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-    int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-    if (ov > bv || (ov == bv && oi < bi)) {
-      bv = ov;
-      bi = oi;
-    }
-  }
-  __syncthreads();
-  if (lane == 0) {
-    best_v[warp] = bv;
-    best_i[warp] = bi;
-  }
-  __syncthreads();
-  if (warp == 0) {
-    bv = lane < (blockDim.x >> 5) ? best_v[lane] : -INFINITY;
-    bi = lane < (blockDim.x >> 5) ? best_i[lane] : 0x7fffffff;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-      int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (ov > bv || (ov == bv && oi < bi)) {
-        bv = ov;
-        bi = oi;
-      }
-    }
-    if (lane == 0) tokens[blockIdx.x] = bi == 0x7fffffff ? 0 : bi;
-  }
+  for (int o = 16; o > 0; o >>= 1) better(bv, bi, __shfl_xor_sync(0xffffffffu, bv, o), __shfl_xor_sync(0xffffffffu, bi, o));
+  if (threadIdx.x == 0) tokens[r] = bi == 0x7fffffff ? 0 : bi;
 }
 
 // After a decode step: feed every row's sampled token back as its next input, move its position on
@@ -186,6 +217,8 @@ __global__ void __launch_bounds__(kThreads) sample_rows_kernel(const float* __re
 __global__ void advance_rows_kernel(const int* __restrict__ sampled, int* __restrict__ token_in, int* __restrict__ positions,
                                     int* __restrict__ pos0, RowParams* __restrict__ params, int* __restrict__ history, int* __restrict__ count,
                                     int rows, int history_len) {
+  ib::pdl_launch_dependents();
+  ib::pdl_wait();
   int i = blockIdx.x * blockDim.x + threadIdx.x;
   int c = count[0];
   if (i < rows) {
@@ -206,15 +239,29 @@ extern "C" int ib_advance_rows(const int* sampled, int* token_in, int* positions
                                int history_len, cudaStream_t stream) {
   if (rows == 0) return 0;
   IB_CHECK_ARG(rows > 0 && rows <= 1024 && history_len >= 0, "advance_rows: bad sizes rows=%d history=%d", rows, history_len);
-  advance_rows_kernel<<<1, 1024, 0, stream>>>(sampled, token_in, positions, pos0, (RowParams*)params, history, count, rows, history_len);
+  ib::launch(advance_rows_kernel, 1, 1024, 0, stream, sampled, token_in, positions, pos0, (RowParams*)params, history, count, rows, history_len);
   IB_CHECK_LAUNCH("advance_rows");
   return 0;
 }
 
-extern "C" int ib_sample_rows(const float* logits, int rows, int V, const void* params, int* tokens, cudaStream_t stream) {
+// chunks of the vocabulary per row in stage 2
+extern "C" int ib_sample_chunks(int V) { return V <= 4096 ? 1 : (V + 4095) / 4096 > 64 ? 64 : (V + 4095) / 4096; }
+
+// logits float32 [rows, V], params [rows] of six words -> tokens int32 [rows].
+// scratch: float32 [rows * (1 + 2 * ib_sample_chunks(V))] (threshold, then per-chunk best values and indices).
+extern "C" int ib_sample_rows(const float* logits, int rows, int V, const void* params, int* tokens, float* scratch, cudaStream_t stream) {
   if (rows == 0) return 0;
-  IB_CHECK_ARG(rows > 0 && V > 0, "sample_rows: bad sizes rows=%d V=%d", rows, V);
-  sample_rows_kernel<<<rows, kThreads, 0, stream>>>(logits, V, (const RowParams*)params, tokens);
-  IB_CHECK_LAUNCH("sample_rows");
+  IB_CHECK_ARG(rows > 0 && rows <= 65535 && V > 0, "sample_rows: bad sizes rows=%d V=%d", rows, V);
+  const int chunks = ib_sample_chunks(V);
+  const int chunk = (V + chunks - 1) / chunks;
+  float* threshold = scratch;
+  float* part_v = scratch + rows;
+  int* part_i = (int*)(part_v + (size_t)rows * chunks);
+  ib::launch(sample_threshold_kernel, rows, kThreads, 0, stream, logits, V, (const RowParams*)params, threshold);
+  IB_CHECK_LAUNCH("sample_rows threshold");
+  ib::launch(sample_pick_kernel, dim3(chunks, rows), kPickThreads, 0, stream, logits, V, (const RowParams*)params, threshold, part_v, part_i, chunk);
+  IB_CHECK_LAUNCH("sample_rows pick");
+  ib::launch(sample_final_kernel, rows, 32, 0, stream, part_v, part_i, chunks, tokens);
+  IB_CHECK_LAUNCH("sample_rows final");
   return 0;
 }

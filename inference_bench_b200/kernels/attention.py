@@ -14,7 +14,10 @@ import torch
 from . import lib as L
 from . import ops
 
-SLICE = 128   # keys per CTA of the decode kernel (csrc/attention_decode.cu)
+def decode_slice() -> int:
+    """Keys per CTA of the decode kernel (csrc/attention_decode.cu)."""
+    return int(L.load().ib_attention_decode_slice())
+
 QTILE = 64    # query rows per CTA of the prefill kernel (csrc/attention_prefill.cu)
 
 L.register("ib_attention_decode", [L._p, C.POINTER(L.KvView), L._p, L._i, L._p, L._p, L._i, L._f, L._p, L._p, L._p, L._i, L._i, L._p, L._p])
@@ -62,7 +65,8 @@ def paged_attention(ctx, q: torch.Tensor, cache: ops.KvLayerView, heads: int, wi
     stream = ops._stream()
     if work["n_dec"]:
         limit = view.table_stride * view.page_size
-        max_slices = -(-limit // SLICE) if work["max_pos"] is None else work["max_pos"] // SLICE + 1
+        slice_ = decode_slice()
+        max_slices = -(-limit // slice_) if work["max_pos"] is None else work["max_pos"] // slice_ + 1
         skey = ("decode_scratch", heads, view.head_dim, max_slices)
         if skey not in ctx.memo:
             n = work["n_dec"] * heads * max_slices

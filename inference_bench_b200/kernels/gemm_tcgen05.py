@@ -28,8 +28,9 @@ def choose(T: int, N: int, K: int, allow_split: bool = True) -> tuple[int, int]:
     tiles = -(-N // 128) * -(-T // bn)
     ktiles = -(-K // 64)
     splits = 1
-    if allow_split and tiles < SM_COUNT:
-        splits = max(1, min(SM_COUNT // tiles, ktiles // 4, 16))
+    slots = SM_COUNT * (2 if bn <= 32 else 1)      # CTAs resident at once (two per SM for the small token tiles)
+    if allow_split and tiles < slots:
+        splits = max(1, min(slots // tiles, ktiles // 4, 16))
         per = -(-ktiles // splits)
         splits = -(-ktiles // per)  # no empty split
     return bn, splits

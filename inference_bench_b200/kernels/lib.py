@@ -51,7 +51,7 @@ _SIGNATURES = {
     "ib_qk_norm_rope_kv": [_p, _i, _ll, _p, _p, _f, _p, _p, _i, _p, _p, _p, _i, C.POINTER(KvView), _i, _i, _i, _p, _p],
     "ib_attention_generic": [_p, _i, C.POINTER(KvView), _p, _p, _i, _f, _p, _i, _i, _p, _p],
     "ib_gemm_simt": [_p, _i, _p, _i, _p, _i, _i, _i, _p],
-    "ib_sample_rows": [_p, _i, _i, _p, _p, _p],
+    "ib_sample_rows": [_p, _i, _i, _p, _p, _p, _p],
     "ib_advance_rows": [_p, _p, _p, _p, _p, _p, _p, _i, _i, _p],
 }
 
@@ -94,13 +94,16 @@ def register(name: str, argtypes: list) -> None:
         fn.restype = C.c_int
 
 
-launches = 0   # kernel entry points called so far (each launches one kernel)
+launches = 0   # kernels launched so far through `call`
+
+
+KERNELS_PER_CALL = {"ib_sample_rows": 3, "ib_attention_decode": 2}
 
 
 def call(name: str, *args) -> None:
     global launches
     lib = load()
-    launches += 1
+    launches += KERNELS_PER_CALL.get(name, 1)
     rc = getattr(lib, name)(*args)
     if rc != 0:
         raise KernelError(lib.ib_last_error().decode(errors="replace"))

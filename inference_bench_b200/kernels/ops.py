@@ -166,13 +166,18 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     L.call("ib_gemm_simt", x.data_ptr(), dtype_code(x.dtype), w.data_ptr(), dtype_code(w.dtype), out.data_ptr(), T, N, K, _stream())
 
 
+def sample_chunks(vocab: int) -> int:
+    return int(L.load().ib_sample_chunks(int(vocab)))
+
+
 def sample_rows(logits: torch.Tensor, params: torch.Tensor, tokens: torch.Tensor) -> None:
     """params int32 [rows, 6] = (inv_temp bits, seed, step, top_k, top_p bits, min_p bits)."""
     rows, V = logits.shape
     _check("logits", logits, torch.float32)
     _check("params", params, torch.int32, (rows, 6))
     _check("tokens", tokens, torch.int32, (rows,))
-    L.call("ib_sample_rows", logits.data_ptr(), rows, V, params.data_ptr(), tokens.data_ptr(), _stream())
+    scratch = torch.empty(rows * (1 + 2 * sample_chunks(V)), dtype=torch.float32, device=logits.device)
+    L.call("ib_sample_rows", logits.data_ptr(), rows, V, params.data_ptr(), tokens.data_ptr(), scratch.data_ptr(), _stream())
 
 
 def advance_rows(sampled: torch.Tensor, token_in: torch.Tensor, positions: torch.Tensor, pos0: torch.Tensor, params: torch.Tensor,

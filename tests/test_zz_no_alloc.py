@@ -17,7 +17,6 @@ import torch
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
-SLICE = 128
 MAX_FLOATS = 2 * 1024 * 1024
 
 
@@ -55,6 +54,7 @@ def test_no_alloc_entry_point_matches_the_ordinary_one():
     ref_fn.argtypes = [C.c_void_p, C.POINTER(L.KvView), C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_float, C.c_void_p, C.c_void_p,
                        C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    SLICE = lib.ib_attention_decode_slice()
     stream = torch.cuda.current_stream().cuda_stream
     for seed, (heads, kvh, hd, page, lengths, window) in enumerate([(8, 2, 128, 16, [700, 129, 5, 1024], 0), (4, 1, 64, 32, [300, 64, 2000], 150)]):
         q, view, positions, seg = _case(seed, heads, kvh, hd, page, lengths)
