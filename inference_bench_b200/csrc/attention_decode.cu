@@ -15,7 +15,7 @@ namespace {
 
 constexpr int kWarps = 4;
 constexpr int kKeysPerWarp = 16;                 // 16 or 32
-constexpr int kSlice = kWarps * kKeysPerWarp;    // keys per CTA
+constexpr int kTile = kWarps * kKeysPerWarp;     // keys per tile; a CTA walks tiles_per_slice of them
 constexpr int kNT = kKeysPerWarp / 8;            // 8-key MMA column tiles per warp
 constexpr int kKS = kKeysPerWarp / 16;           // 16-key MMA steps per warp
 
@@ -23,13 +23,15 @@ template <int HD>
 __global__ void __launch_bounds__(kWarps * 32)
     decode_split_kernel(const __nv_bfloat16* __restrict__ q, IbKvView kv, const int* __restrict__ dec_tokens,
                         const int* __restrict__ positions, const int* __restrict__ seg_of_token, int window, float scale_log2e,
-                        float* __restrict__ part_o, float* __restrict__ part_ml, int heads, int max_slices, unsigned* __restrict__ status) {
-  constexpr int CPR = HD / 8;  // 16-byte chunks per row
+                        float* __restrict__ part_o, float* __restrict__ part_ml, int heads, int max_slices, int tiles_per_slice,
+                        unsigned* __restrict__ status) {
+  constexpr int CPR = HD / 8;              // 16-byte chunks per row
+  constexpr int TILE = kTile * HD * 2;     // bytes of one K (or V) tile
   extern __shared__ __align__(128) uint8_t smem[];
-  // layout: Q tile [16][HD] | K tile [slice][HD] | V tile [slice][HD]; the merge buffers reuse all three
+  // layout: Q tile [16][HD] | 2 stages x (K tile, V tile) | key offsets [2][kTile]; the merge buffers reuse the tiles
   const uint32_t q_s = mt::smem_u32(smem);
-  const uint32_t k_s = q_s + 16 * HD * 2;
-  const uint32_t v_s = k_s + kSlice * HD * 2;
+  const uint32_t kv_s = q_s + 16 * HD * 2;
+  long long* offs = (long long*)(smem + 16 * HD * 2 + 4 * TILE);
 
   ib::pdl_launch_dependents();
   ib::pdl_wait();
@@ -37,13 +39,41 @@ __global__ void __launch_bounds__(kWarps * 32)
   const int t = dec_tokens[item];
   const int pos = positions[t], seg = seg_of_token[t];
   const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-  const int k0 = slice * kSlice;
-  const int k_begin = max(lo, k0), k_end = min(pos + 1, k0 + kSlice);
+  const int slice_keys = tiles_per_slice * kTile;
+  const int k_begin = max(lo, slice * slice_keys), k_end = min(pos + 1, (slice + 1) * slice_keys);
   if (k_begin >= k_end) return;
+  const int tile_begin = k_begin / kTile, tile_end = (k_end - 1) / kTile + 1;
   const int group = heads / kv.kv_heads;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, tq = lane & 3;
+  const __nv_bfloat16* base = (const __nv_bfloat16*)kv.base;
 
-  // ---- stage Q (rows = the group's heads, zero rows above), K and V of the slice
+  // One thread per key looks its page up; then all threads copy 16-byte chunks.
+  auto load_tile = [&](int tile, int stage) {
+    long long* o = offs + stage * kTile;
+    if (tid < kTile) {
+      int key = tile * kTile + tid;
+      long long off = (key >= k_begin && key < k_end) ? ib::kv_offset(kv, seg, key, kvh) : -2;
+      if (off == -1) atomicOr(status, IB_ERR_BAD_PAGE);
+      o[tid] = off;
+    }
+    __syncthreads();
+    const uint32_t k_s = kv_s + stage * 2 * TILE, v_s = k_s + TILE;
+    for (int idx = tid; idx < kTile * CPR; idx += kWarps * 32) {
+      int row = idx / CPR, c = idx % CPR;
+      long long off = o[row];
+      uint32_t kd = k_s + mt::tile_offset<HD>(row, c), vd = v_s + mt::tile_offset<HD>(row, c);
+      if (off >= 0) {
+        mt::cp_async16(kd, base + off + c * 8);
+        mt::cp_async16(vd, base + off + kv.v_offset + c * 8);
+      } else {
+        mt::st_shared_zero16(kd);
+        mt::st_shared_zero16(vd);
+      }
+    }
+  };
+
+  // ---- stage Q (rows = the group's heads, zero rows above) and the first tile
   for (int idx = tid; idx < 16 * CPR; idx += kWarps * 32) {
     int row = idx / CPR, c = idx % CPR;
     uint32_t dst = q_s + mt::tile_offset<HD>(row, c);
@@ -52,94 +82,104 @@ __global__ void __launch_bounds__(kWarps * 32)
     else
       mt::st_shared_zero16(dst);
   }
-  const __nv_bfloat16* base = (const __nv_bfloat16*)kv.base;
-  bool bad_page = false;
-  for (int idx = tid; idx < kSlice * CPR; idx += kWarps * 32) {
-    int row = idx / CPR, c = idx % CPR;
-    int key = k0 + row;
-    long long off = (key >= k_begin && key < k_end) ? ib::kv_offset(kv, seg, key, kvh) : -2;
-    uint32_t kd = k_s + mt::tile_offset<HD>(row, c), vd = v_s + mt::tile_offset<HD>(row, c);
-    if (off >= 0) {
-      mt::cp_async16(kd, base + off + c * 8);
-      mt::cp_async16(vd, base + off + kv.v_offset + c * 8);
-    } else {
-      if (off == -1) bad_page = true;
-      mt::st_shared_zero16(kd);
-      mt::st_shared_zero16(vd);
-    }
-  }
-  if (bad_page) atomicOr(status, IB_ERR_BAD_PAGE);
+  load_tile(tile_begin, 0);
   mt::cp_async_commit();
-  mt::cp_async_wait<0>();
-  __syncthreads();
 
-  // ---- S = Q K^T for this warp's keys
+  // ---- running softmax state of this warp's share of the keys (rows g and g+8 of the 16-row tile)
   const int wkey = warp * kKeysPerWarp;
-  float s[kNT][4];
-#pragma unroll
-  for (int j = 0; j < kNT; j++)
-#pragma unroll
-    for (int e = 0; e < 4; e++) s[j][e] = 0.f;
-#pragma unroll
-  for (int kk = 0; kk < HD / 16; kk++) {
-    uint32_t a[4], b[4];
-    mt::load_a_frag<HD>(q_s, 0, kk, lane, a);
-#pragma unroll
-    for (int pr = 0; pr < kKS; pr++) {
-      mt::load_k_frag<HD>(k_s, wkey + 16 * pr, kk, lane, b);
-      mt::mma_16816(s[2 * pr], a, b[0], b[1]);
-      mt::mma_16816(s[2 * pr + 1], a, b[2], b[3]);
-    }
-  }
-  // ---- mask, softmax statistics (rows g and g+8 of the tile; columns = keys)
-  const int g = lane >> 2, tq = lane & 3;
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float o[HD / 8][4];
 #pragma unroll
-  for (int j = 0; j < kNT; j++)
+  for (int n = 0; n < HD / 8; n++)
 #pragma unroll
-    for (int e = 0; e < 4; e++) {
-      int key = k0 + wkey + 8 * j + 2 * tq + (e & 1);
-      float v = (key >= k_begin && key < k_end) ? s[j][e] * scale_log2e : -INFINITY;
-      s[j][e] = v;
-      m[e >> 1] = fmaxf(m[e >> 1], v);
+    for (int e = 0; e < 4; e++) o[n][e] = 0.f;
+
+  for (int tile = tile_begin; tile < tile_end; tile++) {
+    const int stage = (tile - tile_begin) & 1;
+    const uint32_t k_s = kv_s + stage * 2 * TILE, v_s = k_s + TILE;
+    if (tile + 1 < tile_end) {
+      load_tile(tile + 1, stage ^ 1);
+      mt::cp_async_commit();
+      mt::cp_async_wait<1>();
+    } else {
+      mt::cp_async_wait<0>();
     }
+    __syncthreads();
+    // S = Q K^T for this warp's keys of the tile
+    float s[kNT][4];
 #pragma unroll
-  for (int r = 0; r < 2; r++) {
-    m[r] = fmaxf(m[r], __shfl_xor_sync(0xffffffffu, m[r], 1));
-    m[r] = fmaxf(m[r], __shfl_xor_sync(0xffffffffu, m[r], 2));
-  }
-  const float mu[2] = {m[0] == -INFINITY ? 0.f : m[0], m[1] == -INFINITY ? 0.f : m[1]};
-  uint32_t p[kKS][4];  // A fragments of P, one per 16-key step
+    for (int j = 0; j < kNT; j++)
 #pragma unroll
-  for (int j = 0; j < kNT; j++) {
-    float e0 = exp2f(s[j][0] - mu[0]), e1 = exp2f(s[j][1] - mu[0]), e2 = exp2f(s[j][2] - mu[1]), e3 = exp2f(s[j][3] - mu[1]);
-    l[0] += e0 + e1;
-    l[1] += e2 + e3;
-    p[j >> 1][(j & 1) * 2] = mt::pack_bf16(e0, e1);
-    p[j >> 1][(j & 1) * 2 + 1] = mt::pack_bf16(e2, e3);
+      for (int e = 0; e < 4; e++) s[j][e] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < HD / 16; kk++) {
+      uint32_t a[4], b[4];
+      mt::load_a_frag<HD>(q_s, 0, kk, lane, a);
+#pragma unroll
+      for (int pr = 0; pr < kKS; pr++) {
+        mt::load_k_frag<HD>(k_s, wkey + 16 * pr, kk, lane, b);
+        mt::mma_16816(s[2 * pr], a, b[0], b[1]);
+        mt::mma_16816(s[2 * pr + 1], a, b[2], b[3]);
+      }
+    }
+    // mask, running max
+    float mn[2] = {m[0], m[1]};
+#pragma unroll
+    for (int j = 0; j < kNT; j++)
+#pragma unroll
+      for (int e = 0; e < 4; e++) {
+        int key = tile * kTile + wkey + 8 * j + 2 * tq + (e & 1);
+        float v = (key >= k_begin && key < k_end) ? s[j][e] * scale_log2e : -INFINITY;
+        s[j][e] = v;
+        mn[e >> 1] = fmaxf(mn[e >> 1], v);
+      }
+    float mu[2], corr[2];
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+      mn[r] = fmaxf(mn[r], __shfl_xor_sync(0xffffffffu, mn[r], 1));
+      mn[r] = fmaxf(mn[r], __shfl_xor_sync(0xffffffffu, mn[r], 2));
+      mu[r] = mn[r] == -INFINITY ? 0.f : mn[r];
+      corr[r] = exp2f(m[r] - mu[r]);   // 0 while m is still -inf
+      m[r] = mn[r];
+      l[r] *= corr[r];
+    }
+    if (tile > tile_begin) {
+#pragma unroll
+      for (int n = 0; n < HD / 8; n++) {
+        o[n][0] *= corr[0];
+        o[n][1] *= corr[0];
+        o[n][2] *= corr[1];
+        o[n][3] *= corr[1];
+      }
+    }
+    uint32_t p[kKS][4];  // A fragments of P, one per 16-key step
+#pragma unroll
+    for (int j = 0; j < kNT; j++) {
+      float e0 = exp2f(s[j][0] - mu[0]), e1 = exp2f(s[j][1] - mu[0]), e2 = exp2f(s[j][2] - mu[1]), e3 = exp2f(s[j][3] - mu[1]);
+      l[0] += e0 + e1;
+      l[1] += e2 + e3;
+      p[j >> 1][(j & 1) * 2] = mt::pack_bf16(e0, e1);
+      p[j >> 1][(j & 1) * 2 + 1] = mt::pack_bf16(e2, e3);
+    }
+    // O += P V over this warp's keys
+#pragma unroll
+    for (int ks = 0; ks < kKS; ks++)
+#pragma unroll
+      for (int dp = 0; dp < HD / 16; dp++) {
+        uint32_t b[4];
+        mt::load_v_frag<HD>(v_s, wkey + 16 * ks, dp, lane, b);
+        mt::mma_16816(o[2 * dp], p[ks], b[0], b[1]);
+        mt::mma_16816(o[2 * dp + 1], p[ks], b[2], b[3]);
+      }
+    __syncthreads();  // every warp is done with this stage before it is loaded again
   }
 #pragma unroll
   for (int r = 0; r < 2; r++) {
     l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
     l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
   }
-  // ---- O = P V over this warp's keys
-  float o[HD / 8][4];
-#pragma unroll
-  for (int n = 0; n < HD / 8; n++)
-#pragma unroll
-    for (int e = 0; e < 4; e++) o[n][e] = 0.f;
-#pragma unroll
-  for (int ks = 0; ks < kKS; ks++)
-#pragma unroll
-    for (int dp = 0; dp < HD / 16; dp++) {
-      uint32_t b[4];
-      mt::load_v_frag<HD>(v_s, wkey + 16 * ks, dp, lane, b);
-      mt::mma_16816(o[2 * dp], p[ks], b[0], b[1]);
-      mt::mma_16816(o[2 * dp + 1], p[ks], b[2], b[3]);
-    }
-  // ---- merge the four warps through shared memory (the tiles are no longer needed)
-  __syncthreads();
+  // ---- merge the four warps through shared memory (the tiles are no longer needed); only the
+  // rows that are real heads of the group are stored
   float* ml_s = (float*)smem;                                  // [warps][16][2], in the Q tile
   float* o_s = (float*)(smem + 16 * HD * 2);                   // [warps][16][HD], in the K and V tiles
   if (tq == 0) {
@@ -151,8 +191,8 @@ __global__ void __launch_bounds__(kWarps * 32)
 #pragma unroll
   for (int n = 0; n < HD / 8; n++) {
     int d = 8 * n + 2 * tq;
-    *(float2*)&o_s[(warp * 16 + g) * HD + d] = make_float2(o[n][0], o[n][1]);
-    *(float2*)&o_s[(warp * 16 + g + 8) * HD + d] = make_float2(o[n][2], o[n][3]);
+    if (g < group) *(float2*)&o_s[(warp * 16 + g) * HD + d] = make_float2(o[n][0], o[n][1]);
+    if (g + 8 < group) *(float2*)&o_s[(warp * 16 + g + 8) * HD + d] = make_float2(o[n][2], o[n][3]);
   }
   __syncthreads();
   for (int idx = tid; idx < group * HD; idx += kWarps * 32) {
@@ -180,14 +220,15 @@ __global__ void __launch_bounds__(kWarps * 32)
 // out[token][head] = sum over the slices that hold visible keys of O_s 2^(m_s - M) / sum of l_s 2^(m_s - M)
 template <int HD>
 __global__ void decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, const int* __restrict__ dec_tokens,
-                                      const int* __restrict__ positions, int window, __nv_bfloat16* __restrict__ out, int heads, int max_slices) {
+                                      const int* __restrict__ positions, int window, __nv_bfloat16* __restrict__ out, int heads, int max_slices,
+                                      int slice_keys) {
   ib::pdl_launch_dependents();
   ib::pdl_wait();
   const int h = blockIdx.x, item = blockIdx.y;
   const int t = dec_tokens[item];
   const int pos = positions[t];
   const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-  const int s_begin = lo / kSlice, s_end = pos / kSlice + 1;
+  const int s_begin = lo / slice_keys, s_end = pos / slice_keys + 1;
   const size_t slot0 = ((size_t)item * heads + h) * max_slices;
   float M = -INFINITY;
   for (int s = s_begin; s < s_end; s++) M = fmaxf(M, part_ml[(slot0 + s) * 2]);
@@ -204,9 +245,10 @@ __global__ void decode_combine_kernel(const float* __restrict__ part_o, const fl
 
 template <int HD>
 int launch(const void* q, const IbKvView* kv, const int* dec_tokens, int n_dec, const int* positions, const int* seg_of_token, int window,
-           float scale, float* part_o, float* part_ml, void* out, int heads, int max_slices, unsigned* status, cudaStream_t stream) {
-  constexpr int tiles = (16 + 2 * kSlice) * HD * 2, merge = 16 * HD * 2 + kWarps * 16 * HD * 4;
-  constexpr int smem = tiles > merge ? tiles : merge;
+           float scale, float* part_o, float* part_ml, void* out, int heads, int max_slices, int tiles_per_slice, unsigned* status,
+           cudaStream_t stream) {
+  constexpr int smem = 16 * HD * 2 + 4 * kTile * HD * 2 + 2 * kTile * 8;   // Q, two stages of K and V, key offsets
+  static_assert(kWarps * 16 * HD * 4 <= 4 * kTile * HD * 2, "the merge buffer must fit in the tiles");
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(decode_split_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -215,10 +257,10 @@ int launch(const void* q, const IbKvView* kv, const int* dec_tokens, int n_dec, 
   }
   dim3 grid(kv->kv_heads, n_dec, max_slices);
   ib::launch(decode_split_kernel<HD>, grid, kWarps * 32, smem, stream, (const __nv_bfloat16*)q, *kv, dec_tokens, positions, seg_of_token, window,
-                                                               scale * 1.4426950408889634f, part_o, part_ml, heads, max_slices, status);
+             scale * 1.4426950408889634f, part_o, part_ml, heads, max_slices, tiles_per_slice, status);
   IB_CHECK_LAUNCH("attention_decode split");
   ib::launch(decode_combine_kernel<HD>, dim3(heads, n_dec), HD, 0, stream, part_o, part_ml, dec_tokens, positions, window, (__nv_bfloat16*)out, heads,
-                                                                   max_slices);
+             max_slices, tiles_per_slice * kTile);
   IB_CHECK_LAUNCH("attention_decode combine");
   return 0;
 }
@@ -227,22 +269,27 @@ int launch(const void* q, const IbKvView* kv, const int* dec_tokens, int n_dec, 
 
 // Attention for decoded tokens (one query position each). dec_tokens[i] is the flat row of the i-th
 // decoded token in q/out/positions/seg_of_token. Scratch: part_o float32 [n_dec * heads * max_slices * head_dim],
-// part_ml float32 [n_dec * heads * max_slices * 2]; max_slices * ib_attention_decode_slice() must cover every position in use.
-extern "C" int ib_attention_decode_slice() { return kSlice; }
+// part_ml float32 [n_dec * heads * max_slices * 2]. A CTA handles a slice of tiles_per_slice tiles of
+// ib_attention_decode_tile() keys; max_slices slices must cover every position in use. Slices are cut at
+// multiples of their size, so for a given tiles_per_slice a token's result does not depend on the batch.
+extern "C" int ib_attention_decode_tile() { return kTile; }
 
 extern "C" int ib_attention_decode(const void* q, const IbKvView* kv, const int* dec_tokens, int n_dec, const int* positions,
                                    const int* seg_of_token, int window, float scale, float* part_o, float* part_ml, void* out, int heads,
-                                   int max_slices, unsigned* status, cudaStream_t stream) {
+                                   int max_slices, int tiles_per_slice, unsigned* status, cudaStream_t stream) {
   if (n_dec == 0) return 0;
   IB_CHECK_ARG(kv && kv->base && kv->block_table, "attention_decode: the cache view has a null pointer");
+  IB_CHECK_ARG(tiles_per_slice >= 1 && tiles_per_slice <= 1024, "attention_decode: %d tiles per slice", tiles_per_slice);
   IB_CHECK_ARG(kv->dtype == IB_BF16, "attention_decode: the cache must be bfloat16");
   IB_CHECK_ARG(kv->kv_heads > 0 && heads % kv->kv_heads == 0 && heads / kv->kv_heads <= 16,
                "attention_decode: %d query heads on %d kv heads (groups of up to 16 are supported)", heads, kv->kv_heads);
   IB_CHECK_ARG(n_dec > 0 && n_dec <= 65535 && max_slices > 0 && max_slices <= 65535, "attention_decode: bad sizes n=%d slices=%d", n_dec, max_slices);
   if (kv->head_dim == 128)
-    return launch<128>(q, kv, dec_tokens, n_dec, positions, seg_of_token, window, scale, part_o, part_ml, out, heads, max_slices, status, stream);
+    return launch<128>(q, kv, dec_tokens, n_dec, positions, seg_of_token, window, scale, part_o, part_ml, out, heads, max_slices, tiles_per_slice, status,
+                       stream);
   if (kv->head_dim == 64)
-    return launch<64>(q, kv, dec_tokens, n_dec, positions, seg_of_token, window, scale, part_o, part_ml, out, heads, max_slices, status, stream);
+    return launch<64>(q, kv, dec_tokens, n_dec, positions, seg_of_token, window, scale, part_o, part_ml, out, heads, max_slices, tiles_per_slice, status,
+                      stream);
   return ib_set_error("attention_decode: head_dim %d has no tensor-core kernel (64 and 128 have)", kv->head_dim);
 }
 
@@ -280,7 +327,7 @@ int noalloc_scratch(float** ptr) {
 
 extern "C" int ib_attention_decode_noalloc(const void* q, const IbKvView* kv, const int* dec_tokens, int n_dec, const int* positions,
                                            const int* seg_of_token, int window, float scale, void* out, int heads, int max_slices,
-                                           unsigned* status, cudaStream_t stream) {
+                                           int tiles_per_slice, unsigned* status, cudaStream_t stream) {
   if (n_dec == 0) return 0;
   IB_CHECK_ARG(kv, "attention_decode_noalloc: the cache view is null");
   IB_CHECK_ARG(n_dec > 0 && heads > 0 && max_slices > 0 && kv->head_dim > 0, "attention_decode_noalloc: bad sizes n=%d heads=%d slices=%d", n_dec,
@@ -295,6 +342,6 @@ extern "C" int ib_attention_decode_noalloc(const void* q, const IbKvView* kv, co
   if (noalloc_scratch(&scratch)) return 1;
   float* part_o = scratch;
   float* part_ml = scratch + slots * kv->head_dim;
-  return ib_attention_decode(q, kv, dec_tokens, n_dec, positions, seg_of_token, window, scale, part_o, part_ml, out, heads, max_slices, status,
-                             stream);
+  return ib_attention_decode(q, kv, dec_tokens, n_dec, positions, seg_of_token, window, scale, part_o, part_ml, out, heads, max_slices, tiles_per_slice,
+                             status, stream);
 }

@@ -14,13 +14,24 @@ import torch
 from . import lib as L
 from . import ops
 
-def decode_slice() -> int:
-    """Keys per CTA of the decode kernel (csrc/attention_decode.cu)."""
-    return int(L.load().ib_attention_decode_slice())
+def decode_tile() -> int:
+    """Keys per tile of the decode kernel (csrc/attention_decode.cu); a CTA walks a slice of several tiles."""
+    return int(L.load().ib_attention_decode_tile())
+
+
+def decode_tiles_per_slice(n_dec: int, kv_heads: int, max_keys: int) -> int:
+    """How many tiles one CTA takes: one while the step has few (token, kv head, tile) items, so
+    that every SM gets work; more when there are thousands, so that fewer partial results are
+    written and merged. For a given value a token's result does not depend on the batch."""
+    items = n_dec * kv_heads * -(-max_keys // decode_tile())
+    tps = 1
+    while tps < 8 and items // tps > 1024:
+        tps *= 2
+    return tps
 
 QTILE = 64    # query rows per CTA of the prefill kernel (csrc/attention_prefill.cu)
 
-L.register("ib_attention_decode", [L._p, C.POINTER(L.KvView), L._p, L._i, L._p, L._p, L._i, L._f, L._p, L._p, L._p, L._i, L._i, L._p, L._p])
+L.register("ib_attention_decode", [L._p, C.POINTER(L.KvView), L._p, L._i, L._p, L._p, L._i, L._f, L._p, L._p, L._p, L._i, L._i, L._i, L._p, L._p])
 L.register("ib_attention_prefill", [L._p, C.POINTER(L.KvView), L._p, L._p, L._i, L._p, L._p, L._i, L._f, L._p, L._i, L._p, L._p])
 
 
@@ -65,8 +76,9 @@ def paged_attention(ctx, q: torch.Tensor, cache: ops.KvLayerView, heads: int, wi
     stream = ops._stream()
     if work["n_dec"]:
         limit = view.table_stride * view.page_size
-        slice_ = decode_slice()
-        max_slices = -(-limit // slice_) if work["max_pos"] is None else work["max_pos"] // slice_ + 1
+        max_keys = limit if work["max_pos"] is None else work["max_pos"] + 1
+        tps = decode_tiles_per_slice(work["n_dec"], view.kv_heads, max_keys)
+        max_slices = -(-max_keys // (tps * decode_tile()))
         skey = ("decode_scratch", heads, view.head_dim, max_slices)
         if skey not in ctx.memo:
             n = work["n_dec"] * heads * max_slices
@@ -74,7 +86,7 @@ def paged_attention(ctx, q: torch.Tensor, cache: ops.KvLayerView, heads: int, wi
         part_o, part_ml = ctx.memo[skey]
         L.call("ib_attention_decode", q.data_ptr(), C.byref(view), work["dec_tokens"].data_ptr(), work["n_dec"], ctx.positions.data_ptr(),
                ctx.seg_of_token.data_ptr(), int(window or 0), float(scale), part_o.data_ptr(), part_ml.data_ptr(), out.data_ptr(), heads,
-               max_slices, rt.status.data_ptr(), stream)
+               max_slices, tps, rt.status.data_ptr(), stream)
     if work["n_tiles"]:
         L.call("ib_attention_prefill", q.data_ptr(), C.byref(view), work["tile_seg"].data_ptr(), work["tile_row0"].data_ptr(), work["n_tiles"],
                ctx.seg_start.data_ptr(), ctx.seg_pos0.data_ptr(), int(window or 0), float(scale), out.data_ptr(), heads, rt.status.data_ptr(),

@@ -95,7 +95,7 @@ def build(verbose: bool = True) -> Path:
     if not srcs:
         raise BuildError(f"no CUDA sources under {CSRC}")
     out = build_dir()
-    headers = b"".join(p.read_bytes() for p in sorted(CSRC.glob("*.cuh")))
+    headers = b"".join(p.read_bytes() for p in sorted([*CSRC.glob("*.cuh"), *CSRC.glob("*.h")]))
     flags = " ".join(NVCC_FLAGS).encode()
     keys = {s: _digest([s.read_bytes(), headers, flags]) for s in srcs}
     lib_key = _digest([k.encode() for k in keys.values()])

@@ -216,6 +216,24 @@ def test_attention_tensor_core_kernels(status, hd, heads, kvh, page, window):
     assert (out2.float() - out.float()).abs().max() <= 2e-2 * ref.abs().max()
 
 
+@pytest.mark.parametrize("tiles_per_slice", [1, 2, 8])
+def test_attention_decode_slices_of_several_tiles(status, monkeypatch, tiles_per_slice):
+    """The decode kernel walking 1, 2 or 8 tiles per CTA, windows starting inside a slice included."""
+    from inference_bench_b200.engine.context import Segment, build_context
+    from inference_bench_b200.engine.runtime import Runtime
+    from inference_bench_b200.kernels import attention
+    monkeypatch.setattr(attention, "decode_tiles_per_slice", lambda *a: tiles_per_slice)
+    hd, heads, kvh = 128, 8, 2
+    shapes = [(1000, 1), (64, 1), (65, 1), (513, 1), (1, 1), (2047, 1)]
+    for window in (None, 300):
+        q, view, pos, seg, ref, _ = _attention_case(torch.bfloat16, heads, kvh, hd, 16, window, shapes, 21, needle=True)
+        rt = Runtime(DEV, "bfloat16")
+        ctx = build_context(rt, [Segment(i, i, L - n, [0] * n) for i, (L, n) in enumerate(shapes)])
+        out = attention.paged_attention(ctx, q, view, heads, window, 1 / math.sqrt(hd))
+        rt.check_status()
+        assert (out.cpu().double() - ref).abs().max() <= 1.5e-2 * ref.abs().max()
+
+
 def test_attention_reports_missing_page(status):
     from inference_bench_b200.kernels import ops
     q, view, pos, seg, ref, _ = _attention_case(torch.float32, 2, 1, 16, 8, None, [(30, 1)], 13)
