@@ -87,6 +87,22 @@ class Runtime:
         ops.gemm_simt(x, lw.weight, out[0])
         return out
 
+    def gate_up_act(self, x: torch.Tensor, lw: LinearWeights) -> torch.Tensor:
+        """x [T, K] -> silu(x gate^T) * (x up^T) in the activation dtype, [T, I], for a matrix
+        [2I, K] of gate rows then up rows. Enough bfloat16 tokens run as one tensor-core kernel
+        whose epilogue applies the activation; otherwise the product and the SiLU-mul kernel."""
+        T, inter = x.shape[0], lw.n // 2
+        if self.mode == "bfloat16" and self.gemm != "simt":
+            from ..kernels import gemm_tcgen05
+            if gemm_tcgen05.swiglu_supported(T, lw.k):
+                act = self.empty((T, inter))
+                gemm_tcgen05.gemm_swiglu(x, lw.weight, act, self.status)
+                return act
+        gu = self.linear(x, lw)
+        act = self.empty((T, inter))
+        ops.silu_mul(gu, act)
+        return act
+
     # ---------------------------------------------------------------- status word
     def check_status(self) -> None:
         """Read the status word (synchronises) and raise if a kernel reported a fault."""

@@ -15,40 +15,75 @@ from . import ops
 SM_COUNT = 148
 TOKEN_TILES = (16, 32, 64, 128, 256)
 
-L.register("ib_gemm_tcgen05", [L._p, L._p, L._p, L._i, L._i, L._i, L._i, L._i, L._p, L._p])
+L.register("ib_gemm_tcgen05", [L._p, L._p, L._p, L._i, L._i, L._i, L._i, L._i, L._i, L._p, L._p])
+L.register("ib_gemm_swiglu_tcgen05", [L._p, L._p, L._p, L._i, L._i, L._i, L._i, L._p, L._p])
 
 
 def supports(k: int) -> bool:
     return k % 8 == 0
 
 
-def choose(T: int, N: int, K: int, allow_split: bool = True) -> tuple[int, int]:
-    """(tokens per CTA, k-splits)."""
-    bn = next((b for b in TOKEN_TILES if T <= b), 256)
-    tiles = -(-N // 128) * -(-T // bn)
+# relative speed of the large-tile shapes at equal work, measured on Qwen3-8B layer shapes (2,048 tokens)
+_SHAPE_SPEED = {(256, True): 1.0, (256, False): 0.89, (128, True): 0.87, (128, False): 0.78}
+
+
+def choose(T: int, N: int, K: int, allow_split: bool = True) -> tuple[int, int, bool]:
+    """(tokens per CTA, k-splits, wide). Up to 128 tokens: the smallest token tile that holds them,
+    and the k-range split over CTAs until the GPU is full. More tokens: the 128/256-token tile, 128
+    or 256 rows of W per CTA, whichever needs the least time by waves of CTAs times work per CTA."""
     ktiles = -(-K // 64)
-    splits = 1
-    slots = SM_COUNT * (2 if bn <= 32 else 1)      # CTAs resident at once (two per SM for the small token tiles)
-    if allow_split and tiles < slots:
-        splits = max(1, min(slots // tiles, ktiles // 4, 16))
-        per = -(-ktiles // splits)
-        splits = -(-ktiles // per)  # no empty split
-    return bn, splits
+    if T <= 128:
+        bn = next(b for b in TOKEN_TILES if T <= b)
+        tiles = -(-N // 128)
+        slots = SM_COUNT * (2 if bn <= 32 else 1)      # CTAs resident at once (two per SM for the small token tiles)
+        splits = 1
+        if allow_split and tiles < slots:
+            splits = max(1, min(slots // tiles, ktiles // 4, 16))
+            per = -(-ktiles // splits)
+            splits = -(-ktiles // per)  # no empty split
+        return bn, splits, False
+
+    def cost(shape):
+        bn, wide = shape
+        rows = 256 if wide else 128
+        ctas = -(-N // rows) * -(-T // bn)
+        return -(-ctas // SM_COUNT) * rows * bn / _SHAPE_SPEED[shape]
+    bn, wide = min(_SHAPE_SPEED, key=cost)
+    return bn, 1, wide
 
 
-def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bn: int, splits: int, status: torch.Tensor) -> None:
-    """out [splits, T, N] float32 = per-split partial products of x [T, K] and w [N, K] (bfloat16)."""
+def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bn: int, splits: int, status: torch.Tensor, wide: bool = False) -> None:
+    """out [splits, T, N] float32 = per-split partial products of x [T, K] and w [N, K] (bfloat16).
+    wide: 256 rows of w per CTA instead of 128 (token tiles of 128 or 256 only)."""
     T, K = x.shape
     N = w.shape[0]
     ops._check("x", x, torch.bfloat16)
     ops._check("w", w, torch.bfloat16, (N, K))
     ops._check("out", out, torch.float32, (splits, T, N))
-    L.call("ib_gemm_tcgen05", x.data_ptr(), w.data_ptr(), out.data_ptr(), T, N, K, bn, splits, status.data_ptr(), ops._stream())
+    L.call("ib_gemm_tcgen05", x.data_ptr(), w.data_ptr(), out.data_ptr(), T, N, K, bn, splits, 1 if wide else 0, status.data_ptr(), ops._stream())
 
 
 def linear(rt, x: torch.Tensor, lw, allow_split: bool = True) -> torch.Tensor:
     T = x.shape[0]
-    bn, splits = choose(T, lw.n, lw.k, allow_split)
+    bn, splits, wide = choose(T, lw.n, lw.k, allow_split)
     out = rt.empty((splits, T, lw.n), torch.float32)
-    gemm(x, lw.weight, out, bn, splits, rt.status)
+    gemm(x, lw.weight, out, bn, splits, rt.status, wide)
     return out
+
+
+def swiglu_supported(T: int, k: int) -> bool:
+    """The fused gate/up product takes token tiles of 64 and more; fewer tokens go through the
+    split-K product and the SiLU-mul kernel, which fill the GPU better."""
+    return supports(k) and T > 64
+
+
+def gemm_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tensor, status: torch.Tensor, bn: int | None = None) -> None:
+    """act [T, I] bfloat16 = silu(x gate^T) * (x up^T) with w_gate_up [2I, K] = gate rows then up rows."""
+    T, K = x.shape
+    I = w_gate_up.shape[0] // 2
+    ops._check("x", x, torch.bfloat16)
+    ops._check("w_gate_up", w_gate_up, torch.bfloat16, (2 * I, K))
+    ops._check("act", act, torch.bfloat16, (T, I))
+    if bn is None:
+        bn = 64 if T <= 64 else (128 if T <= 128 else 256)
+    L.call("ib_gemm_swiglu_tcgen05", x.data_ptr(), w_gate_up.data_ptr(), act.data_ptr(), T, I, K, bn, status.data_ptr(), ops._stream())

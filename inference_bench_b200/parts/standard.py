@@ -162,10 +162,7 @@ class SwiGLU(base.FeedForward):
 
     def forward(self, ctx, h):
         rt = ctx.rt
-        gu = rt.linear(h, self.wgu)
-        act = rt.empty((ctx.n_tokens, self.intermediate))
-        ops.silu_mul(gu, act)
-        return rt.linear(act, self.wd)
+        return rt.linear(rt.gate_up_act(h, self.wgu), self.wd)
 
 
 # ------------------------------------------------------------------------------------------ embedding and head

@@ -45,10 +45,11 @@ def test_gemm_tcgen05_bfloat16(status, T, N, K, bn, splits):
     from inference_bench_b200.kernels import gemm_tcgen05 as G
     x = (torch.randn(T, K, generator=_g(3)) * 0.5).to(torch.bfloat16).to(DEV)
     w = (torch.randn(N, K, generator=_g(4)) * 0.5).to(torch.bfloat16).to(DEV)
+    wide = False
     if bn is None:
-        bn, splits = G.choose(T, N, K)
+        bn, splits, wide = G.choose(T, N, K)
     out = torch.full((splits, T, N), float("nan"), device=DEV)
-    G.gemm(x, w, out, bn, splits, status)
+    G.gemm(x, w, out, bn, splits, status, wide)
     ref = x.double() @ w.double().T
     got = out.double().sum(0)
     assert status.item() == 0
@@ -60,12 +61,40 @@ def test_gemm_tcgen05_bfloat16(status, T, N, K, bn, splits):
     assert (got - simt.double()).abs().max() <= 2e-5 * ref.abs().max() + 1e-6
 
 
+@pytest.mark.parametrize("T,N,K,bn", [(130, 300, 72, 128), (300, 520, 264, 256), (700, 1000, 1024, 256)])
+def test_gemm_tcgen05_wide_tile(status, T, N, K, bn):
+    from inference_bench_b200.kernels import gemm_tcgen05 as G
+    x = (torch.randn(T, K, generator=_g(3)) * 0.5).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, K, generator=_g(4)) * 0.5).to(torch.bfloat16).to(DEV)
+    out = torch.full((1, T, N), float("nan"), device=DEV)
+    G.gemm(x, w, out, bn, 1, status, wide=True)
+    ref = x.double() @ w.double().T
+    assert status.item() == 0 and (out[0].double() - ref).abs().max() <= 2e-5 * ref.abs().max() + 1e-6
+
+
+@pytest.mark.parametrize("T,I,K,bn", [(65, 200, 136, 64), (70, 136, 72, 128), (300, 520, 264, 128), (513, 1000, 1024, 256), (2048, 384, 512, None)])
+def test_gemm_swiglu_tcgen05(status, T, I, K, bn):
+    """Gate and up products with the activation in the epilogue, against float64."""
+    from inference_bench_b200.kernels import gemm_tcgen05 as G
+    x = (torch.randn(T, K, generator=_g(5)) * 0.5).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(2 * I, K, generator=_g(6)) * 0.2).to(torch.bfloat16).to(DEV)
+    act = torch.full((T, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    G.gemm_swiglu(x, w, act, status, bn)
+    gu = x.double() @ w.double().T
+    g, u = gu[:, :I], gu[:, I:]
+    ref = g / (1 + torch.exp(-g)) * u
+    assert status.item() == 0
+    assert ((act.double() - ref).abs() <= 2.0 ** -8 * ref.abs() + 1e-5 * ref.abs().max()).all()
+
+
 def test_gemm_tcgen05_refuses_bad_sizes(status):
     from inference_bench_b200.kernels import gemm_tcgen05 as G, lib
     x = torch.zeros(4, 100, dtype=torch.bfloat16, device=DEV)   # K = 100 is no multiple of 8
     w = torch.zeros(8, 100, dtype=torch.bfloat16, device=DEV)
     with pytest.raises(lib.KernelError, match="multiple of 8"):
         G.gemm(x, w, torch.empty(1, 4, 8, device=DEV), 16, 1, status)
+    with pytest.raises(lib.KernelError, match="wide tile"):
+        G.gemm(torch.zeros(4, 64, dtype=torch.bfloat16, device=DEV), torch.zeros(8, 64, dtype=torch.bfloat16, device=DEV), torch.empty(1, 4, 8, device=DEV), 16, 1, status, wide=True)
     assert not G.supports(100)
 
 
