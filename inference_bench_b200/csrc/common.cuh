@@ -29,6 +29,7 @@ int ib_set_error(const char* fmt, ...);
 #define IB_ERR_BAD_PAGE 1u      // a block table entry that a kernel had to use was negative or out of range
 #define IB_ERR_BAD_TOKEN 2u     // a token id outside the vocabulary
 #define IB_ERR_WAIT_TIMEOUT 4u  // a bounded wait on an mbarrier ran out
+#define IB_ERR_INTERNAL 8u      // a kernel found one of its own assumptions broken and did nothing
 
 // Programmatic dependent launch: a kernel may be scheduled while the kernel before it in the stream
 // is still running; it runs its own set-up, and ib::pdl_wait() then blocks until everything earlier

@@ -111,5 +111,6 @@ class Runtime:
             self.status.zero_()
             what = [name for bit, name in ((L.ERR_BAD_PAGE, "a block table entry was missing or out of range"),
                                            (L.ERR_BAD_TOKEN, "a token id was outside the vocabulary"),
-                                           (L.ERR_WAIT_TIMEOUT, "a bounded wait inside a kernel ran out")) if bits & bit]
+                                           (L.ERR_WAIT_TIMEOUT, "a bounded wait inside a kernel ran out"),
+                                           (L.ERR_INTERNAL, "a kernel found one of its own assumptions broken")) if bits & bit]
             raise DeviceStatusError("; ".join(what) or f"status bits {bits}")

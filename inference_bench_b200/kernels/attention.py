@@ -29,10 +29,12 @@ def decode_tiles_per_slice(n_dec: int, kv_heads: int, max_keys: int) -> int:
         tps *= 2
     return tps
 
-QTILE = 64    # query rows per CTA of the prefill kernel (csrc/attention_prefill.cu)
+QTILE = {"tcgen05": 128, "mma": 64}   # query rows per CTA of the prefill kernels (csrc/attention_prefill_tc.cu, attention_prefill.cu)
+PREFILL_KERNEL = "tcgen05"               # which one the engine uses; the other stays as a tested alternative
 
 L.register("ib_attention_decode", [L._p, C.POINTER(L.KvView), L._p, L._i, L._p, L._p, L._i, L._f, L._p, L._p, L._p, L._i, L._i, L._i, L._p, L._p])
 L.register("ib_attention_prefill", [L._p, C.POINTER(L.KvView), L._p, L._p, L._i, L._p, L._p, L._i, L._f, L._p, L._i, L._p, L._p])
+L.register("ib_attention_prefill_tc", [L._p, C.POINTER(L.KvView), L._p, L._p, L._i, L._p, L._p, L._i, L._f, L._p, L._i, L._p, L._p])
 
 
 def has_tensor_core_kernel(dtype: torch.dtype, head_dim: int, heads: int, kv_heads: int) -> bool:
@@ -41,7 +43,8 @@ def has_tensor_core_kernel(dtype: torch.dtype, head_dim: int, heads: int, kv_hea
 
 def _work_lists(ctx):
     """Per step, shared by all layers: flat rows of decoded tokens, and 64-row query tiles of portions."""
-    key = "attention_work"
+    qtile = QTILE[PREFILL_KERNEL]
+    key = ("attention_work", qtile)
     if key in ctx.memo:
         return ctx.memo[key]
     if ctx.fixed_shape:
@@ -51,7 +54,7 @@ def _work_lists(ctx):
         dec = ctx.h_seg_start[:-1][lens == 1].astype(np.int32)
         tile_seg, tile_row0 = [], []
         for s in np.nonzero(lens > 1)[0]:
-            for r in range(0, int(lens[s]), QTILE):
+            for r in range(0, int(lens[s]), qtile):
                 tile_seg.append(s)
                 tile_row0.append(r)
         flat = np.concatenate([dec, np.asarray(tile_seg, np.int32), np.asarray(tile_row0, np.int32)]).astype(np.int32)
@@ -88,7 +91,7 @@ def paged_attention(ctx, q: torch.Tensor, cache: ops.KvLayerView, heads: int, wi
                ctx.seg_of_token.data_ptr(), int(window or 0), float(scale), part_o.data_ptr(), part_ml.data_ptr(), out.data_ptr(), heads,
                max_slices, tps, rt.status.data_ptr(), stream)
     if work["n_tiles"]:
-        L.call("ib_attention_prefill", q.data_ptr(), C.byref(view), work["tile_seg"].data_ptr(), work["tile_row0"].data_ptr(), work["n_tiles"],
+        L.call("ib_attention_prefill_tc" if PREFILL_KERNEL == "tcgen05" else "ib_attention_prefill", q.data_ptr(), C.byref(view), work["tile_seg"].data_ptr(), work["tile_row0"].data_ptr(), work["n_tiles"],
                ctx.seg_start.data_ptr(), ctx.seg_pos0.data_ptr(), int(window or 0), float(scale), out.data_ptr(), heads, rt.status.data_ptr(),
                stream)
     return out

@@ -14,7 +14,7 @@ from . import build as _build
 
 F32, BF16 = 0, 1  # dtype codes of csrc/common.cuh
 
-ERR_BAD_PAGE, ERR_BAD_TOKEN, ERR_WAIT_TIMEOUT = 1, 2, 4
+ERR_BAD_PAGE, ERR_BAD_TOKEN, ERR_WAIT_TIMEOUT, ERR_INTERNAL = 1, 2, 4, 8
 
 
 class KernelLibraryError(RuntimeError):

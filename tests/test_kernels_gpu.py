@@ -222,11 +222,13 @@ def test_attention_generic(status, dtype, window):
 
 @pytest.mark.parametrize("hd,heads,kvh,page", [(128, 8, 2, 16), (64, 5, 1, 32), (128, 16, 1, 16), (64, 4, 4, 8)])
 @pytest.mark.parametrize("window", [None, 100])
-def test_attention_tensor_core_kernels(status, hd, heads, kvh, page, window):
-    """Decode slices and prefill tiles through the engine's dispatch, against the plain reference."""
+@pytest.mark.parametrize("prefill", ["tcgen05", "mma"])
+def test_attention_tensor_core_kernels(status, monkeypatch, hd, heads, kvh, page, window, prefill):
+    """Decode slices and prefill tiles (either prefill kernel) through the engine's dispatch, against the plain reference."""
     from inference_bench_b200.engine.context import Segment, build_context
     from inference_bench_b200.engine.runtime import Runtime
     from inference_bench_b200.kernels import attention
+    monkeypatch.setattr(attention, "PREFILL_KERNEL", prefill)
     shapes = [(300, 300), (500, 70), (1000, 1), (129, 1), (128, 1), (5, 2), (260, 1), (64, 64), (65, 65)]
     q, view, pos, seg, ref, _ = _attention_case(torch.bfloat16, heads, kvh, hd, page, window, shapes, 12, needle=True)
     rt = Runtime(DEV, "bfloat16")
