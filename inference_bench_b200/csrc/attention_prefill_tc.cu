@@ -28,11 +28,20 @@ __device__ __forceinline__ uint32_t blk_offset(int rows, int r, int cc) {  // cc
   return (uint32_t)((cc >> 3) * rows * 128 + r * 128 + (((cc & 7) ^ (r & 7)) << 4));
 }
 
+// 2^x, hardware approximation (relative error about 2^-22); 2^-inf = 0
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 template <int HD>
 struct Smem {
   static constexpr int kQ = BM * HD * 2, kKV = BN * HD * 2, kP = BM * BN * 2;
-  static constexpr int oQ = 0, oK = kQ, oV = kQ + 2 * kKV, oP = kQ + 4 * kKV, oBar = oP + kP;
-  static constexpr int kBytes = oBar + 64;  // barriers and the tmem slot; two CTAs of this size fit one SM
+  static constexpr int oQ = 0, oK = kQ, oV = kQ + 2 * kKV, oP = kQ + 4 * kKV, oBar = oP + kP, oOffs = oBar + 64;
+  // barriers and the tmem slot, then where the keys of three tiles live in the cache (int32, in rows of
+  // head_dim elements; -1 = no such key, -2 = its page is missing); two CTAs of this size fit one SM
+  static constexpr int kBytes = oOffs + 3 * BN * 4;
 };
 
 template <int HD>
@@ -53,6 +62,7 @@ __global__ void __launch_bounds__(kThreads, 2)
   uint64_t* bar_s = (uint64_t*)(sm + SM::oBar);  // [2]
   uint64_t* bar_o = bar_s + 2;
   uint32_t* tmem_slot = (uint32_t*)(bar_o + 1);
+  int* offs = (int*)(sm + SM::oOffs);  // [3][BN]
 
   const int tid = threadIdx.x, warp = tid >> 5;
   ib::pdl_launch_dependents();
@@ -87,19 +97,32 @@ __global__ void __launch_bounds__(kThreads, 2)
   const int kt_begin = key_lo / BN, kt_end = pos_last / BN + 1;
   const int n_kt = kt_end - kt_begin;
 
-  // copies one K or V tile (64 keys) into a swizzled buffer; keys outside [key_lo, pos_last] become zero
-  auto load_kv = [&](uint32_t dst, int kt, long long plane) {
-    for (int idx = tid; idx < BN * CPR; idx += kThreads) {
-      const int r = idx / CPR, cc = idx % CPR;
-      const int key = kt * BN + r;
-      const long long off = (key >= key_lo && key <= pos_last) ? ib::kv_offset(kv, seg, key, kvh) : -2;
-      const uint32_t d = dst + blk_offset(BN, r, cc);
-      if (off >= 0) {
-        mt::cp_async16(d, base + off + plane + cc * 8);
-      } else {
-        if (off == -1) atomicOr(status, IB_ERR_BAD_PAGE);
-        mt::st_shared_zero16(d);
+  // One thread per key looks up where the key lives (once per tile, kept for the K and the V copy).
+  auto find_keys = [&](int kt) {
+    if (tid < BN) {
+      const int key = kt * BN + tid;
+      int o = -1;
+      if (key >= key_lo && key <= pos_last) {
+        const long long off = ib::kv_offset(kv, seg, key, kvh);
+        if (off < 0) atomicOr(status, IB_ERR_BAD_PAGE);
+        o = off < 0 ? -2 : (int)(off / HD);      // elements -> rows of head_dim elements (offsets are whole rows)
       }
+      offs[(kt % 3) * BN + tid] = o;
+    }
+  };
+  // copies one K or V tile (64 keys) into a swizzled buffer; keys outside [key_lo, pos_last] become zero
+  const int my_cc = tid % CPR, my_r0 = tid / CPR;
+  auto load_kv = [&](uint32_t dst, int kt, long long plane) {
+    const int* o = offs + (kt % 3) * BN;
+    const __nv_bfloat16* src = base + plane + my_cc * 8;
+#pragma unroll
+    for (int r = my_r0; r < BN; r += kThreads / CPR) {
+      const int off = o[r];
+      const uint32_t d = dst + blk_offset(BN, r, my_cc);
+      if (off >= 0)
+        mt::cp_async16(d, src + (size_t)off * HD);
+      else
+        mt::st_shared_zero16(d);
     }
   };
 
@@ -112,6 +135,9 @@ __global__ void __launch_bounds__(kThreads, 2)
     else
       mt::st_shared_zero16(d);
   }
+  find_keys(kt_begin);
+  if (n_kt > 1) find_keys(kt_begin + 1);
+  __syncthreads();
   load_kv(k_s, kt_begin, 0);
   load_kv(v_s, kt_begin, kv.v_offset);
   mt::cp_async_commit();
@@ -157,7 +183,11 @@ __global__ void __launch_bounds__(kThreads, 2)
     }
     sm100::tc_fence_after();
     // fetch ahead: K of tile j+2 into the buffer S_j just finished with, V of tile j+1
-    if (j + 2 < n_kt) load_kv(k_s + (j & 1) * SM::kKV, kt + 2, 0);
+    if (j + 2 < n_kt) {
+      find_keys(kt + 2);
+      __syncthreads();
+      load_kv(k_s + (j & 1) * SM::kKV, kt + 2, 0);
+    }
     if (j + 1 < n_kt) load_kv(v_s + ((j + 1) & 1) * SM::kKV, kt + 1, kv.v_offset);
     mt::cp_async_commit();
 
@@ -168,18 +198,18 @@ __global__ void __launch_bounds__(kThreads, 2)
     sm100::tmem_ld_wait();
     const int key0 = kt * BN;
     const bool need_mask = key0 + BN - 1 > pos_first || key0 < key_lo || (window > 0 && key0 <= pos_last - window);
-    float tile_max = -INFINITY;
+    float tile_max = -INFINITY;   // of the raw products; the scale (positive) is applied once below
+    if (need_mask) {
 #pragma unroll
-    for (int c = 0; c < BN; c++) {
-      float v = __uint_as_float(sr[c]) * scale_log2e;
-      if (need_mask) {
+      for (int c = 0; c < BN; c++) {
         const int key = key0 + c;
         const bool live = key <= my_pos && key >= key_lo && (window <= 0 || key > my_pos - window);
-        v = live ? v : -INFINITY;
+        if (!live) sr[c] = 0xff800000u;  // -inf
       }
-      sr[c] = __float_as_uint(v);
-      tile_max = fmaxf(tile_max, v);
     }
+#pragma unroll
+    for (int c = 0; c < BN; c++) tile_max = fmaxf(tile_max, __uint_as_float(sr[c]));
+    tile_max *= scale_log2e;
     // ---- reference maximum: moved only when a row's maximum grew a lot (or at the first tile)
     const bool grow = tile_max > m_ref + kRescaleThreshold || (m_ref == -INFINITY && tile_max > -INFINITY);
     if (j == 0) {
@@ -207,7 +237,8 @@ __global__ void __launch_bounds__(kThreads, 2)
       uint32_t w[4];
 #pragma unroll
       for (int e = 0; e < 4; e++) {
-        const float p0 = exp2f(__uint_as_float(sr[c8 * 8 + 2 * e]) - mu), p1 = exp2f(__uint_as_float(sr[c8 * 8 + 2 * e + 1]) - mu);
+        const float p0 = ex2(fmaf(__uint_as_float(sr[c8 * 8 + 2 * e]), scale_log2e, -mu));
+        const float p1 = ex2(fmaf(__uint_as_float(sr[c8 * 8 + 2 * e + 1]), scale_log2e, -mu));
         l += p0 + p1;
         w[e] = mt::pack_bf16(p0, p1);
       }
