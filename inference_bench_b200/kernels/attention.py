@@ -52,11 +52,12 @@ def _work_lists(ctx):
     else:
         lens = np.diff(ctx.h_seg_start)
         dec = ctx.h_seg_start[:-1][lens == 1].astype(np.int32)
-        tile_seg, tile_row0 = [], []
+        tiles = []   # (last position the tile sees, segment, first row): the tiles with the most keys go first
         for s in np.nonzero(lens > 1)[0]:
             for r in range(0, int(lens[s]), qtile):
-                tile_seg.append(s)
-                tile_row0.append(r)
+                tiles.append((int(ctx.h_seg_pos0[s]) + min(r + qtile, int(lens[s])), int(s), r))
+        tiles.sort(key=lambda t: -t[0])
+        tile_seg, tile_row0 = [t[1] for t in tiles], [t[2] for t in tiles]
         flat = np.concatenate([dec, np.asarray(tile_seg, np.int32), np.asarray(tile_row0, np.int32)]).astype(np.int32)
         dev = torch.from_numpy(flat).pin_memory().to(ctx.rt.device, non_blocking=True) if flat.size else None
         nd, nt = dec.size, len(tile_seg)
