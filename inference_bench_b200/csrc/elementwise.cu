@@ -47,33 +47,74 @@ __global__ void embed_kernel(const W* __restrict__ table, const int* __restrict_
 //   if write_x: x[t] = v
 //   out[r] = w * (v * rsqrt(mean(v^2) + eps))
 // The row lives in dynamic shared memory (H floats) between the two passes.
-template <typename O>
+// VEC = 4 when H is a multiple of 4 (16-byte loads), else 1.
+template <typename O, int VEC>
 __global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, int P, size_t delta_stride,
                                    const float* __restrict__ w, O* __restrict__ out, const int* __restrict__ rows, int H, float eps,
                                    int write_x) {
-  extern __shared__ float row[];
+  extern __shared__ __align__(16) float row[];
   __shared__ float scratch[32];
   ib::pdl_launch_dependents();
   ib::pdl_wait();
-  int r = blockIdx.x;
-  int t = rows ? rows[r] : r;
+  const int r = blockIdx.x;
+  const int t = rows ? rows[r] : r;
   float* xr = x + (size_t)t * H;
+  const float* dr = delta + (size_t)t * H;
   float ss = 0.f;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) {
-    float v = xr[i];
-    if (P > 0) {
-      float d = delta[(size_t)t * H + i];
-      for (int p = 1; p < P; p++) d += delta[p * delta_stride + (size_t)t * H + i];
-      v += d;
-      if (write_x) xr[i] = v;
+  if constexpr (VEC == 4) {
+    for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+      float4 v = *(const float4*)(xr + i);
+      if (P > 0) {
+        float4 d = *(const float4*)(dr + i);
+        int p = 1;
+        for (; p + 3 < P; p += 4) {   // four independent loads in flight, added in order
+          const float4 a = *(const float4*)(dr + p * delta_stride + i), b = *(const float4*)(dr + (p + 1) * delta_stride + i),
+                       c = *(const float4*)(dr + (p + 2) * delta_stride + i), e = *(const float4*)(dr + (p + 3) * delta_stride + i);
+          d.x = (((d.x + a.x) + b.x) + c.x) + e.x;
+          d.y = (((d.y + a.y) + b.y) + c.y) + e.y;
+          d.z = (((d.z + a.z) + b.z) + c.z) + e.z;
+          d.w = (((d.w + a.w) + b.w) + c.w) + e.w;
+        }
+        for (; p < P; p++) {
+          const float4 a = *(const float4*)(dr + p * delta_stride + i);
+          d.x += a.x, d.y += a.y, d.z += a.z, d.w += a.w;
+        }
+        v.x += d.x, v.y += d.y, v.z += d.z, v.w += d.w;
+        if (write_x) *(float4*)(xr + i) = v;
+      }
+      *(float4*)(row + i) = v;
+      ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
     }
-    row[i] = v;
-    ss += v * v;
+  } else {
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+      float v = xr[i];
+      if (P > 0) {
+        float d = dr[i];
+        for (int p = 1; p < P; p++) d += dr[p * delta_stride + i];
+        v += d;
+        if (write_x) xr[i] = v;
+      }
+      row[i] = v;
+      ss += v * v;
+    }
   }
   ss = ib::block_sum(ss, scratch);
-  float inv = rsqrtf(ss / (float)H + eps);
+  const float inv = rsqrtf(ss / (float)H + eps);
   O* o = out + (size_t)r * H;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = ib::from_f32<O>(w[i] * (row[i] * inv));
+  if constexpr (VEC == 4) {
+    for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+      const float4 v = *(const float4*)(row + i), g = *(const float4*)(w + i);
+      const float a = g.x * (v.x * inv), b = g.y * (v.y * inv), c = g.z * (v.z * inv), d = g.w * (v.w * inv);
+      if constexpr (sizeof(O) == 4) {
+        *(float4*)((float*)o + i) = make_float4(a, b, c, d);
+      } else {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+        *(uint2*)((__nv_bfloat16*)o + i) = make_uint2(*(uint32_t*)&lo, *(uint32_t*)&hi);
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = ib::from_f32<O>(w[i] * (row[i] * inv));
+  }
 }
 
 // ---------------------------------------------------------------- rotation tables
@@ -136,15 +177,20 @@ extern "C" int ib_add_rmsnorm(float* x, const float* delta, int P, long long del
   IB_CHECK_ARG(!(rows && write_x), "add_rmsnorm: a gathered call must not write x back");
   size_t smem = (size_t)H * sizeof(float);
   IB_CHECK_ARG(smem <= 200 * 1024, "add_rmsnorm: hidden size %d needs %zu bytes of shared memory, more than 200 KiB", H, smem);
-  int threads = H >= 4096 ? 1024 : (H >= 1024 ? 512 : 256);
+  const bool vec = H % 4 == 0 && ((uintptr_t)x % 16 == 0) && (!delta || (uintptr_t)delta % 16 == 0) && ((uintptr_t)w % 16 == 0) &&
+                   ((uintptr_t)out % 16 == 0) && (delta_stride % 4 == 0);
+  const int per = vec ? 4 : 1;
+  int threads = H / per >= 1024 ? 1024 : (H / per >= 512 ? 512 : (H / per >= 256 ? 256 : 128));
+  auto go = [&](auto kernel, auto* o) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    ib::launch(kernel, n_rows, threads, smem, stream, x, delta, P, (size_t)delta_stride, w, o, rows, H, eps, write_x);
+  };
   if (out_dtype == IB_F32) {
-    if (smem > 48 * 1024) cudaFuncSetAttribute(add_rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    ib::launch(add_rmsnorm_kernel<float>, n_rows, threads, smem, stream, x, delta, P, (size_t)delta_stride, w, (float*)out, rows, H, eps, write_x);
+    if (vec) go(add_rmsnorm_kernel<float, 4>, (float*)out);
+    else go(add_rmsnorm_kernel<float, 1>, (float*)out);
   } else if (out_dtype == IB_BF16) {
-    if (smem > 48 * 1024)
-      cudaFuncSetAttribute(add_rmsnorm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    ib::launch(add_rmsnorm_kernel<__nv_bfloat16>, n_rows, threads, smem, stream, x, delta, P, (size_t)delta_stride, w, (__nv_bfloat16*)out, rows, H,
-                                                                          eps, write_x);
+    if (vec) go(add_rmsnorm_kernel<__nv_bfloat16, 4>, (__nv_bfloat16*)out);
+    else go(add_rmsnorm_kernel<__nv_bfloat16, 1>, (__nv_bfloat16*)out);
   } else {
     return ib_set_error("add_rmsnorm: unknown output dtype %d", out_dtype);
   }

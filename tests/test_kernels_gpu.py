@@ -276,7 +276,7 @@ def test_attention_reports_missing_page(status):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("hd,rot", [(24, 24), (64, 32), (16, 0)])
+@pytest.mark.parametrize("hd,rot", [(24, 24), (64, 32), (16, 0), (64, 64), (128, 128), (128, 0)])
 def test_qk_norm_rope_kv(status, dtype, hd, rot):
     from inference_bench_b200.kernels import ops
     heads, kvh, page, T = 4, 2, 8, 21
