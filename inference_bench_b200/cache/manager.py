@@ -177,9 +177,7 @@ class CacheManager:
         for gi, g in enumerate(self.groups):
             first = self._first_live_page(g, r.length)
             last = -(-new_length // self.page_size)
-            for p in range(first, last):
-                if r.tables[gi][p] >= 0:
-                    continue
+            for p in (np.nonzero(r.tables[gi][first:last] < 0)[0] + first).tolist():
                 page = g.pool.allocate()
                 if page is None:
                     for gj, pj in taken:

@@ -120,15 +120,16 @@ class _DecodeGraph:
         n = len(entries)
         if n < self.rows:
             self._pad_all()
-        for i, e in enumerate(entries):
-            pos = cache.length(e.request)
-            self.h_tokens[i] = e.tokens[0]
-            self.h_pos[i] = pos
-            self.h_pos0[i] = pos
-            self.h_slot[i] = cache.slot(e.request)
-            self.h_params[i] = sampling[i][0].row(sampling[i][1])
-            for g, t in enumerate(self.h_tables):
-                t[i] = cache.table(g, e.request)
+        reqs = [cache._get(e.request) for e in entries]
+        pos = [r.length for r in reqs]
+        self.h_tokens[:n] = [e.tokens[0] for e in entries]
+        self.h_pos[:n] = pos
+        self.h_pos0[:n] = pos
+        self.h_slot[:n] = [r.slot for r in reqs]
+        self.h_params[:n] = [p.row(step) for p, step in sampling]
+        for g, t in enumerate(self.h_tables):
+            for i, r in enumerate(reqs):
+                t[i] = r.tables[g]
 
 
 class GpuExecutor:

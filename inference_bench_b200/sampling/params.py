@@ -3,6 +3,7 @@
 number feed the noise; top_k 0, top_p 1 and min_p 0 switch those filters off."""
 from __future__ import annotations
 
+import functools
 import struct
 from dataclasses import dataclass
 
@@ -32,10 +33,18 @@ class SamplingParams:
     def row(self, step: int) -> tuple[int, int, int, int, int, int]:
         """The six 32-bit words the sampling kernel reads for one row
         (crates/specrt/src/runtime/step.rs:76-85): inv_temp bits, seed, step, top_k, top_p bits, min_p bits."""
-        bits = lambda f: struct.unpack("<i", struct.pack("<f", f))[0]
-        inv_temp = 0.0 if self.greedy else 1.0 / self.temperature
-        wrap = lambda u: struct.unpack("<i", struct.pack("<I", u & 0xFFFFFFFF))[0]
-        return (bits(inv_temp), wrap(self.seed), wrap(step), int(self.top_k), bits(self.top_p), bits(self.min_p))
+        a, b, d, e, f = _fixed_words(self)
+        step &= 0xFFFFFFFF
+        return (a, b, step - (1 << 32) if step >= (1 << 31) else step, d, e, f)
+
+
+@functools.lru_cache(maxsize=4096)
+def _fixed_words(p: SamplingParams) -> tuple[int, int, int, int, int]:
+    """The words of a row that do not change from step to step."""
+    bits = lambda f: struct.unpack("<i", struct.pack("<f", f))[0]
+    wrap = lambda u: struct.unpack("<i", struct.pack("<I", u & 0xFFFFFFFF))[0]
+    inv_temp = 0.0 if p.greedy else 1.0 / p.temperature
+    return (bits(inv_temp), wrap(p.seed), int(p.top_k), bits(p.top_p), bits(p.min_p))
 
 
 GREEDY = SamplingParams()
