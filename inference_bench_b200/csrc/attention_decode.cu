@@ -8,8 +8,12 @@
 // unnormalised (max, sum, O) triple per (token, head, slice). A second kernel merges the slices.
 // Slices are cut at fixed absolute key positions, so a token's result does not depend on the batch.
 // Reference design: crates/kir/src/cuda/attention/decode.rs, combine.rs (split-KV with packed GQA rows).
+#include <cuda.h>
+
 #include "kv_view.cuh"
 #include "mma_tiles.cuh"
+#include "sm100.cuh"
+#include "tma_host.cuh"
 
 namespace {
 
@@ -24,7 +28,7 @@ __global__ void __launch_bounds__(kWarps * 32)
     decode_split_kernel(const __nv_bfloat16* __restrict__ q, IbKvView kv, const int* __restrict__ dec_tokens,
                         const int* __restrict__ positions, const int* __restrict__ seg_of_token, int window, float scale_log2e,
                         float* __restrict__ part_o, float* __restrict__ part_ml, int heads, int max_slices, int tiles_per_slice,
-                        unsigned* __restrict__ status) {
+                        const __grid_constant__ CUtensorMap kv_map, long long view_row0, int use_tma, unsigned* __restrict__ status) {
   constexpr int CPR = HD / 8;              // 16-byte chunks per row
   constexpr int TILE = kTile * HD * 2;     // bytes of one K (or V) tile
   extern __shared__ __align__(128) uint8_t smem[];
@@ -32,6 +36,7 @@ __global__ void __launch_bounds__(kWarps * 32)
   const uint32_t q_s = mt::smem_u32(smem);
   const uint32_t kv_s = q_s + 16 * HD * 2;
   long long* offs = (long long*)(smem + 16 * HD * 2 + 4 * TILE);
+  uint64_t* full = (uint64_t*)(offs + 2 * kTile);   // [2], one per stage, for tiles that TMA brings
 
   ib::pdl_launch_dependents();
   ib::pdl_wait();
@@ -47,9 +52,63 @@ __global__ void __launch_bounds__(kWarps * 32)
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, tq = lane & 3;
   const __nv_bfloat16* base = (const __nv_bfloat16*)kv.base;
+  if (use_tma) {
+    if (tid == 0) {
+      sm100::mbar_init(&full[0], 1);
+      sm100::mbar_init(&full[1], 1);
+      sm100::fence_barrier_init();
+    }
+    __syncthreads();
+  }
 
-  // One thread per key looks its page up; then all threads copy 16-byte chunks.
+  // With TMA (page sizes that divide the tile): one thread sends one box copy per page, plane and
+  // 64-dim block; the cache, seen as a matrix of [all rows, head_dim], is described by kv_map. Pages
+  // that hold no needed key, or that the table does not have, are cleared instead.
+  auto load_tile_tma = [&](int tile, int stage) {
+    const int ps = kv.page_size, pages = kTile / ps;
+    const long long rows_per_page = kv.page_stride / HD, v_rows = kv.v_offset / HD;
+    const uint32_t k_s = kv_s + stage * 2 * TILE, v_s = k_s + TILE;
+    uint32_t bytes = 0;
+    for (int pg = 0; pg < pages; pg++) {
+      const int key0 = tile * kTile + pg * ps;
+      const bool needed = key0 < k_end && key0 + ps > k_begin;
+      const int page = needed ? kv.block_table[(size_t)seg * kv.table_stride + tile * pages + pg] : -1;
+      const bool valid = page >= 0 && page < kv.num_pages;
+      if (needed && !valid && tid == 0) atomicOr(status, IB_ERR_BAD_PAGE);
+      if (valid) {
+        bytes += 2 * ps * HD * 2;
+      } else {
+        for (int idx = tid; idx < ps * CPR; idx += kWarps * 32) {
+          const int row = pg * ps + idx / CPR, c = idx % CPR;
+          mt::st_shared_zero16(k_s + mt::tile_offset<HD, kTile>(row, c));
+          mt::st_shared_zero16(v_s + mt::tile_offset<HD, kTile>(row, c));
+        }
+      }
+    }
+    if (tid == 0) {
+      sm100::mbar_arrive_expect_tx(&full[stage], bytes);
+      for (int pg = 0; pg < pages; pg++) {
+        const int key0 = tile * kTile + pg * ps;
+        if (!(key0 < k_end && key0 + ps > k_begin)) continue;
+        const int page = kv.block_table[(size_t)seg * kv.table_stride + tile * pages + pg];
+        if (page < 0 || page >= kv.num_pages) continue;
+        const long long row = (long long)page * rows_per_page + view_row0 + (long long)kvh * ps;
+#pragma unroll
+        for (int hb = 0; hb < HD / 64; hb++) {
+          uint8_t* dk = smem + 16 * HD * 2 + stage * 2 * TILE + hb * kTile * 128 + pg * ps * 128;
+          sm100::tma_load_2d(dk, &kv_map, hb * 64, (int)row, &full[stage]);
+          sm100::tma_load_2d(dk + TILE, &kv_map, hb * 64, (int)(row + v_rows), &full[stage]);
+        }
+      }
+    }
+  };
+
+  // Without: one thread per key looks its page up; then all threads copy 16-byte chunks.
   auto load_tile = [&](int tile, int stage) {
+    if (use_tma) {
+      load_tile_tma(tile, stage);
+      return;
+    }
     long long* o = offs + stage * kTile;
     if (tid < kTile) {
       int key = tile * kTile + tid;
@@ -62,7 +121,7 @@ __global__ void __launch_bounds__(kWarps * 32)
     for (int idx = tid; idx < kTile * CPR; idx += kWarps * 32) {
       int row = idx / CPR, c = idx % CPR;
       long long off = o[row];
-      uint32_t kd = k_s + mt::tile_offset<HD>(row, c), vd = v_s + mt::tile_offset<HD>(row, c);
+      uint32_t kd = k_s + mt::tile_offset<HD, kTile>(row, c), vd = v_s + mt::tile_offset<HD, kTile>(row, c);
       if (off >= 0) {
         mt::cp_async16(kd, base + off + c * 8);
         mt::cp_async16(vd, base + off + kv.v_offset + c * 8);
@@ -76,7 +135,7 @@ __global__ void __launch_bounds__(kWarps * 32)
   // ---- stage Q (rows = the group's heads, zero rows above) and the first tile
   for (int idx = tid; idx < 16 * CPR; idx += kWarps * 32) {
     int row = idx / CPR, c = idx % CPR;
-    uint32_t dst = q_s + mt::tile_offset<HD>(row, c);
+    uint32_t dst = q_s + mt::tile_offset<HD, 16>(row, c);
     if (row < group)
       mt::cp_async16(dst, q + ((size_t)t * heads + (size_t)kvh * group + row) * HD + c * 8);
     else
@@ -104,6 +163,9 @@ __global__ void __launch_bounds__(kWarps * 32)
     } else {
       mt::cp_async_wait<0>();
     }
+    if (use_tma && !sm100::mbar_wait(&full[stage], ((tile - tile_begin) >> 1) & 1)) {
+      if (lane == 0) atomicOr(status, IB_ERR_WAIT_TIMEOUT);   // the tile never came: its keys count as garbage, the status says so
+    }
     __syncthreads();
     // S = Q K^T for this warp's keys of the tile
     float s[kNT][4];
@@ -114,10 +176,10 @@ __global__ void __launch_bounds__(kWarps * 32)
 #pragma unroll
     for (int kk = 0; kk < HD / 16; kk++) {
       uint32_t a[4], b[4];
-      mt::load_a_frag<HD>(q_s, 0, kk, lane, a);
+      mt::load_a_frag<HD, 16>(q_s, 0, kk, lane, a);
 #pragma unroll
       for (int pr = 0; pr < kKS; pr++) {
-        mt::load_k_frag<HD>(k_s, wkey + 16 * pr, kk, lane, b);
+        mt::load_k_frag<HD, kTile>(k_s, wkey + 16 * pr, kk, lane, b);
         mt::mma_16816(s[2 * pr], a, b[0], b[1]);
         mt::mma_16816(s[2 * pr + 1], a, b[2], b[3]);
       }
@@ -167,7 +229,7 @@ __global__ void __launch_bounds__(kWarps * 32)
 #pragma unroll
       for (int dp = 0; dp < HD / 16; dp++) {
         uint32_t b[4];
-        mt::load_v_frag<HD>(v_s, wkey + 16 * ks, dp, lane, b);
+        mt::load_v_frag<HD, kTile>(v_s, wkey + 16 * ks, dp, lane, b);
         mt::mma_16816(o[2 * dp], p[ks], b[0], b[1]);
         mt::mma_16816(o[2 * dp + 1], p[ks], b[2], b[3]);
       }
@@ -245,9 +307,10 @@ __global__ void decode_combine_kernel(const float* __restrict__ part_o, const fl
 
 template <int HD>
 int launch(const void* q, const IbKvView* kv, const int* dec_tokens, int n_dec, const int* positions, const int* seg_of_token, int window,
-           float scale, float* part_o, float* part_ml, void* out, int heads, int max_slices, int tiles_per_slice, unsigned* status,
-           cudaStream_t stream) {
-  constexpr int smem = 16 * HD * 2 + 4 * kTile * HD * 2 + 2 * kTile * 8;   // Q, two stages of K and V, key offsets
+           float scale, float* part_o, float* part_ml, void* out, int heads, int max_slices, int tiles_per_slice, const CUtensorMap* kv_map,
+           long long view_row0, unsigned* status, cudaStream_t stream) {
+  constexpr int smem = 16 * HD * 2 + 4 * kTile * HD * 2 + 2 * kTile * 8 + 16;   // Q, two stages of K and V, key offsets, two barriers
+  CUtensorMap none = {};
   static_assert(kWarps * 16 * HD * 4 <= 4 * kTile * HD * 2, "the merge buffer must fit in the tiles");
   static bool configured = false;
   if (!configured) {
@@ -257,7 +320,8 @@ int launch(const void* q, const IbKvView* kv, const int* dec_tokens, int n_dec, 
   }
   dim3 grid(kv->kv_heads, n_dec, max_slices);
   ib::launch(decode_split_kernel<HD>, grid, kWarps * 32, smem, stream, (const __nv_bfloat16*)q, *kv, dec_tokens, positions, seg_of_token, window,
-             scale * 1.4426950408889634f, part_o, part_ml, heads, max_slices, tiles_per_slice, status);
+             scale * 1.4426950408889634f, part_o, part_ml, heads, max_slices, tiles_per_slice, kv_map ? *kv_map : none, view_row0,
+             kv_map ? 1 : 0, status);
   IB_CHECK_LAUNCH("attention_decode split");
   ib::launch(decode_combine_kernel<HD>, dim3(heads, n_dec), HD, 0, stream, part_o, part_ml, dec_tokens, positions, window, (__nv_bfloat16*)out, heads,
              max_slices, tiles_per_slice * kTile);
@@ -272,24 +336,50 @@ int launch(const void* q, const IbKvView* kv, const int* dec_tokens, int n_dec, 
 // part_ml float32 [n_dec * heads * max_slices * 2]. A CTA handles a slice of tiles_per_slice tiles of
 // ib_attention_decode_tile() keys; max_slices slices must cover every position in use. Slices are cut at
 // multiples of their size, so for a given tiles_per_slice a token's result does not depend on the batch.
+// kv_map: a tensor map of the view's pool from ib_make_kv_map (then view_row0 = the pool row where this
+// view's keys of page 0, head 0 start), or null to copy keys and values with cp.async.
 extern "C" int ib_attention_decode_tile() { return kTile; }
+
+// Describes a whole cache pool [pages, executions, 2, kv_heads, page_size, head_dim] (bfloat16) to TMA
+// as a matrix of [all rows, head_dim] read in boxes of [page_size rows, 64 columns] with the 128-byte
+// swizzle. `map_out` receives the 128-byte tensor map that the attention entry points take.
+// Returns 1 with a message when the geometry cannot be served (the kernels then copy with cp.async).
+extern "C" int ib_make_kv_map(void* map_out, const void* pool_base, long long total_rows, int head_dim, int page_size) {
+  IB_CHECK_ARG(map_out && pool_base && total_rows > 0, "make_kv_map: null pointer or no rows");
+  IB_CHECK_ARG(head_dim % 64 == 0, "make_kv_map: head_dim %d is not a multiple of 64", head_dim);
+  IB_CHECK_ARG(page_size % 8 == 0 && page_size <= 256, "make_kv_map: page size %d is not a multiple of 8 up to 256", page_size);
+  IB_CHECK_ARG(total_rows < (1ll << 31), "make_kv_map: %lld rows exceed the 32-bit coordinate range", total_rows);
+  tma_host::EncodeTiledFn fn = tma_host::encode_fn();
+  IB_CHECK_ARG(fn, "make_kv_map: the driver has no cuTensorMapEncodeTiled");
+  cuuint64_t dims[2] = {(cuuint64_t)head_dim, (cuuint64_t)total_rows};
+  cuuint64_t strides[1] = {(cuuint64_t)head_dim * 2};
+  cuuint32_t box[2] = {64, (cuuint32_t)page_size};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn((CUtensorMap*)map_out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool_base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  IB_CHECK_ARG(r == CUDA_SUCCESS, "make_kv_map: cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return 0;
+}
 
 extern "C" int ib_attention_decode(const void* q, const IbKvView* kv, const int* dec_tokens, int n_dec, const int* positions,
                                    const int* seg_of_token, int window, float scale, float* part_o, float* part_ml, void* out, int heads,
-                                   int max_slices, int tiles_per_slice, unsigned* status, cudaStream_t stream) {
+                                   int max_slices, int tiles_per_slice, const void* kv_map, long long view_row0, unsigned* status,
+                                   cudaStream_t stream) {
   if (n_dec == 0) return 0;
   IB_CHECK_ARG(kv && kv->base && kv->block_table, "attention_decode: the cache view has a null pointer");
+  IB_CHECK_ARG(!kv_map || (kv->page_size % 8 == 0 && kTile % kv->page_size == 0),
+               "attention_decode: TMA copies need a page size that divides %d and is a multiple of 8, not %d", kTile, kv->page_size);
   IB_CHECK_ARG(tiles_per_slice >= 1 && tiles_per_slice <= 1024, "attention_decode: %d tiles per slice", tiles_per_slice);
   IB_CHECK_ARG(kv->dtype == IB_BF16, "attention_decode: the cache must be bfloat16");
   IB_CHECK_ARG(kv->kv_heads > 0 && heads % kv->kv_heads == 0 && heads / kv->kv_heads <= 16,
                "attention_decode: %d query heads on %d kv heads (groups of up to 16 are supported)", heads, kv->kv_heads);
   IB_CHECK_ARG(n_dec > 0 && n_dec <= 65535 && max_slices > 0 && max_slices <= 65535, "attention_decode: bad sizes n=%d slices=%d", n_dec, max_slices);
   if (kv->head_dim == 128)
-    return launch<128>(q, kv, dec_tokens, n_dec, positions, seg_of_token, window, scale, part_o, part_ml, out, heads, max_slices, tiles_per_slice, status,
-                       stream);
+    return launch<128>(q, kv, dec_tokens, n_dec, positions, seg_of_token, window, scale, part_o, part_ml, out, heads, max_slices, tiles_per_slice,
+                       (const CUtensorMap*)kv_map, view_row0, status, stream);
   if (kv->head_dim == 64)
-    return launch<64>(q, kv, dec_tokens, n_dec, positions, seg_of_token, window, scale, part_o, part_ml, out, heads, max_slices, tiles_per_slice, status,
-                      stream);
+    return launch<64>(q, kv, dec_tokens, n_dec, positions, seg_of_token, window, scale, part_o, part_ml, out, heads, max_slices, tiles_per_slice,
+                      (const CUtensorMap*)kv_map, view_row0, status, stream);
   return ib_set_error("attention_decode: head_dim %d has no tensor-core kernel (64 and 128 have)", kv->head_dim);
 }
 
@@ -327,7 +417,8 @@ int noalloc_scratch(float** ptr) {
 
 extern "C" int ib_attention_decode_noalloc(const void* q, const IbKvView* kv, const int* dec_tokens, int n_dec, const int* positions,
                                            const int* seg_of_token, int window, float scale, void* out, int heads, int max_slices,
-                                           int tiles_per_slice, unsigned* status, cudaStream_t stream) {
+                                           int tiles_per_slice, const void* kv_map, long long view_row0, unsigned* status,
+                                           cudaStream_t stream) {
   if (n_dec == 0) return 0;
   IB_CHECK_ARG(kv, "attention_decode_noalloc: the cache view is null");
   IB_CHECK_ARG(n_dec > 0 && heads > 0 && max_slices > 0 && kv->head_dim > 0, "attention_decode_noalloc: bad sizes n=%d heads=%d slices=%d", n_dec,
@@ -343,5 +434,5 @@ extern "C" int ib_attention_decode_noalloc(const void* q, const IbKvView* kv, co
   float* part_o = scratch;
   float* part_ml = scratch + slots * kv->head_dim;
   return ib_attention_decode(q, kv, dec_tokens, n_dec, positions, seg_of_token, window, scale, part_o, part_ml, out, heads, max_slices, tiles_per_slice,
-                             status, stream);
+                             kv_map, view_row0, status, stream);
 }

@@ -22,7 +22,7 @@ __device__ __forceinline__ void load_kv_tile(uint32_t k_s, uint32_t v_s, const I
     int row = idx / CPR, c = idx % CPR;
     int key = key0 + row;
     long long off = (key >= key_lo && key <= key_hi) ? ib::kv_offset(kv, seg, key, kvh) : -2;
-    uint32_t kd = k_s + mt::tile_offset<HD>(row, c), vd = v_s + mt::tile_offset<HD>(row, c);
+    uint32_t kd = k_s + mt::tile_offset<HD, BN>(row, c), vd = v_s + mt::tile_offset<HD, BN>(row, c);
     if (off >= 0) {
       mt::cp_async16(kd, base + off + c * 8);
       mt::cp_async16(vd, base + off + kv.v_offset + c * 8);
@@ -63,7 +63,7 @@ __global__ void __launch_bounds__(kWarps * 32)
 
   for (int idx = tid; idx < BM * CPR; idx += kWarps * 32) {
     int row = idx / CPR, c = idx % CPR;
-    uint32_t dst = q_s + mt::tile_offset<HD>(row, c);
+    uint32_t dst = q_s + mt::tile_offset<HD, BM>(row, c);
     if (row < rows)
       mt::cp_async16(dst, q + ((size_t)(t0 + row) * heads + h) * HD + c * 8);
     else
@@ -95,7 +95,7 @@ __global__ void __launch_bounds__(kWarps * 32)
     __syncthreads();
     if (kt == kt_begin) {
 #pragma unroll
-      for (int kk = 0; kk < HD / 16; kk++) mt::load_a_frag<HD>(q_s, warp * 16, kk, lane, qa[kk]);
+      for (int kk = 0; kk < HD / 16; kk++) mt::load_a_frag<HD, BM>(q_s, warp * 16, kk, lane, qa[kk]);
     }
     const int key0 = kt * BN;
     // skip tiles wholly outside this warp's rows' sight (after their last position or before their window)
@@ -112,7 +112,7 @@ __global__ void __launch_bounds__(kWarps * 32)
 #pragma unroll
         for (int pr = 0; pr < BN / 16; pr++) {
           uint32_t b[4];
-          mt::load_k_frag<HD>(k_s, 16 * pr, kk, lane, b);
+          mt::load_k_frag<HD, BN>(k_s, 16 * pr, kk, lane, b);
           mt::mma_16816(s[2 * pr], qa[kk], b[0], b[1]);
           mt::mma_16816(s[2 * pr + 1], qa[kk], b[2], b[3]);
         }
@@ -160,7 +160,7 @@ __global__ void __launch_bounds__(kWarps * 32)
 #pragma unroll
         for (int dp = 0; dp < HD / 16; dp++) {
           uint32_t b[4];
-          mt::load_v_frag<HD>(v_s, 16 * ks, dp, lane, b);
+          mt::load_v_frag<HD, BN>(v_s, 16 * ks, dp, lane, b);
           mt::mma_16816(o[2 * dp], p[ks], b[0], b[1]);
           mt::mma_16816(o[2 * dp + 1], p[ks], b[2], b[3]);
         }

@@ -18,6 +18,7 @@
 #include <cuda.h>
 
 #include "sm100.cuh"
+#include "tma_host.cuh"
 
 namespace {
 
@@ -34,7 +35,7 @@ struct Tile {
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = MT * kABytes + kBBytes;
   // few tokens: shallower pipelines so that two CTAs share an SM and more loads are in flight
-  static constexpr int kStages = MT == 2 ? (BN >= 256 ? 3 : 4) : (BN >= 256 ? 4 : (BN >= 128 ? 6 : (BN >= 64 ? 8 : (BN >= 32 ? 5 : 6))));
+  static constexpr int kStages = MT == 2 ? (BN >= 256 ? 3 : 4) : (BN >= 256 ? 4 : (BN >= 128 ? 6 : (BN >= 64 ? 4 : (BN >= 32 ? 5 : 6))));
   static constexpr int kCols = MT * BN;
   static constexpr int kTmemCols = kCols <= 32 ? 32 : (kCols <= 64 ? 64 : (kCols <= 128 ? 128 : (kCols <= 256 ? 256 : 512)));
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
@@ -214,24 +215,10 @@ __global__ void __launch_bounds__(kThreads, 1)
 }
 
 // ---------------------------------------------------------------- host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiledFn)p;
-  }
-  return fn;
-}
-
 // A [rows, K] row-major bfloat16 matrix read in boxes of [box_rows, 64] with the 128-byte swizzle;
 // out-of-range rows and columns read as zero.
 int make_tmap(CUtensorMap* m, const void* ptr, int rows, int K, int box_rows) {
-  EncodeTiledFn fn = encode_fn();
+  tma_host::EncodeTiledFn fn = tma_host::encode_fn();
   IB_CHECK_ARG(fn, "gemm_tcgen05: the driver has no cuTensorMapEncodeTiled");
   cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)K * 2};

@@ -1,9 +1,10 @@
 // Building blocks of the warp-level tensor-core attention kernels: 16-byte asynchronous copies
 // into swizzled shared-memory tiles, ldmatrix fragment loads and the m16n8k16 bfloat16 MMA.
 //
-// A tile is [rows][HD] bfloat16 with rows of HD*2 bytes cut into 16-byte chunks; chunk c of row r
-// is stored at chunk position c ^ (r & 7), which makes both the row-wise stores and the 8x8
-// ldmatrix reads free of bank conflicts.
+// A tile of ROWS rows of HD bfloat16 is stored as HD/64 blocks of [ROWS][64 elements]: rows of 128
+// bytes, the 16-byte chunk c of row r at chunk position c ^ (r & 7). This is the layout a TMA copy
+// with the 128-byte swizzle writes (so tiles may be filled by TMA or by cp.async), and it keeps
+// both row-wise stores and the 8x8 ldmatrix reads free of bank conflicts.
 #pragma once
 #include "common.cuh"
 
@@ -11,9 +12,9 @@ namespace mt {
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
-template <int HD>
-__device__ __forceinline__ uint32_t tile_offset(int row, int chunk) {  // byte offset inside a tile
-  return (uint32_t)(row * HD * 2 + ((chunk ^ (row & 7)) << 4));
+template <int HD, int ROWS>
+__device__ __forceinline__ uint32_t tile_offset(int row, int chunk) {  // byte offset inside a tile; chunk < HD / 8
+  return (uint32_t)((chunk >> 3) * ROWS * 128 + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
 }
 
 __device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void* gmem_src) {
@@ -50,24 +51,24 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 // A fragments of a 16-row tile for k-step kk (16 values of the head dimension).
-template <int HD>
+template <int HD, int ROWS>
 __device__ __forceinline__ void load_a_frag(uint32_t tile, int row0, int kk, int lane, uint32_t (&a)[4]) {
   int row = row0 + (lane & 7) + 8 * ((lane >> 3) & 1);
-  ldmatrix_x4(tile + tile_offset<HD>(row, 2 * kk + (lane >> 4)), a[0], a[1], a[2], a[3]);
+  ldmatrix_x4(tile + tile_offset<HD, ROWS>(row, 2 * kk + (lane >> 4)), a[0], a[1], a[2], a[3]);
 }
 // B fragments of K for the product Q K^T: keys key0..key0+15 (two n-tiles), k-step kk.
 // r0,r1 = b0,b1 of keys key0..+7; r2,r3 = b0,b1 of keys key0+8..+15.
-template <int HD>
+template <int HD, int ROWS>
 __device__ __forceinline__ void load_k_frag(uint32_t tile, int key0, int kk, int lane, uint32_t (&r)[4]) {
   int row = key0 + (lane & 7) + 8 * (lane >> 4);
-  ldmatrix_x4(tile + tile_offset<HD>(row, 2 * kk + ((lane >> 3) & 1)), r[0], r[1], r[2], r[3]);
+  ldmatrix_x4(tile + tile_offset<HD, ROWS>(row, 2 * kk + ((lane >> 3) & 1)), r[0], r[1], r[2], r[3]);
 }
 // B fragments of V for the product P V: keys key0..key0+15 (one k-step), dims 16*dp..16*dp+15 (two n-tiles).
 // r0,r1 = b0,b1 of dims 16dp..+7; r2,r3 = b0,b1 of dims 16dp+8..+15.
-template <int HD>
+template <int HD, int ROWS>
 __device__ __forceinline__ void load_v_frag(uint32_t tile, int key0, int dp, int lane, uint32_t (&r)[4]) {
   int row = key0 + (lane & 7) + 8 * ((lane >> 3) & 1);
-  ldmatrix_x4_trans(tile + tile_offset<HD>(row, 2 * dp + (lane >> 4)), r[0], r[1], r[2], r[3]);
+  ldmatrix_x4_trans(tile + tile_offset<HD, ROWS>(row, 2 * dp + (lane >> 4)), r[0], r[1], r[2], r[3]);
 }
 
 }  // namespace mt

@@ -32,7 +32,9 @@ def decode_tiles_per_slice(n_dec: int, kv_heads: int, max_keys: int) -> int:
 QTILE = {"tcgen05": 128, "mma": 64}   # query rows per CTA of the prefill kernels (csrc/attention_prefill_tc.cu, attention_prefill.cu)
 PREFILL_KERNEL = "tcgen05"               # which one the engine uses; the other stays as a tested alternative
 
-L.register("ib_attention_decode", [L._p, C.POINTER(L.KvView), L._p, L._i, L._p, L._p, L._i, L._f, L._p, L._p, L._p, L._i, L._i, L._i, L._p, L._p])
+L.register("ib_attention_decode", [L._p, C.POINTER(L.KvView), L._p, L._i, L._p, L._p, L._i, L._f, L._p, L._p, L._p, L._i, L._i, L._i, L._p, L._ll, L._p, L._p])
+USE_TMA = False  # decode keys and values by TMA box copies (one thread, one 2 KiB box per page and plane) instead of cp.async by all
+                 # threads: measured slower at page size 16 (3.86 against 3.71 ms per step at batch 8), so off; kept and tested
 L.register("ib_attention_prefill", [L._p, C.POINTER(L.KvView), L._p, L._p, L._i, L._p, L._p, L._i, L._f, L._p, L._i, L._p, L._p])
 L.register("ib_attention_prefill_tc", [L._p, C.POINTER(L.KvView), L._p, L._p, L._i, L._p, L._p, L._i, L._f, L._p, L._i, L._p, L._p])
 
@@ -88,9 +90,10 @@ def paged_attention(ctx, q: torch.Tensor, cache: ops.KvLayerView, heads: int, wi
             n = work["n_dec"] * heads * max_slices
             ctx.memo[skey] = (rt.empty((n * view.head_dim,), torch.float32), rt.empty((n * 2,), torch.float32))
         part_o, part_ml = ctx.memo[skey]
+        kv_map, row0 = cache.tma() if USE_TMA else (None, 0)
         L.call("ib_attention_decode", q.data_ptr(), C.byref(view), work["dec_tokens"].data_ptr(), work["n_dec"], ctx.positions.data_ptr(),
                ctx.seg_of_token.data_ptr(), int(window or 0), float(scale), part_o.data_ptr(), part_ml.data_ptr(), out.data_ptr(), heads,
-               max_slices, tps, rt.status.data_ptr(), stream)
+               max_slices, tps, kv_map, row0, rt.status.data_ptr(), stream)
     if work["n_tiles"]:
         L.call("ib_attention_prefill_tc" if PREFILL_KERNEL == "tcgen05" else "ib_attention_prefill", q.data_ptr(), C.byref(view), work["tile_seg"].data_ptr(), work["tile_row0"].data_ptr(), work["n_tiles"],
                ctx.seg_start.data_ptr(), ctx.seg_pos0.data_ptr(), int(window or 0), float(scale), out.data_ptr(), heads, rt.status.data_ptr(),

@@ -35,7 +35,7 @@ def choose(T: int, N: int, K: int, allow_split: bool = True) -> tuple[int, int, 
     if T <= 128:
         bn = next(b for b in TOKEN_TILES if T <= b)
         tiles = -(-N // 128)
-        slots = SM_COUNT * (2 if bn <= 32 else 1)      # CTAs resident at once (two per SM for the small token tiles)
+        slots = SM_COUNT * (2 if bn <= 64 else 1)      # CTAs resident at once (two per SM for the small token tiles)
         splits = 1
         if allow_split and tiles < slots:
             splits = max(1, min(slots // tiles, ktiles // 4, 16))

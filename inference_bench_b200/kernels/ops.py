@@ -41,12 +41,40 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+_KV_MAPS: dict = {}   # (pool address, shape) -> (buffer that owns the bytes, aligned address of the 128-byte tensor map) or None
+
+
+def kv_tensor_map(pool: torch.Tensor):
+    """The TMA description of a bfloat16 cache pool, made once per pool; None when the geometry
+    cannot be served by TMA (the attention kernels then copy with cp.async)."""
+    key = (pool.data_ptr(), tuple(pool.shape), pool.dtype)
+    if key not in _KV_MAPS:
+        pages, entries, two, kv_heads, page_size, head_dim = pool.shape
+        made = None
+        if pool.dtype == torch.bfloat16 and head_dim % 64 == 0 and page_size % 8 == 0 and page_size <= 64 and 64 % page_size == 0:
+            buf = C.create_string_buffer(128 + 64)
+            addr = (C.addressof(buf) + 63) & ~63
+            lib = L.load()
+            lib.ib_make_kv_map.argtypes = [C.c_void_p, C.c_void_p, C.c_longlong, C.c_int, C.c_int]
+            lib.ib_make_kv_map.restype = C.c_int
+            if lib.ib_make_kv_map(addr, pool.data_ptr(), pages * entries * two * kv_heads * page_size, head_dim, page_size) == 0:
+                made = (buf, addr)
+        _KV_MAPS[key] = made
+    return _KV_MAPS[key]
+
+
 @dataclass
 class KvLayerView:
     """One layer's keys and values inside a paged pool, plus the block table of the step."""
     pool: torch.Tensor          # [pages, entries, 2, kv_heads, page_size, head_dim]
     entry: int
     block_table: torch.Tensor   # int32 [segments, table_stride]
+
+    def tma(self) -> tuple[Optional[int], int]:
+        """(address of the pool's tensor map or None, pool row where this view's keys of page 0, head 0 start)."""
+        m = kv_tensor_map(self.pool)
+        _, _, _, kv_heads, page_size, _ = self.pool.shape
+        return (m[1] if m else None), self.entry * 2 * kv_heads * page_size
 
     def c_view(self) -> L.KvView:
         pages, entries, two, kv_heads, page_size, head_dim = self.pool.shape

@@ -248,16 +248,20 @@ def test_attention_tensor_core_kernels(status, monkeypatch, hd, heads, kvh, page
 
 
 @pytest.mark.parametrize("tiles_per_slice", [1, 2, 8])
-def test_attention_decode_slices_of_several_tiles(status, monkeypatch, tiles_per_slice):
-    """The decode kernel walking 1, 2 or 8 tiles per CTA, windows starting inside a slice included."""
+@pytest.mark.parametrize("tma,page,hd", [(True, 16, 128), (True, 64, 64), (True, 8, 128), (False, 16, 128), (False, 24, 64)])
+def test_attention_decode_slices_of_several_tiles(status, monkeypatch, tiles_per_slice, tma, page, hd):
+    """The decode kernel walking 1, 2 or 8 tiles per CTA, windows starting inside a slice included,
+    with keys and values brought by TMA or by cp.async (a page size of 24 can only go the second way)."""
     from inference_bench_b200.engine.context import Segment, build_context
     from inference_bench_b200.engine.runtime import Runtime
     from inference_bench_b200.kernels import attention
     monkeypatch.setattr(attention, "decode_tiles_per_slice", lambda *a: tiles_per_slice)
-    hd, heads, kvh = 128, 8, 2
+    monkeypatch.setattr(attention, "USE_TMA", tma)
+    heads, kvh = 8, 2
     shapes = [(1000, 1), (64, 1), (65, 1), (513, 1), (1, 1), (2047, 1)]
     for window in (None, 300):
-        q, view, pos, seg, ref, _ = _attention_case(torch.bfloat16, heads, kvh, hd, 16, window, shapes, 21, needle=True)
+        q, view, pos, seg, ref, _ = _attention_case(torch.bfloat16, heads, kvh, hd, page, window, shapes, 21, needle=True)
+        assert (view.tma()[0] is not None) == (page != 24)
         rt = Runtime(DEV, "bfloat16")
         ctx = build_context(rt, [Segment(i, i, L - n, [0] * n) for i, (L, n) in enumerate(shapes)])
         out = attention.paged_attention(ctx, q, view, heads, window, 1 / math.sqrt(hd))

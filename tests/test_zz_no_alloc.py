@@ -48,11 +48,11 @@ def test_no_alloc_entry_point_matches_the_ordinary_one():
     fn = lib.ib_attention_decode_noalloc
     fn.restype = C.c_int
     fn.argtypes = [C.c_void_p, C.POINTER(L.KvView), C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_float, C.c_void_p, C.c_int, C.c_int,
-                   C.c_int, C.c_void_p, C.c_void_p]
+                   C.c_int, C.c_void_p, C.c_longlong, C.c_void_p, C.c_void_p]
     ref_fn = lib.ib_attention_decode
     ref_fn.restype = C.c_int
     ref_fn.argtypes = [C.c_void_p, C.POINTER(L.KvView), C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_float, C.c_void_p, C.c_void_p,
-                       C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
+                       C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_longlong, C.c_void_p, C.c_void_p]
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
     TILE = lib.ib_attention_decode_tile()
     stream = torch.cuda.current_stream().cuda_stream
@@ -66,13 +66,14 @@ def test_no_alloc_entry_point_matches_the_ordinary_one():
         part_ml = torch.empty(n * heads * max_slices * 2, device=DEV)
         want = torch.empty_like(q)
         rc = ref_fn(q.data_ptr(), C.byref(cview), seg.data_ptr(), n, positions.data_ptr(), seg.data_ptr(), window, scale, part_o.data_ptr(),
-                    part_ml.data_ptr(), want.data_ptr(), heads, max_slices, tps, status.data_ptr(), stream)
+                    part_ml.data_ptr(), want.data_ptr(), heads, max_slices, tps, None, 0, status.data_ptr(), stream)
         assert rc == 0, lib.ib_last_error()
+        kv_map, row0 = view.tma()   # the second call brings keys and values by TMA, the first by cp.async
         for call in range(2):
             got = torch.full_like(q, float("nan"))
             before = torch.cuda.memory_allocated(DEV)
             rc = fn(q.data_ptr(), C.byref(cview), seg.data_ptr(), n, positions.data_ptr(), seg.data_ptr(), window, scale, got.data_ptr(), heads,
-                    max_slices, tps, status.data_ptr(), stream)
+                    max_slices, tps, kv_map if call else None, row0, status.data_ptr(), stream)
             assert rc == 0, lib.ib_last_error()
             torch.cuda.synchronize()
             assert torch.cuda.memory_allocated(DEV) == before
@@ -85,7 +86,7 @@ def test_no_alloc_entry_point_matches_the_ordinary_one():
     out = torch.zeros_like(q)
     too_many = MAX_FLOATS // (8 * 32 * 130) + 1
     rc = fn(q.data_ptr(), C.byref(cview), seg.data_ptr(), 8, positions.data_ptr(), seg.data_ptr(), 0, 0.1, out.data_ptr(), 32, too_many,
-            1, status.data_ptr(), stream)
+            1, None, 0, status.data_ptr(), stream)
     torch.cuda.synchronize()
     assert rc != 0 and b"more than the fixed scratch" in lib.ib_last_error()
     assert out.abs().max().item() == 0
