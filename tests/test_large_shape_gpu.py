@@ -1,0 +1,37 @@
+"""Two layers at Qwen3-8B layer sizes (random weights made on the device): the bfloat16 path with
+its tensor-core kernels against the true 32-bit path of the same weights, whole prompt and decode."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+QWEN3_8B_2L = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=151936, hidden_size=4096, intermediate_size=12288,
+    num_hidden_layers=2, num_attention_heads=32, num_key_value_heads=8, head_dim=128, rms_norm_eps=1e-6, rope_theta=1000000.0,
+    tie_word_embeddings=False, max_position_embeddings=40960, hidden_act="silu", attention_bias=False, torch_dtype="bfloat16")
+
+
+def test_bfloat16_against_float32_at_8b_layer_sizes():
+    from inference_bench_b200 import Engine
+    from inference_bench_b200.engine.step import StepEntry
+    rng = np.random.default_rng(0)
+    prompt = rng.integers(0, 151936, 300).tolist()
+    logits = {}
+    for dtype in ("float32", "bfloat16"):
+        eng = Engine(QWEN3_8B_2L, dtype=dtype, max_ctx=512, page_size=16, num_pages=64, max_num_seqs=2, random_weights_seed=0)
+        eng.cache.admit("r")
+        rows = [eng.runner.step([StepEntry("r", prompt[:257], [0, 100, 256])]).cpu()]         # a portion that crosses query tiles
+        rows.append(eng.runner.step([StepEntry("r", prompt[257:299], [41])]).cpu())              # a second portion
+        rows.append(eng.runner.step([StepEntry("r", prompt[299:], [0])]).cpu())                  # one decoded token
+        logits[dtype] = torch.cat(rows)
+        eng.cache.release("r")
+        del eng
+        torch.cuda.empty_cache()
+    ref, got = logits["float32"], logits["bfloat16"]
+    assert torch.isfinite(got).all()
+    err = (got - ref).abs().max().item() / ref.abs().max().item()
+    assert err <= 3e-2, f"bfloat16 differs from float32 by {err:.3e} of max|logit|"
+    print(f"8B layer sizes, 2 layers: bfloat16 vs float32 worst {err:.3e} of max|logit|")
