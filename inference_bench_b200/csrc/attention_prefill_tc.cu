@@ -125,15 +125,22 @@ __global__ void __launch_bounds__(kThreads, 2)
   const int n_kt = kt_end - kt_begin;
 
   // One thread per key looks up where the key lives (once per tile, kept for the K and the V copy).
-  auto find_keys = [&](int kt) {
+  // The lookup reads the block table from memory, so it is started one tile before its result is
+  // needed: look_up() returns the row in a register, post() puts it into shared memory a tile later.
+  auto look_up = [&](int kt) -> int {
+    int o = -1;
     if (tid < BN) {
       const int key = kt * BN + tid;
-      int o = -1;
       if (key >= key_lo && key <= pos_last) {
         const long long off = ib::kv_offset(kv, seg, key, kvh);
-        if (off < 0) atomicOr(status, IB_ERR_BAD_PAGE);
         o = off < 0 ? -2 : (int)(off / HD);      // elements -> rows of head_dim elements (offsets are whole rows)
       }
+    }
+    return o;
+  };
+  auto post = [&](int kt, int o) {
+    if (tid < BN) {
+      if (o == -2) atomicOr(status, IB_ERR_BAD_PAGE);
       offs[(kt & 1) * BN + tid] = o;
     }
   };
@@ -162,8 +169,9 @@ __global__ void __launch_bounds__(kThreads, 2)
     else
       mt::st_shared_zero16(d);
   }
-  find_keys(kt_begin);
-  if (n_kt > 1) find_keys(kt_begin + 1);
+  post(kt_begin, look_up(kt_begin));
+  if (n_kt > 1) post(kt_begin + 1, look_up(kt_begin + 1));
+  int next_rows = n_kt > 2 ? look_up(kt_begin + 2) : -1;   // of tile 2, posted when tile 0 is processed
   __syncthreads();
   load_kv(k_s, kt_begin, 0);
   load_kv(v_s, kt_begin, kv.v_offset);
@@ -211,7 +219,8 @@ __global__ void __launch_bounds__(kThreads, 2)
       break;
     }
     sm100::tc_fence_after();
-    if (j + 2 < n_kt) find_keys(kt + 2);
+    if (j + 2 < n_kt) post(kt + 2, next_rows);
+    if (j + 3 < n_kt) next_rows = look_up(kt + 3);
     mt::cp_async_wait<1>();                                 // K of tile j+1 has landed (all but the newest group, a V)
     sm100::fence_proxy_async();
     sm100::tc_fence_before();
