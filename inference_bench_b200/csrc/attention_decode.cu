@@ -31,15 +31,21 @@ __global__ void __launch_bounds__(kWarps * 32)
                         const __grid_constant__ CUtensorMap kv_map, long long view_row0, int use_tma, unsigned* __restrict__ status) {
   constexpr int CPR = HD / 8;              // 16-byte chunks per row
   constexpr int TILE = kTile * HD * 2;     // bytes of one K (or V) tile
-  extern __shared__ __align__(128) uint8_t smem[];
+  // no static shared memory in this kernel: the tiles must start 1024-byte aligned for TMA's swizzle
+  extern __shared__ __align__(1024) uint8_t smem[];
   // layout: Q tile [16][HD] | 2 stages x (K tile, V tile) | key offsets [2][kTile]; the merge buffers reuse the tiles
   const uint32_t q_s = mt::smem_u32(smem);
   const uint32_t kv_s = q_s + 16 * HD * 2;
   long long* offs = (long long*)(smem + 16 * HD * 2 + 4 * TILE);
   uint64_t* full = (uint64_t*)(offs + 2 * kTile);   // [2], one per stage, for tiles that TMA brings
 
+  // What the kernel before this one in the stream writes is q and the key and value of each token's
+  // own position; the index arrays, the block table and every older key and value were complete
+  // before the step began. So the first tile of older keys is requested before the dependency
+  // wait (it then travels while the kernel before still runs); q and the row of the token's own
+  // position are fetched after it.
   ib::pdl_launch_dependents();
-  ib::pdl_wait();
+  if (use_tma) ib::pdl_wait();
   const int kvh = blockIdx.x, item = blockIdx.y, slice = blockIdx.z;
   const int t = dec_tokens[item];
   const int pos = positions[t], seg = seg_of_token[t];
@@ -104,7 +110,8 @@ __global__ void __launch_bounds__(kWarps * 32)
   };
 
   // Without: one thread per key looks its page up; then all threads copy 16-byte chunks.
-  auto load_tile = [&](int tile, int stage) {
+  // `own_later`: leave out the row of the token's own position (it is not written yet); it is fetched after the wait.
+  auto load_tile = [&](int tile, int stage, bool own_later = false) {
     if (use_tma) {
       load_tile_tma(tile, stage);
       return;
@@ -121,6 +128,7 @@ __global__ void __launch_bounds__(kWarps * 32)
     for (int idx = tid; idx < kTile * CPR; idx += kWarps * 32) {
       int row = idx / CPR, c = idx % CPR;
       long long off = o[row];
+      if (own_later && tile * kTile + row == pos) continue;
       uint32_t kd = k_s + mt::tile_offset<HD, kTile>(row, c), vd = v_s + mt::tile_offset<HD, kTile>(row, c);
       if (off >= 0) {
         mt::cp_async16(kd, base + off + c * 8);
@@ -132,7 +140,24 @@ __global__ void __launch_bounds__(kWarps * 32)
     }
   };
 
-  // ---- stage Q (rows = the group's heads, zero rows above) and the first tile
+  // ---- the first tile of older keys, then (after the dependency wait) Q and the token's own row
+  load_tile(tile_begin, 0, true);
+  if (!use_tma) ib::pdl_wait();
+  if (!use_tma && pos / kTile == tile_begin && pos >= k_begin && pos < k_end) {
+    const long long off = offs[pos % kTile];
+    const int row = pos % kTile;
+    for (int c = tid; c < CPR; c += kWarps * 32) {
+      const uint32_t kd = kv_s + mt::tile_offset<HD, kTile>(row, c), vd = kd + TILE;
+      if (off >= 0) {
+        mt::cp_async16(kd, base + off + c * 8);
+        mt::cp_async16(vd, base + off + kv.v_offset + c * 8);
+      } else {
+        mt::st_shared_zero16(kd);
+        mt::st_shared_zero16(vd);
+      }
+    }
+  }
+  // Q: rows = the group's heads, zero rows above
   for (int idx = tid; idx < 16 * CPR; idx += kWarps * 32) {
     int row = idx / CPR, c = idx % CPR;
     uint32_t dst = q_s + mt::tile_offset<HD, 16>(row, c);
@@ -141,7 +166,6 @@ __global__ void __launch_bounds__(kWarps * 32)
     else
       mt::st_shared_zero16(dst);
   }
-  load_tile(tile_begin, 0);
   mt::cp_async_commit();
 
   // ---- running softmax state of this warp's share of the keys (rows g and g+8 of the 16-row tile)

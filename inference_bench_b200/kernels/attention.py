@@ -24,7 +24,7 @@ def decode_tiles_per_slice(n_dec: int, kv_heads: int, max_keys: int) -> int:
     that every SM gets work; more when there are thousands, so that fewer partial results are
     written and merged. For a given value a token's result does not depend on the batch."""
     items = n_dec * kv_heads * -(-max_keys // decode_tile())
-    tps = 1
+    tps = 2 if max_keys > 2 * decode_tile() else 1      # two tiles: the second is fetched while the first is used
     while tps < 8 and items // tps > 1024:
         tps *= 2
     return tps
