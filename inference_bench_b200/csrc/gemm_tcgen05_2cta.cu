@@ -1,0 +1,333 @@
+// The large-tile matrix product on CTA pairs: out[t][n] = sum_k x[t][k] * w[n][k], bfloat16 operands,
+// float32 accumulation, for prompts (256 tokens per tile; 128 with the SwiGLU epilogue).
+//
+// Two CTAs of a cluster (two neighbouring SMs) work on one 256 (rows of W) x 256 (tokens) tile with
+// tcgen05.mma.cta_group::2: each CTA loads its own 128 rows of W and its own 128 of the 256 tokens,
+// the MMA reads both halves of the token tile from the two SMs' shared memory, and each CTA's
+// tensor memory receives the 128 x 256 block of its rows. Per FLOP this moves half the token-tile
+// bytes of the single-CTA kernel, which is what limits that one. With two accumulators per CTA
+// (gate rows and up rows of a SwiGLU feed-forward) the epilogue writes silu(gate) * up directly.
+//
+// Roles per CTA: warp 0 issues its TMA loads (completion is counted on the leader CTA's barrier),
+// warp 1 of the leader CTA issues the MMAs for the pair and signals both CTAs' barriers, warps 2-5
+// store this CTA's accumulator rows. No load uses cluster multicast. Every wait is bounded.
+// The reference's equivalent is its mma.sync tile kernel (crates/kir/src/cuda/gemm/core.rs:14-155).
+#include <cuda.h>
+
+#include "sm100.cuh"
+#include "tma_host.cuh"
+
+namespace {
+
+constexpr int BM = 128;      // rows of W per CTA (256 per pair)
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int kThreads = 192;
+constexpr int EPI_STORE = 0, EPI_SWIGLU = 1;
+constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;   // clears the bit that tells the two CTAs of a pair apart in a shared::cluster address
+
+// BN: tokens per tile = accumulator columns (each CTA loads half of them)
+template <int MT, int BN>
+struct Tile {
+  static constexpr int kABytes = BM * BK * 2, kBBytes = (BN / 2) * BK * 2;
+  static constexpr int kStageBytes = MT * kABytes + kBBytes;
+  static constexpr int kStages = (200 * 1024) / kStageBytes;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+  static constexpr int kAccSets = 512 / (MT * BN);   // accumulator sets that fit tensor memory
+};
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_alloc2(uint32_t* slot, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sm100::smem_u32(slot)), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish2() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc2(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+// TMA tile load whose completion bytes are counted on the barrier at the same offset in the pair's leader CTA.
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* m, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+          sm100::smem_u32(smem_dst)),
+      "l"(m), "r"(x), "r"(y), "r"(sm100::smem_u32(bar) & kPeerBitMask)
+      : "memory");
+}
+__device__ __forceinline__ void mma_bf16_ss_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive on the barrier at this offset in both CTAs of the pair once the MMAs issued so far are done.
+__device__ __forceinline__ void mma_commit_pair(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(sm100::smem_u32(bar)),
+               "h"((uint16_t)3)
+               : "memory");
+}
+
+// Arrive on the barrier at this offset in the pair's leader CTA (from either CTA).
+__device__ __forceinline__ void arrive_on_leader(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(sm100::smem_u32(bar) & kPeerBitMask) : "memory");
+}
+
+// Persistent: each CTA pair walks tiles pair, pair + n_pairs, ... (token tiles vary fastest, so the
+// pairs that work at the same time share rows of W). The TMA warps run ahead into the next tile
+// while the accumulator of the last one is stored; with one accumulator per tile (MT = 1) tensor
+// memory holds two of them, so the next tile's MMAs also run during that store.
+template <int MT, int EPI, int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+    gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, void* __restrict__ out_, int T, int N,
+                     int K, int token_tiles, int total_tiles, int second_off, unsigned* __restrict__ status) {
+  using TL = Tile<MT, BN>;
+  constexpr int STAGES = TL::kStages;
+  constexpr int BNH = BN / 2;
+  constexpr int NBUF = TL::kAccSets >= 2 ? 2 : 1;   // accumulator sets in use
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = sm100::smem_u32(smem_raw);
+  uint8_t* tiles = smem_raw + (((raw + 1023u) & ~1023u) - raw);   // the same offset in both CTAs: same kernel, same launch
+  uint64_t* full = (uint64_t*)(tiles + STAGES * TL::kStageBytes);
+  uint64_t* empty = full + STAGES;
+  uint64_t* acc_full = empty + STAGES;   // [NBUF]
+  uint64_t* acc_empty = acc_full + 2;    // [NBUF], used in the leader CTA
+  uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_rank();          // 0 = leader
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const int nkt = (K + BK - 1) / BK;
+  constexpr int kColsPerPair = EPI == EPI_SWIGLU ? 2 * BM : 2 * BM * MT;
+
+  ib::pdl_launch_dependents();
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; s++) {
+      sm100::mbar_init(&full[s], 1);
+      sm100::mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; b++) {
+      sm100::mbar_init(&acc_full[b], 1);
+      sm100::mbar_init(&acc_empty[b], 8);   // four epilogue warps in each of the two CTAs
+    }
+    sm100::fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc2(tmem_slot, 512);
+    tmem_relinquish2();
+  }
+  sm100::tc_fence_before();
+  __syncthreads();
+  cluster_sync();   // both CTAs' barriers exist before either signals the other's
+  sm100::tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  // W rows of accumulator m of this CTA for the pair's row block rb: plain tiles stack 256-row pairs;
+  // SwiGLU takes gate rows and, second_off on, up rows
+  auto w_row = [&](int rb, int m) {
+    const int n_pair = rb * kColsPerPair;
+    return EPI == EPI_SWIGLU ? n_pair + (int)rank * BM + m * second_off : n_pair + m * 2 * BM + (int)rank * BM;
+  };
+
+  if (warp == 0) {
+    if (sm100::elect_one()) {
+      sm100::prefetch_tensormap(&tmap_w);
+      sm100::prefetch_tensormap(&tmap_x);
+      bool waited = false, ok = true;
+      int it = 0;   // k-tiles sent so far, over all tiles: stage = it % STAGES
+      for (int tile = pair; tile < total_tiles && ok; tile += n_pairs) {
+        const int t0 = (tile % token_tiles) * BN, rb = tile / token_tiles;
+        for (int i = 0; i < nkt; i++, it++) {
+          const int s = it % STAGES;
+          if (!sm100::mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1)) {
+            atomicOr(status, IB_ERR_WAIT_TIMEOUT);
+            ok = false;
+            break;
+          }
+          uint8_t* a = tiles + s * TL::kStageBytes;
+          if (rank == 0) sm100::mbar_arrive_expect_tx(&full[s], 2 * TL::kStageBytes);   // the leader counts both CTAs' bytes
+#pragma unroll
+          for (int m = 0; m < MT; m++) tma_load_2d_pair(a + m * TL::kABytes, &tmap_w, i * BK, w_row(rb, m), &full[s]);
+          if (!waited) {   // the weights above do not depend on earlier kernels; x does
+            ib::pdl_wait();
+            waited = true;
+          }
+          tma_load_2d_pair(a + MT * TL::kABytes, &tmap_x, i * BK, t0 + (int)rank * BNH, &full[s]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (rank == 0 && sm100::elect_one()) {
+      constexpr uint32_t idesc = sm100::idesc_bf16_f32(2 * BM, BN);
+      bool ok = true;
+      int it = 0, tl = 0;
+      for (int tile = pair; tile < total_tiles && ok; tile += n_pairs, tl++) {
+        const int b = tl % NBUF;
+        if (tl >= NBUF && !sm100::mbar_wait(&acc_empty[b], ((tl / NBUF) - 1) & 1)) {   // the accumulator's last contents have been stored
+          atomicOr(status, IB_ERR_WAIT_TIMEOUT);
+          ok = false;
+          break;
+        }
+        sm100::tc_fence_after();
+        for (int i = 0; i < nkt; i++, it++) {
+          const int s = it % STAGES;
+          if (!sm100::mbar_wait(&full[s], (it / STAGES) & 1)) {
+            atomicOr(status, IB_ERR_WAIT_TIMEOUT);
+            ok = false;
+            break;
+          }
+          sm100::tc_fence_after();
+          const uint32_t a_addr = sm100::smem_u32(tiles + s * TL::kStageBytes);
+          const uint64_t db = sm100::smem_desc_sw128(a_addr + MT * TL::kABytes);
+#pragma unroll
+          for (int m = 0; m < MT; m++) {
+            const uint64_t da = sm100::smem_desc_sw128(a_addr + m * TL::kABytes);
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; k++) mma_bf16_ss_pair(tmem + b * MT * BN + m * BN, da + 2 * k, db + 2 * k, idesc, (i | k) != 0);
+          }
+          mma_commit_pair(&empty[s]);
+        }
+        if (ok) mma_commit_pair(&acc_full[b]);
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    ib::pdl_wait();
+    const uint32_t lane_addr = tmem + ((uint32_t)(q * 32) << 16);
+    int tl = 0;
+    for (int tile = pair; tile < total_tiles; tile += n_pairs, tl++) {
+      const int b = tl % NBUF;
+      const int t0 = (tile % token_tiles) * BN, n_pair = (tile / token_tiles) * kColsPerPair;
+      bool ok = sm100::mbar_wait(&acc_full[b], (tl / NBUF) & 1);
+      if (!ok && lane == 0) atomicOr(status, IB_ERR_WAIT_TIMEOUT);
+      sm100::tc_fence_after();
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      if constexpr (EPI == EPI_STORE) {
+        float* dst = (float*)out_;
+#pragma unroll 1
+        for (int m = 0; m < MT; m++) {
+          const int n = n_pair + m * 2 * BM + (int)rank * BM + q * 32 + lane;
+#pragma unroll 1
+          for (int c0 = 0; c0 < BN; c0 += 32) {
+            uint32_t r[32];
+            sm100::tmem_ld_32x32b_x32(lane_addr + b * MT * BN + m * BN + c0, r);
+            sm100::tmem_ld_wait();
+            if (n < N) {
+#pragma unroll
+              for (int c = 0; c < 32; c++) {
+                const int t = t0 + c0 + c;
+                if (t < T) dst[(size_t)t * N + n] = __uint_as_float(r[c]);
+              }
+            }
+          }
+        }
+      } else {
+        __nv_bfloat16* dst = (__nv_bfloat16*)out_;
+        const int n = n_pair + (int)rank * BM + q * 32 + lane;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          uint32_t g[32], u[32];
+          sm100::tmem_ld_32x32b_x32(lane_addr + b * MT * BN + c0, g);
+          sm100::tmem_ld_32x32b_x32(lane_addr + b * MT * BN + BN + c0, u);
+          sm100::tmem_ld_wait();
+          if (n < N) {
+#pragma unroll
+            for (int c = 0; c < 32; c++) {
+              const int t = t0 + c0 + c;
+              const float gv = __uint_as_float(g[c]), uv = __uint_as_float(u[c]);
+              if (t < T) dst[(size_t)t * N + n] = __float2bfloat16_rn(__fdividef(gv, 1.f + __expf(-gv)) * uv);
+            }
+          }
+        }
+      }
+      // this warp has read its part of the accumulator: tell the leader's MMA warp
+      sm100::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) arrive_on_leader(&acc_empty[b]);
+    }
+  }
+  sm100::tc_fence_before();
+  __syncthreads();
+  cluster_sync();   // neither CTA leaves (or frees tensor memory) while its partner may still signal it
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc2(tmem, 512);
+  }
+}
+
+int make_tmap(CUtensorMap* m, const void* ptr, int rows, int K, int box_rows) {
+  tma_host::EncodeTiledFn fn = tma_host::encode_fn();
+  IB_CHECK_ARG(fn, "gemm_tcgen05_2cta: the driver has no cuTensorMapEncodeTiled");
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  IB_CHECK_ARG(r == CUDA_SUCCESS, "gemm_tcgen05_2cta: cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return 0;
+}
+
+template <int MT, int EPI, int BN>
+int launch(const void* x, const void* w, void* out, int T, int N, int K, int w_rows, int second_off, unsigned* status, cudaStream_t stream) {
+  using TL = Tile<MT, BN>;
+  IB_CHECK_ARG(T > 0 && N > 0 && K > 0 && K % 8 == 0, "gemm_tcgen05_2cta: bad sizes T=%d N=%d K=%d (K must be a multiple of 8)", T, N, K);
+  IB_CHECK_ARG(((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0, "gemm_tcgen05_2cta: operands must be 16-byte aligned");
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_2cta_kernel<MT, EPI, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, TL::kSmemBytes);
+    IB_CHECK_ARG(e == cudaSuccess, "gemm_tcgen05_2cta: cannot reserve %d bytes of shared memory: %s", TL::kSmemBytes, cudaGetErrorString(e));
+    configured = true;
+  }
+  CUtensorMap tw, tx;
+  if (make_tmap(&tw, w, w_rows, K, BM)) return 1;
+  if (make_tmap(&tx, x, T, K, BN / 2)) return 1;
+  const int cols_per_pair = EPI == EPI_SWIGLU ? 2 * BM : 2 * BM * MT;
+  const int token_tiles = (T + BN - 1) / BN, row_blocks = (N + cols_per_pair - 1) / cols_per_pair;
+  const int total_tiles = token_tiles * row_blocks;
+  static int sm_count = 0;
+  if (!sm_count) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+  }
+  const int n_pairs = total_tiles < sm_count / 2 ? total_tiles : sm_count / 2;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * n_pairs);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = TL::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = ib_pdl_enabled();
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_2cta_kernel<MT, EPI, BN>, tw, tx, out, T, N, K, token_tiles, total_tiles, second_off, status);
+  IB_CHECK_ARG(e == cudaSuccess, "gemm_tcgen05_2cta: launch failed: %s", cudaGetErrorString(e));
+  return 0;
+}
+
+}  // namespace
+
+// x [T, K], w [N, K] bfloat16 -> out [T, N] float32, 256 x 256 tiles on CTA pairs (meant for T >= 256).
+extern "C" int ib_gemm_tcgen05_2cta(const void* x, const void* w, float* out, int T, int N, int K, unsigned* status, cudaStream_t stream) {
+  if (T == 0 || N == 0) return 0;
+  return launch<1, EPI_STORE, 256>(x, w, out, T, N, K, N, 0, status, stream);
+}
+
+// w [2*I, K] = gate rows then up rows -> act [T, I] bfloat16 = silu(x gate^T) * (x up^T), on CTA pairs.
+extern "C" int ib_gemm_swiglu_tcgen05_2cta(const void* x, const void* w, void* act, int T, int I, int K, unsigned* status, cudaStream_t stream) {
+  if (T == 0 || I == 0) return 0;
+  return launch<2, EPI_SWIGLU, 128>(x, w, act, T, I, K, 2 * I, I, status, stream);
+}

@@ -17,6 +17,10 @@ TOKEN_TILES = (16, 32, 64, 128, 256)
 
 L.register("ib_gemm_tcgen05", [L._p, L._p, L._p, L._i, L._i, L._i, L._i, L._i, L._i, L._p, L._p])
 L.register("ib_gemm_swiglu_tcgen05", [L._p, L._p, L._p, L._i, L._i, L._i, L._i, L._p, L._p])
+L.register("ib_gemm_tcgen05_2cta", [L._p, L._p, L._p, L._i, L._i, L._i, L._p, L._p])
+L.register("ib_gemm_swiglu_tcgen05_2cta", [L._p, L._p, L._p, L._i, L._i, L._i, L._p, L._p])
+
+PAIR_MIN_TOKENS = 256   # from here on the persistent CTA-pair kernels (csrc/gemm_tcgen05_2cta.cu) take over
 
 
 def supports(k: int) -> bool:
@@ -63,8 +67,22 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bn: int, splits: i
     L.call("ib_gemm_tcgen05", x.data_ptr(), w.data_ptr(), out.data_ptr(), T, N, K, bn, splits, 1 if wide else 0, status.data_ptr(), ops._stream())
 
 
+def gemm_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> None:
+    """out [T, N] float32 = x [T, K] w[N, K]^T on CTA pairs (256 x 256 tiles, persistent)."""
+    T, K = x.shape
+    N = w.shape[0]
+    ops._check("x", x, torch.bfloat16)
+    ops._check("w", w, torch.bfloat16, (N, K))
+    ops._check("out", out, torch.float32, (T, N))
+    L.call("ib_gemm_tcgen05_2cta", x.data_ptr(), w.data_ptr(), out.data_ptr(), T, N, K, status.data_ptr(), ops._stream())
+
+
 def linear(rt, x: torch.Tensor, lw, allow_split: bool = True) -> torch.Tensor:
     T = x.shape[0]
+    if T >= PAIR_MIN_TOKENS:
+        out = rt.empty((1, T, lw.n), torch.float32)
+        gemm_pair(x, lw.weight, out[0], rt.status)
+        return out
     bn, splits, wide = choose(T, lw.n, lw.k, allow_split)
     out = rt.empty((splits, T, lw.n), torch.float32)
     gemm(x, lw.weight, out, bn, splits, rt.status, wide)
@@ -84,6 +102,9 @@ def gemm_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tensor, sta
     ops._check("x", x, torch.bfloat16)
     ops._check("w_gate_up", w_gate_up, torch.bfloat16, (2 * I, K))
     ops._check("act", act, torch.bfloat16, (T, I))
+    if bn is None and T >= PAIR_MIN_TOKENS:
+        L.call("ib_gemm_swiglu_tcgen05_2cta", x.data_ptr(), w_gate_up.data_ptr(), act.data_ptr(), T, I, K, status.data_ptr(), ops._stream())
+        return
     if bn is None:
         bn = 64 if T <= 64 else (128 if T <= 128 else 256)
     L.call("ib_gemm_swiglu_tcgen05", x.data_ptr(), w_gate_up.data_ptr(), act.data_ptr(), T, I, K, bn, status.data_ptr(), ops._stream())

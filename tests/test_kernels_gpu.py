@@ -87,6 +87,32 @@ def test_gemm_swiglu_tcgen05(status, T, I, K, bn):
     assert ((act.double() - ref).abs() <= 2.0 ** -8 * ref.abs() + 1e-5 * ref.abs().max()).all()
 
 
+@pytest.mark.parametrize("T,N,K", [(256, 256, 64), (257, 130, 72), (300, 520, 264), (1000, 1000, 1024), (2048, 1536, 512), (4152, 640, 256)])
+def test_gemm_tcgen05_cta_pairs(status, T, N, K):
+    """The persistent CTA-pair kernel (cta_group::2), more tiles than pairs included."""
+    from inference_bench_b200.kernels import gemm_tcgen05 as G
+    x = (torch.randn(T, K, generator=_g(3)) * 0.5).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, K, generator=_g(4)) * 0.5).to(torch.bfloat16).to(DEV)
+    out = torch.full((T, N), float("nan"), device=DEV)
+    G.gemm_pair(x, w, out, status)
+    ref = x.double() @ w.double().T
+    assert status.item() == 0 and (out.double() - ref).abs().max() <= 2e-5 * ref.abs().max() + 1e-6
+
+
+@pytest.mark.parametrize("T,I,K", [(256, 128, 64), (300, 520, 264), (1000, 1000, 1024), (2048, 20000, 128)])
+def test_gemm_swiglu_cta_pairs(status, T, I, K):
+    from inference_bench_b200.kernels import gemm_tcgen05 as G
+    x = (torch.randn(T, K, generator=_g(5)) * 0.5).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(2 * I, K, generator=_g(6)) * 0.2).to(torch.bfloat16).to(DEV)
+    act = torch.full((T, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    G.gemm_swiglu(x, w, act, status)          # no tile given: 256 tokens and more go to the CTA pairs
+    gu = x.double() @ w.double().T
+    g, u = gu[:, :I], gu[:, I:]
+    ref = g / (1 + torch.exp(-g)) * u
+    assert status.item() == 0
+    assert ((act.double() - ref).abs() <= 2.0 ** -8 * ref.abs() + 1e-5 * ref.abs().max()).all()
+
+
 def test_gemm_tcgen05_refuses_bad_sizes(status):
     from inference_bench_b200.kernels import gemm_tcgen05 as G, lib
     x = torch.zeros(4, 100, dtype=torch.bfloat16, device=DEV)   # K = 100 is no multiple of 8
