@@ -3,7 +3,7 @@ with the same needs, and beside them slots of fixed-size per-request state.
 
 Executions of the schedule whose mixers ask for the same `PagedKV(kv_heads, head_dim, window)` form a
 group. A group has its own page pool, its own device tensor
-[pages, executions, 2 (K, V), kv_heads, page_size, head_dim] and its own block table per request; a
+[executions, pages, 2 (K, V), kv_heads, page_size, head_dim] and its own block table per request; a
 page therefore holds `page_size` positions of every execution in the group, and one table serves
 them all (block-major, like the reference: docs/specrt-scheduler.md:11, 20-22). A group with a window
 gives a page back as soon as every position in it has fallen out of the window of the request's
@@ -92,7 +92,7 @@ class CacheManager:
             for g in self.groups:
                 n = g.need
                 # one page more than the pool hands out: the scratch page that padded rows of a fixed-size batch write to
-                g.tensor = torch.zeros((g.pool.num_pages + 1, len(g.entries), 2, n.kv_heads, page_size, n.head_dim), dtype=dtype, device=device)
+                g.tensor = torch.zeros((len(g.entries), g.pool.num_pages + 1, 2, n.kv_heads, page_size, n.head_dim), dtype=dtype, device=device)
             for i, n in self._fixed.items():
                 # and one scratch slot more than requests can hold
                 self.states[i].tensor = torch.zeros((max_requests + 1, *n.shape), dtype=n.dtype, device=device)

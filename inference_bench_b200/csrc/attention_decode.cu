@@ -23,6 +23,23 @@ constexpr int kTile = kWarps * kKeysPerWarp;     // keys per tile; a CTA walks t
 constexpr int kNT = kKeysPerWarp / 8;            // 8-key MMA column tiles per warp
 constexpr int kKS = kKeysPerWarp / 16;           // 16-key MMA steps per warp
 
+// How the visible keys [lo, pos] of a decoded token are cut into slices of `tps` tiles from tile `tile_lo` on.
+// tiles_per_slice > 0: slices of that many tiles at fixed absolute positions. 0: the token's own visible
+// tiles in max_slices equal parts of at least kMinTiles tiles, so that every token gives about as many
+// units of work, of about equal size, whatever its length.
+constexpr int kMinTiles = 2;
+__device__ __forceinline__ void slice_plan(int pos, int window, int max_slices, int tiles_per_slice, int& lo, int& tile_lo, int& tps) {
+  lo = window > 0 ? max(0, pos - window + 1) : 0;
+  if (tiles_per_slice > 0) {
+    tile_lo = 0;
+    tps = tiles_per_slice;
+    return;
+  }
+  tile_lo = lo / kTile;
+  const int tiles = pos / kTile - tile_lo + 1;
+  tps = max(kMinTiles, (tiles + max_slices - 1) / max_slices);
+}
+
 template <int HD>
 __global__ void __launch_bounds__(kWarps * 32)
     decode_split_kernel(const __nv_bfloat16* __restrict__ q, IbKvView kv, const int* __restrict__ dec_tokens,
@@ -303,30 +320,413 @@ __global__ void __launch_bounds__(kWarps * 32)
   }
 }
 
-// out[token][head] = sum over the slices that hold visible keys of O_s 2^(m_s - M) / sum of l_s 2^(m_s - M)
+// out[token][head] = sum over the slices that hold visible keys of O_s 2^(m_s - M) / sum of l_s 2^(m_s - M).
+// One CTA per (head, token): kCombineThreads threads as [slice lanes][head_dim / 4]; a thread sums every
+// lane-th slice for four values of the head, and the lanes are added in order through shared memory.
+constexpr int kCombineThreads = 256;
+
 template <int HD>
-__global__ void decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, const int* __restrict__ dec_tokens,
-                                      const int* __restrict__ positions, int window, __nv_bfloat16* __restrict__ out, int heads, int max_slices,
-                                      int slice_keys) {
+__global__ void __launch_bounds__(kCombineThreads)
+    decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, const int* __restrict__ dec_tokens,
+                          const int* __restrict__ positions, int window, __nv_bfloat16* __restrict__ out, int heads, int max_slices,
+                          int tiles_per_slice) {
+  constexpr int DQ = HD / 4;
+  constexpr int SG = kCombineThreads / DQ;
+  __shared__ float4 o_red[SG][DQ];
+  __shared__ float m_red[SG], l_red[SG];
   ib::pdl_launch_dependents();
-  ib::pdl_wait();
   const int h = blockIdx.x, item = blockIdx.y;
   const int t = dec_tokens[item];
   const int pos = positions[t];
-  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-  const int s_begin = lo / slice_keys, s_end = pos / slice_keys + 1;
+  int lo, tile_lo, tps;
+  slice_plan(pos, window, max_slices, tiles_per_slice, lo, tile_lo, tps);
+  const int s_begin = (lo / kTile - tile_lo) / tps, s_end = (pos / kTile - tile_lo) / tps + 1;
   const size_t slot0 = ((size_t)item * heads + h) * max_slices;
+  const int sg = threadIdx.x / DQ, dq = threadIdx.x % DQ;
+  ib::pdl_wait();
+  float mx = -INFINITY;
+  for (int s = s_begin + sg; s < s_end; s += SG) mx = fmaxf(mx, part_ml[(slot0 + s) * 2]);
+  if (dq == 0) m_red[sg] = mx;
+  __syncthreads();
   float M = -INFINITY;
-  for (int s = s_begin; s < s_end; s++) M = fmaxf(M, part_ml[(slot0 + s) * 2]);
-  for (int d = threadIdx.x; d < HD; d += blockDim.x) {
-    float L = 0.f, O = 0.f;
-    for (int s = s_begin; s < s_end; s++) {
-      float f = exp2f(part_ml[(slot0 + s) * 2] - M);
-      L += part_ml[(slot0 + s) * 2 + 1] * f;
-      O += part_o[(slot0 + s) * HD + d] * f;
-    }
-    out[((size_t)t * heads + h) * HD + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+#pragma unroll
+  for (int i = 0; i < SG; i++) M = fmaxf(M, m_red[i]);
+  float Lp = 0.f;
+  float4 Op = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int s = s_begin + sg; s < s_end; s += SG) {
+    const float f = exp2f(part_ml[(slot0 + s) * 2] - M);
+    Lp += part_ml[(slot0 + s) * 2 + 1] * f;
+    const float4 v = *(const float4*)&part_o[(slot0 + s) * HD + 4 * dq];
+    Op.x += v.x * f;
+    Op.y += v.y * f;
+    Op.z += v.z * f;
+    Op.w += v.w * f;
   }
+  o_red[sg][dq] = Op;
+  if (dq == 0) l_red[sg] = Lp;
+  __syncthreads();
+  if (sg == 0) {
+    float Lsum = 0.f;
+    float4 O = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int i = 0; i < SG; i++) {
+      Lsum += l_red[i];
+      const float4 v = o_red[i][dq];
+      O.x += v.x;
+      O.y += v.y;
+      O.z += v.z;
+      O.w += v.w;
+    }
+    if (!(Lsum > 0.f)) {
+      O = make_float4(0.f, 0.f, 0.f, 0.f);
+      Lsum = 1.f;
+    }
+    uint2 packed = make_uint2(mt::pack_bf16(O.x / Lsum, O.y / Lsum), mt::pack_bf16(O.z / Lsum, O.w / Lsum));
+    *(uint2*)&out[((size_t)t * heads + h) * HD + 4 * dq] = packed;
+  }
+}
+
+// ---------------------------------------------------------------- the streaming variant
+//
+// The same slices, the same arithmetic and the same scratch, but CTAs that stay: a CTA takes every
+// gridDim.x-th unit (slice, token, kv head), and a fifth warp runs ahead of the four computing warps
+// through a ring of kRing tiles that TMA box copies fill (one box per page, plane and 64 values of
+// the head dimension). The ring does not drain where a unit ends, so copies are in flight all the
+// time; with one short-lived CTA per unit the memory system idles while each CTA looks its pages
+// up and while it merges its warps. Needs the tensor map of the pool (ib_make_kv_map).
+constexpr int kRing = 3;
+constexpr int kMeta = 256;   // decoded tokens whose row, position and segment are kept in shared memory
+
+__device__ __forceinline__ void bar_sync_compute() { asm volatile("bar.sync 1, %0;" ::"n"(kWarps * 32) : "memory"); }
+
+template <int HD>
+__global__ void __launch_bounds__((kWarps + 1) * 32, 2)
+    decode_stream_kernel(const __nv_bfloat16* __restrict__ q, IbKvView kv, const int* __restrict__ dec_tokens, const int* __restrict__ positions,
+                         const int* __restrict__ seg_of_token, int window, float scale_log2e, float* __restrict__ part_o,
+                         float* __restrict__ part_ml, int heads, int n_dec, int max_slices, int tiles_per_slice,
+                         const __grid_constant__ CUtensorMap kv_map, long long view_row0, unsigned* __restrict__ status) {
+  constexpr int CPR = HD / 8;
+  constexpr int TILE = kTile * HD * 2;
+  constexpr int HB = HD / 64;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const int group = heads / kv.kv_heads;
+  // layout: kRing x (K tile, V tile) | Q tile [16][HD] | (max, sum) [warps][16] | O [warps][group][HD] | barriers | flag | token table
+  uint8_t* ring = smem;
+  const uint32_t q_s = mt::smem_u32(smem + kRing * 2 * TILE);
+  float* ml_s = (float*)(smem + kRing * 2 * TILE + 16 * HD * 2);
+  float* o_s = ml_s + kWarps * 16 * 2;
+  uint64_t* full = (uint64_t*)(o_s + kWarps * group * HD);
+  uint64_t* empty = full + kRing;
+  volatile int* gave_up = (volatile int*)(empty + kRing);
+  int* meta = (int*)(empty + kRing) + 2;   // [kMeta][3]
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if ((mt::smem_u32(smem) & 1023u) != 0) {   // the swizzle of the box copies counts from 1024-byte boundaries
+    if (tid == 0) atomicOr(status, IB_ERR_INTERNAL);
+    return;
+  }
+  if (tid == 0) {
+    for (int s = 0; s < kRing; s++) {
+      sm100::mbar_init(&full[s], 1);
+      sm100::mbar_init(&empty[s], kWarps);
+    }
+    *gave_up = 0;
+    sm100::fence_barrier_init();
+  }
+  __syncthreads();
+  ib::pdl_launch_dependents();
+
+  const int n_units = max_slices * n_dec * kv.kv_heads;
+  // Row, position and segment of the first kMeta decoded tokens, fetched once: opening a unit then costs
+  // no chain of loads from global memory. Index arrays and the block table were complete before the
+  // step began, so they are read without waiting for the kernel before.
+  for (int i = tid; i < min(n_dec, kMeta); i += (kWarps + 1) * 32) {
+    const int tt = dec_tokens[i];
+    meta[3 * i] = tt;
+    meta[3 * i + 1] = positions[tt];
+    meta[3 * i + 2] = seg_of_token[tt];
+  }
+  __syncthreads();
+  // unit -> what it covers; false when it holds no visible key
+  int kvh, item, slice, t, pos, seg, k_begin, k_end;
+  auto open_unit = [&](int u) {
+    kvh = u % kv.kv_heads;
+    const int r = u / kv.kv_heads;
+    item = r % n_dec;
+    slice = r / n_dec;
+    if (item < kMeta) {
+      t = meta[3 * item];
+      pos = meta[3 * item + 1];
+      seg = meta[3 * item + 2];
+    } else {
+      t = dec_tokens[item];
+      pos = positions[t];
+      seg = seg_of_token[t];
+    }
+    int lo, tile_lo, tps;
+    slice_plan(pos, window, max_slices, tiles_per_slice, lo, tile_lo, tps);
+    k_begin = max(lo, (tile_lo + slice * tps) * kTile);
+    k_end = min(pos + 1, (tile_lo + (slice + 1) * tps) * kTile);
+    return k_begin < k_end;
+  };
+  auto next_unit = [&](int u) {   // the first unit from u on, in this CTA's stride, that holds a visible key; opened
+    while (u < n_units && !open_unit(u)) u += gridDim.x;
+    return u;
+  };
+
+  if (warp == kWarps) {
+    // ---------------- the copying warp
+    const int box_rows = min(kv.page_size, kTile);   // rows of one box: a page, or the tile's part of a larger page
+    const int ppt = kTile / box_rows;                // boxes per tile, plane and 64-value block
+    const long long rows_per_page = kv.page_stride / HD, v_rows = kv.v_offset / HD;
+    uint32_t n = 0;        // tiles sent so far
+    bool waited = false;   // the kernel before this one writes only the rows of the tokens' own positions
+    bool ok = true;
+    for (int u = next_unit(blockIdx.x); u < n_units && ok; u = next_unit(u + gridDim.x)) {
+      const int tile_begin = k_begin / kTile, tile_end = (k_end - 1) / kTile + 1;
+      int held = -2;       // page of box (tile_begin * ppt + base + lane), looked up 32 boxes at a time
+      for (int tile = tile_begin; tile < tile_end; tile++, n++) {
+        const int rel = (tile - tile_begin) * ppt;
+        if ((rel & 31) == 0) {
+          const int key0 = (tile_begin * ppt + rel + lane) * box_rows;
+          const int col = key0 / kv.page_size;
+          held = -2;
+          if (key0 < k_end && key0 + box_rows > k_begin) held = col < kv.table_stride ? kv.block_table[(size_t)seg * kv.table_stride + col] : -1;
+        }
+        const int my = (lane - rel) & 31;            // which box of this tile this lane holds, if < ppt
+        const bool mine = my < ppt;
+        const bool valid = mine && held >= 0 && held < kv.num_pages;
+        if (mine && held != -2 && !valid) atomicOr(status, IB_ERR_BAD_PAGE);
+        const unsigned vmask = __ballot_sync(0xffffffffu, valid);
+        if (!waited && pos >= tile * kTile && pos < (tile + 1) * kTile) {
+          ib::pdl_wait();
+          waited = true;
+        }
+        const int stage = n % kRing;
+        if (lane == 0) ok = sm100::mbar_wait(&empty[stage], ((n / kRing) & 1) ^ 1);
+        ok = __shfl_sync(0xffffffffu, ok, 0) && !*gave_up;
+        if (!ok) break;
+        uint8_t* k_t = ring + stage * 2 * TILE;
+        // boxes that are not copied (no visible key in them, or no page) are cleared: a masked key's value still meets a zero weight
+        bool cleared = false;
+        for (int pg = 0; pg < ppt; pg++) {
+          if ((vmask >> ((rel + pg) & 31)) & 1) continue;
+          cleared = true;
+          for (int idx = lane; idx < box_rows * 8 * HB * 2; idx += 32) {
+            const int plane = idx / (box_rows * 8 * HB), r2 = idx % (box_rows * 8 * HB);
+            const int hb = r2 / (box_rows * 8), r3 = r2 % (box_rows * 8);
+            mt::st_shared_zero16(mt::smem_u32(k_t + plane * TILE + hb * kTile * 128 + pg * box_rows * 128) + r3 * 16);
+          }
+        }
+        if (cleared) sm100::fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) sm100::mbar_arrive_expect_tx(&full[stage], (uint32_t)(__popc(vmask) * box_rows * 128 * HB * 2));
+        __syncwarp();
+        if (valid) {
+          const int key0 = tile * kTile + my * box_rows;
+          const long long row = (long long)held * rows_per_page + view_row0 + (long long)kvh * kv.page_size + key0 % kv.page_size;
+#pragma unroll
+          for (int hb = 0; hb < HB; hb++) {
+            uint8_t* dk = k_t + hb * kTile * 128 + my * box_rows * 128;
+            sm100::tma_load_2d(dk, &kv_map, hb * 64, (int)row, &full[stage]);
+            sm100::tma_load_2d(dk + TILE, &kv_map, hb * 64, (int)(row + v_rows), &full[stage]);
+          }
+        }
+      }
+    }
+    if (!ok) {   // a wait ran out: say so, and let the copies in flight land before the shared memory goes
+      if (lane == 0) {
+        *gave_up = 1;
+        atomicOr(status, IB_ERR_WAIT_TIMEOUT);
+        for (uint32_t j = n > kRing ? n - kRing : 0; j < n; j++) sm100::mbar_wait(&full[j % kRing], (j / kRing) & 1);
+      }
+    }
+    return;
+  }
+
+  // ---------------- the four computing warps
+  const int g = lane >> 2, tq = lane & 3;
+  const int wkey = warp * kKeysPerWarp;
+  ib::pdl_wait();   // q comes from the kernel before
+  uint32_t n = 0;
+  bool dead = false;
+  for (int idx = tid; idx < 16 * CPR; idx += kWarps * 32)   // rows above the group stay zero
+    if (idx / CPR >= group) mt::st_shared_zero16(q_s + mt::tile_offset<HD, 16>(idx / CPR, idx % CPR));
+  auto fetch_q = [&]() {   // the opened unit's query rows into the Q tile
+    for (int idx = tid; idx < group * CPR; idx += kWarps * 32) {
+      const int row = idx / CPR, c = idx % CPR;
+      mt::cp_async16(q_s + mt::tile_offset<HD, 16>(row, c), q + ((size_t)t * heads + (size_t)kvh * group + row) * HD + c * 8);
+    }
+    mt::cp_async_commit();
+  };
+  int u = next_unit(blockIdx.x);
+  if (u < n_units) fetch_q();
+  while (u < n_units) {
+    mt::cp_async_wait<0>();
+    bar_sync_compute();   // the Q tile is whole; every warp is done with the last unit's merge buffers
+    uint32_t qa[HD / 16][4];
+#pragma unroll
+    for (int kk = 0; kk < HD / 16; kk++) mt::load_a_frag<HD, 16>(q_s, 0, kk, lane, qa[kk]);
+    bar_sync_compute();   // every warp holds its fragments: the Q tile is free for the next unit's rows, which travel during this unit
+    const int u_next = next_unit(u + gridDim.x);
+    if (u_next < n_units) fetch_q();
+    open_unit(u);
+    const int tile_begin = k_begin / kTile, tile_end = (k_end - 1) / kTile + 1;
+
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float o[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; i++)
+#pragma unroll
+      for (int e = 0; e < 4; e++) o[i][e] = 0.f;
+
+    for (int tile = tile_begin; tile < tile_end; tile++, n++) {
+      const int stage = n % kRing;
+      // After a wait that ran out nothing is waited for any more; the loops still run to their ends,
+      // so that every warp meets the others at the barriers (the results are then void, and the status says so).
+      if (!dead) {
+        if (!sm100::mbar_wait(&full[stage], (n / kRing) & 1)) {
+          *gave_up = 1;
+          if (lane == 0) atomicOr(status, IB_ERR_WAIT_TIMEOUT);
+        }
+        if (*gave_up) dead = true;
+      }
+      __syncwarp();
+      const uint32_t k_s = mt::smem_u32(ring + stage * 2 * TILE), v_s = k_s + TILE;
+      float s[kNT][4];
+#pragma unroll
+      for (int j = 0; j < kNT; j++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) s[j][e] = 0.f;
+#pragma unroll
+      for (int kk = 0; kk < HD / 16; kk++) {
+        uint32_t b[4];
+#pragma unroll
+        for (int pr = 0; pr < kKS; pr++) {
+          mt::load_k_frag<HD, kTile>(k_s, wkey + 16 * pr, kk, lane, b);
+          mt::mma_16816(s[2 * pr], qa[kk], b[0], b[1]);
+          mt::mma_16816(s[2 * pr + 1], qa[kk], b[2], b[3]);
+        }
+      }
+      float mn[2] = {m[0], m[1]};
+#pragma unroll
+      for (int j = 0; j < kNT; j++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+          const int key = tile * kTile + wkey + 8 * j + 2 * tq + (e & 1);
+          const float v = (key >= k_begin && key < k_end) ? s[j][e] * scale_log2e : -INFINITY;
+          s[j][e] = v;
+          mn[e >> 1] = fmaxf(mn[e >> 1], v);
+        }
+      float mu[2], corr[2];
+#pragma unroll
+      for (int r = 0; r < 2; r++) {
+        mn[r] = fmaxf(mn[r], __shfl_xor_sync(0xffffffffu, mn[r], 1));
+        mn[r] = fmaxf(mn[r], __shfl_xor_sync(0xffffffffu, mn[r], 2));
+        mu[r] = mn[r] == -INFINITY ? 0.f : mn[r];
+        corr[r] = exp2f(m[r] - mu[r]);   // 0 while m is still -inf
+        m[r] = mn[r];
+        l[r] *= corr[r];
+      }
+      if (tile > tile_begin) {
+#pragma unroll
+        for (int i = 0; i < HD / 8; i++) {
+          o[i][0] *= corr[0];
+          o[i][1] *= corr[0];
+          o[i][2] *= corr[1];
+          o[i][3] *= corr[1];
+        }
+      }
+      uint32_t p[kKS][4];
+#pragma unroll
+      for (int j = 0; j < kNT; j++) {
+        const float e0 = exp2f(s[j][0] - mu[0]), e1 = exp2f(s[j][1] - mu[0]), e2 = exp2f(s[j][2] - mu[1]), e3 = exp2f(s[j][3] - mu[1]);
+        l[0] += e0 + e1;
+        l[1] += e2 + e3;
+        p[j >> 1][(j & 1) * 2] = mt::pack_bf16(e0, e1);
+        p[j >> 1][(j & 1) * 2 + 1] = mt::pack_bf16(e2, e3);
+      }
+#pragma unroll
+      for (int ks = 0; ks < kKS; ks++)
+#pragma unroll
+        for (int dp = 0; dp < HD / 16; dp++) {
+          uint32_t b[4];
+          mt::load_v_frag<HD, kTile>(v_s, wkey + 16 * ks, dp, lane, b);
+          mt::mma_16816(o[2 * dp], p[ks], b[0], b[1]);
+          mt::mma_16816(o[2 * dp + 1], p[ks], b[2], b[3]);
+        }
+      __syncwarp();
+      if (lane == 0) sm100::mbar_arrive(&empty[stage]);   // this warp has read what it needs of the stage
+    }
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+      l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+      l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+    }
+    // merge the four warps; only the rows that are heads of the group are kept
+    if (tq == 0) {
+      ml_s[(warp * 16 + g) * 2] = m[0];
+      ml_s[(warp * 16 + g) * 2 + 1] = l[0];
+      ml_s[(warp * 16 + g + 8) * 2] = m[1];
+      ml_s[(warp * 16 + g + 8) * 2 + 1] = l[1];
+    }
+#pragma unroll
+    for (int i = 0; i < HD / 8; i++) {
+      const int d = 8 * i + 2 * tq;
+      if (g < group) *(float2*)&o_s[(warp * group + g) * HD + d] = make_float2(o[i][0], o[i][1]);
+      if (g + 8 < group) *(float2*)&o_s[(warp * group + g + 8) * HD + d] = make_float2(o[i][2], o[i][3]);
+    }
+    bar_sync_compute();
+    for (int idx = tid; idx < group * HD; idx += kWarps * 32) {
+      const int row = idx / HD, d = idx % HD;
+      float M = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < kWarps; w++) M = fmaxf(M, ml_s[(w * 16 + row) * 2]);
+      float Lsum = 0.f, O = 0.f;
+#pragma unroll
+      for (int w = 0; w < kWarps; w++) {
+        const float mw = ml_s[(w * 16 + row) * 2];
+        const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
+        Lsum += ml_s[(w * 16 + row) * 2 + 1] * f;
+        O += o_s[(w * group + row) * HD + d] * f;
+      }
+      const size_t slot = ((size_t)item * heads + (size_t)kvh * group + row) * max_slices + slice;
+      part_o[slot * HD + d] = O;
+      if (d == 0) {
+        part_ml[slot * 2] = M;
+        part_ml[slot * 2 + 1] = Lsum;
+      }
+    }
+    u = u_next;
+  }
+}
+
+template <int HD>
+int launch_stream(const void* q, const IbKvView* kv, const int* dec_tokens, int n_dec, const int* positions, const int* seg_of_token, int window,
+                  float scale, float* part_o, float* part_ml, void* out, int heads, int max_slices, int tiles_per_slice, const CUtensorMap* kv_map,
+                  long long view_row0, unsigned* status, cudaStream_t stream) {
+  const int group = heads / kv->kv_heads;
+  const int smem = kRing * 2 * kTile * HD * 2 + 16 * HD * 2 + kWarps * 16 * 2 * 4 + kWarps * group * HD * 4 + 2 * kRing * 8 + 16 + kMeta * 12;
+  static int reserved = 0, per_sm = 0, sms = 0;
+  if (smem != reserved) {
+    cudaError_t e = cudaFuncSetAttribute(decode_stream_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    IB_CHECK_ARG(e == cudaSuccess, "attention_decode_stream: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_stream_kernel<HD>, (kWarps + 1) * 32, smem);
+    IB_CHECK_ARG(e == cudaSuccess && per_sm >= 1, "attention_decode_stream: no CTA fits an SM with %d bytes of shared memory", smem);
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    reserved = smem;
+  }
+  const long long units = (long long)max_slices * n_dec * kv->kv_heads;
+  IB_CHECK_ARG(units < (1ll << 31), "attention_decode_stream: %lld units", units);
+  const int grid = (int)(units < (long long)sms * per_sm ? units : (long long)sms * per_sm);
+  ib::launch(decode_stream_kernel<HD>, grid, (kWarps + 1) * 32, smem, stream, (const __nv_bfloat16*)q, *kv, dec_tokens, positions, seg_of_token,
+             window, scale * 1.4426950408889634f, part_o, part_ml, heads, n_dec, max_slices, tiles_per_slice, *kv_map, view_row0, status);
+  IB_CHECK_LAUNCH("attention_decode_stream split");
+  ib::launch(decode_combine_kernel<HD>, dim3(heads, n_dec), kCombineThreads, 0, stream, part_o, part_ml, dec_tokens, positions, window, (__nv_bfloat16*)out, heads,
+             max_slices, tiles_per_slice);
+  IB_CHECK_LAUNCH("attention_decode_stream combine");
+  return 0;
 }
 
 template <int HD>
@@ -347,8 +747,8 @@ int launch(const void* q, const IbKvView* kv, const int* dec_tokens, int n_dec, 
              scale * 1.4426950408889634f, part_o, part_ml, heads, max_slices, tiles_per_slice, kv_map ? *kv_map : none, view_row0,
              kv_map ? 1 : 0, status);
   IB_CHECK_LAUNCH("attention_decode split");
-  ib::launch(decode_combine_kernel<HD>, dim3(heads, n_dec), HD, 0, stream, part_o, part_ml, dec_tokens, positions, window, (__nv_bfloat16*)out, heads,
-             max_slices, tiles_per_slice * kTile);
+  ib::launch(decode_combine_kernel<HD>, dim3(heads, n_dec), kCombineThreads, 0, stream, part_o, part_ml, dec_tokens, positions, window, (__nv_bfloat16*)out, heads,
+             max_slices, tiles_per_slice);
   IB_CHECK_LAUNCH("attention_decode combine");
   return 0;
 }
@@ -364,20 +764,20 @@ int launch(const void* q, const IbKvView* kv, const int* dec_tokens, int n_dec, 
 // view's keys of page 0, head 0 start), or null to copy keys and values with cp.async.
 extern "C" int ib_attention_decode_tile() { return kTile; }
 
-// Describes a whole cache pool [pages, executions, 2, kv_heads, page_size, head_dim] (bfloat16) to TMA
+// Describes a whole cache pool [executions, pages, 2, kv_heads, page_size, head_dim] (bfloat16) to TMA
 // as a matrix of [all rows, head_dim] read in boxes of [page_size rows, 64 columns] with the 128-byte
 // swizzle. `map_out` receives the 128-byte tensor map that the attention entry points take.
 // Returns 1 with a message when the geometry cannot be served (the kernels then copy with cp.async).
 extern "C" int ib_make_kv_map(void* map_out, const void* pool_base, long long total_rows, int head_dim, int page_size) {
   IB_CHECK_ARG(map_out && pool_base && total_rows > 0, "make_kv_map: null pointer or no rows");
   IB_CHECK_ARG(head_dim % 64 == 0, "make_kv_map: head_dim %d is not a multiple of 64", head_dim);
-  IB_CHECK_ARG(page_size % 8 == 0 && page_size <= 256, "make_kv_map: page size %d is not a multiple of 8 up to 256", page_size);
+  IB_CHECK_ARG(page_size % 8 == 0 && (kTile % page_size == 0 || page_size % kTile == 0), "make_kv_map: page size %d is not a multiple of 8 that divides %d or a multiple of it", page_size, kTile);
   IB_CHECK_ARG(total_rows < (1ll << 31), "make_kv_map: %lld rows exceed the 32-bit coordinate range", total_rows);
   tma_host::EncodeTiledFn fn = tma_host::encode_fn();
   IB_CHECK_ARG(fn, "make_kv_map: the driver has no cuTensorMapEncodeTiled");
   cuuint64_t dims[2] = {(cuuint64_t)head_dim, (cuuint64_t)total_rows};
   cuuint64_t strides[1] = {(cuuint64_t)head_dim * 2};
-  cuuint32_t box[2] = {64, (cuuint32_t)page_size};
+  cuuint32_t box[2] = {64, (cuuint32_t)(page_size < kTile ? page_size : kTile)};   // a page, or the tile's part of a larger one
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn((CUtensorMap*)map_out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool_base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -405,6 +805,32 @@ extern "C" int ib_attention_decode(const void* q, const IbKvView* kv, const int*
     return launch<64>(q, kv, dec_tokens, n_dec, positions, seg_of_token, window, scale, part_o, part_ml, out, heads, max_slices, tiles_per_slice,
                       (const CUtensorMap*)kv_map, view_row0, status, stream);
   return ib_set_error("attention_decode: head_dim %d has no tensor-core kernel (64 and 128 have)", kv->head_dim);
+}
+
+// The streaming variant: the same arguments and scratch; kv_map is required, and the page size must be a
+// multiple of 8 that divides the tile or a multiple of the tile. tiles_per_slice = 0 cuts every token's
+// visible keys into max_slices equal slices (of two tiles at least) instead of slices at fixed positions.
+extern "C" int ib_attention_decode_stream(const void* q, const IbKvView* kv, const int* dec_tokens, int n_dec, const int* positions,
+                                          const int* seg_of_token, int window, float scale, float* part_o, float* part_ml, void* out,
+                                          int heads, int max_slices, int tiles_per_slice, const void* kv_map, long long view_row0,
+                                          unsigned* status, cudaStream_t stream) {
+  if (n_dec == 0) return 0;
+  IB_CHECK_ARG(kv && kv->base && kv->block_table && kv_map, "attention_decode_stream: the cache view or the tensor map is a null pointer");
+  IB_CHECK_ARG(kv->page_size % 8 == 0 && (kTile % kv->page_size == 0 || kv->page_size % kTile == 0),
+               "attention_decode_stream: page size %d is not a multiple of 8 that divides %d or a multiple of %d", kv->page_size, kTile, kTile);
+  IB_CHECK_ARG(tiles_per_slice >= 0 && tiles_per_slice <= 1024, "attention_decode_stream: %d tiles per slice", tiles_per_slice);
+  IB_CHECK_ARG(kv->dtype == IB_BF16, "attention_decode_stream: the cache must be bfloat16");
+  IB_CHECK_ARG(kv->kv_heads > 0 && heads % kv->kv_heads == 0 && heads / kv->kv_heads <= 16,
+               "attention_decode_stream: %d query heads on %d kv heads (groups of up to 16 are supported)", heads, kv->kv_heads);
+  IB_CHECK_ARG(n_dec > 0 && n_dec <= 65535 && max_slices > 0 && max_slices <= 65535, "attention_decode_stream: bad sizes n=%d slices=%d", n_dec, max_slices);
+  IB_CHECK_ARG(kv->page_stride % kv->head_dim == 0 && kv->v_offset % kv->head_dim == 0, "attention_decode_stream: strides are not whole rows");
+  if (kv->head_dim == 128)
+    return launch_stream<128>(q, kv, dec_tokens, n_dec, positions, seg_of_token, window, scale, part_o, part_ml, out, heads, max_slices,
+                              tiles_per_slice, (const CUtensorMap*)kv_map, view_row0, status, stream);
+  if (kv->head_dim == 64)
+    return launch_stream<64>(q, kv, dec_tokens, n_dec, positions, seg_of_token, window, scale, part_o, part_ml, out, heads, max_slices,
+                             tiles_per_slice, (const CUtensorMap*)kv_map, view_row0, status, stream);
+  return ib_set_error("attention_decode_stream: head_dim %d has no tensor-core kernel (64 and 128 have)", kv->head_dim);
 }
 
 // ---------------------------------------------------------------- the variant that allocates nothing

@@ -217,7 +217,9 @@ __global__ void sample_final_kernel(const float* __restrict__ part_v, const int*
 __global__ void advance_rows_kernel(const int* __restrict__ sampled, int* __restrict__ token_in, int* __restrict__ positions,
                                     int* __restrict__ pos0, RowParams* __restrict__ params, int* __restrict__ history, int* __restrict__ count,
                                     int rows, int history_len) {
-  ib::pdl_launch_dependents();
+  // No early launch of the kernels that follow: the attention kernels of the next step read
+  // `positions` before their own dependency wait, so nothing of the next step may start before
+  // the rows are written. The next kernel starts when this one has finished.
   ib::pdl_wait();
   int i = blockIdx.x * blockDim.x + threadIdx.x;
   int c = count[0];

@@ -29,10 +29,44 @@ def decode_tiles_per_slice(n_dec: int, kv_heads: int, max_keys: int) -> int:
         tps *= 2
     return tps
 
+_SM_COUNT: dict = {}
+
+
+def stream_pays(n_dec: int, kv_heads: int, device) -> bool:
+    """Whether the streaming decode kernel is the faster one: measured inside whole decode steps at
+    Qwen3-8B shape, it wins (by up to 6 % of the step) from 4 to 32 requests of 8 kv heads, where the
+    kernel with one CTA per slice runs a few short waves of CTAs; with fewer (token, kv head) pairs every
+    slice gets a CTA at once and the shorter start decides, and with more pairs than CTAs that stay, the
+    longer waves of the other kernel overlap better with the kernels around it."""
+    if STREAM_ALWAYS:
+        return True
+    if device not in _SM_COUNT:
+        _SM_COUNT[device] = torch.cuda.get_device_properties(device).multi_processor_count
+    return 24 <= n_dec * kv_heads <= 2 * _SM_COUNT[device]
+
+
+def stream_slices(n_dec: int, kv_heads: int, max_keys: int, device) -> int:
+    """Into how many slices the streaming decode kernel cuts each token's keys. Its CTAs stay (two per
+    SM) and take (slice, token, kv head) units in turn: with few tokens, as many slices as give every
+    CTA one unit; with more (token, kv head) pairs than CTAs, enough slices for about six units per
+    CTA, so that the last round leaves few CTAs idle. A slice has two tiles at least."""
+    if device not in _SM_COUNT:
+        _SM_COUNT[device] = torch.cuda.get_device_properties(device).multi_processor_count
+    slots = 2 * _SM_COUNT[device]
+    pairs = n_dec * kv_heads
+    want = slots // pairs if pairs <= slots else -(-6 * slots // pairs)
+    tiles = -(-max_keys // decode_tile())
+    return max(1, min(want, -(-tiles // 2)))
+
+
 QTILE = {"tcgen05": 128, "mma": 64}   # query rows per CTA of the prefill kernels (csrc/attention_prefill_tc.cu, attention_prefill.cu)
 PREFILL_KERNEL = "tcgen05"               # which one the engine uses; the other stays as a tested alternative
 
 L.register("ib_attention_decode", [L._p, C.POINTER(L.KvView), L._p, L._i, L._p, L._p, L._i, L._f, L._p, L._p, L._p, L._i, L._i, L._i, L._p, L._ll, L._p, L._p])
+L.register("ib_attention_decode_stream", [L._p, C.POINTER(L.KvView), L._p, L._i, L._p, L._p, L._i, L._f, L._p, L._p, L._p, L._i, L._i, L._i, L._p, L._ll, L._p, L._p])
+DECODE_KERNEL = "stream"   # "stream": CTAs that stay and a ring that TMA fills (needs a page size TMA can serve); "split": one CTA per slice
+STREAM_ALWAYS = False        # tests set this to reach the streaming kernel at any batch size
+STREAM_TILES_PER_SLICE = 0   # 0: every token's visible keys in stream_slices() equal parts; n > 0: slices of n tiles at fixed positions
 USE_TMA = False  # decode keys and values by TMA box copies (one thread, one 2 KiB box per page and plane) instead of cp.async by all
                  # threads: measured slower at page size 16 (3.86 against 3.71 ms per step at batch 8), so off; kept and tested
 L.register("ib_attention_prefill", [L._p, C.POINTER(L.KvView), L._p, L._p, L._i, L._p, L._p, L._i, L._f, L._p, L._i, L._p, L._p])
@@ -83,17 +117,23 @@ def paged_attention(ctx, q: torch.Tensor, cache: ops.KvLayerView, heads: int, wi
     if work["n_dec"]:
         limit = view.table_stride * view.page_size
         max_keys = limit if work["max_pos"] is None else work["max_pos"] + 1
-        tps = decode_tiles_per_slice(work["n_dec"], view.kv_heads, max_keys)
-        max_slices = -(-max_keys // (tps * decode_tile()))
+        stream_map, stream_row0 = cache.tma() if DECODE_KERNEL == "stream" and stream_pays(work["n_dec"], view.kv_heads, q.device) else (None, 0)
+        if stream_map:
+            tps = STREAM_TILES_PER_SLICE
+            max_slices = -(-max_keys // (tps * decode_tile())) if tps else stream_slices(work["n_dec"], view.kv_heads, max_keys, q.device)
+            kv_map, row0 = stream_map, stream_row0
+        else:
+            tps = decode_tiles_per_slice(work["n_dec"], view.kv_heads, max_keys)
+            max_slices = -(-max_keys // (tps * decode_tile()))
+            kv_map, row0 = cache.tma() if USE_TMA and decode_tile() % view.page_size == 0 else (None, 0)
         skey = ("decode_scratch", heads, view.head_dim, max_slices)
         if skey not in ctx.memo:
             n = work["n_dec"] * heads * max_slices
             ctx.memo[skey] = (rt.empty((n * view.head_dim,), torch.float32), rt.empty((n * 2,), torch.float32))
         part_o, part_ml = ctx.memo[skey]
-        kv_map, row0 = cache.tma() if USE_TMA else (None, 0)
-        L.call("ib_attention_decode", q.data_ptr(), C.byref(view), work["dec_tokens"].data_ptr(), work["n_dec"], ctx.positions.data_ptr(),
-               ctx.seg_of_token.data_ptr(), int(window or 0), float(scale), part_o.data_ptr(), part_ml.data_ptr(), out.data_ptr(), heads,
-               max_slices, tps, kv_map, row0, rt.status.data_ptr(), stream)
+        L.call("ib_attention_decode_stream" if stream_map else "ib_attention_decode", q.data_ptr(), C.byref(view), work["dec_tokens"].data_ptr(),
+               work["n_dec"], ctx.positions.data_ptr(), ctx.seg_of_token.data_ptr(), int(window or 0), float(scale), part_o.data_ptr(),
+               part_ml.data_ptr(), out.data_ptr(), heads, max_slices, tps, kv_map, row0, rt.status.data_ptr(), stream)
     if work["n_tiles"]:
         L.call("ib_attention_prefill_tc" if PREFILL_KERNEL == "tcgen05" else "ib_attention_prefill", q.data_ptr(), C.byref(view), work["tile_seg"].data_ptr(), work["tile_row0"].data_ptr(), work["n_tiles"],
                ctx.seg_start.data_ptr(), ctx.seg_pos0.data_ptr(), int(window or 0), float(scale), out.data_ptr(), heads, rt.status.data_ptr(),

@@ -49,9 +49,9 @@ def kv_tensor_map(pool: torch.Tensor):
     cannot be served by TMA (the attention kernels then copy with cp.async)."""
     key = (pool.data_ptr(), tuple(pool.shape), pool.dtype)
     if key not in _KV_MAPS:
-        pages, entries, two, kv_heads, page_size, head_dim = pool.shape
+        entries, pages, two, kv_heads, page_size, head_dim = pool.shape
         made = None
-        if pool.dtype == torch.bfloat16 and head_dim % 64 == 0 and page_size % 8 == 0 and page_size <= 64 and 64 % page_size == 0:
+        if pool.dtype == torch.bfloat16 and head_dim % 64 == 0 and page_size % 8 == 0 and (64 % page_size == 0 or page_size % 64 == 0):
             buf = C.create_string_buffer(128 + 64)
             addr = (C.addressof(buf) + 63) & ~63
             lib = L.load()
@@ -66,27 +66,27 @@ def kv_tensor_map(pool: torch.Tensor):
 @dataclass
 class KvLayerView:
     """One layer's keys and values inside a paged pool, plus the block table of the step."""
-    pool: torch.Tensor          # [pages, entries, 2, kv_heads, page_size, head_dim]
+    pool: torch.Tensor          # [entries, pages, 2, kv_heads, page_size, head_dim]: one layer's pages lie together
     entry: int
     block_table: torch.Tensor   # int32 [segments, table_stride]
 
     def tma(self) -> tuple[Optional[int], int]:
         """(address of the pool's tensor map or None, pool row where this view's keys of page 0, head 0 start)."""
         m = kv_tensor_map(self.pool)
-        _, _, _, kv_heads, page_size, _ = self.pool.shape
-        return (m[1] if m else None), self.entry * 2 * kv_heads * page_size
+        _, pages, _, kv_heads, page_size, _ = self.pool.shape
+        return (m[1] if m else None), self.entry * pages * 2 * kv_heads * page_size
 
     def c_view(self) -> L.KvView:
-        pages, entries, two, kv_heads, page_size, head_dim = self.pool.shape
+        entries, pages, two, kv_heads, page_size, head_dim = self.pool.shape
         if two != 2:
-            raise L.KernelError(f"a KV pool must be [pages, entries, 2, kv_heads, page_size, head_dim], got {tuple(self.pool.shape)}")
+            raise L.KernelError(f"a KV pool must be [entries, pages, 2, kv_heads, page_size, head_dim], got {tuple(self.pool.shape)}")
         _check("kv pool", self.pool)
         _check("block_table", self.block_table, torch.int32)
         per_kv = kv_heads * page_size * head_dim
         esz = self.pool.element_size()
         return L.KvView(
-            base=self.pool.data_ptr() + self.entry * 2 * per_kv * esz,
-            page_stride=entries * 2 * per_kv,
+            base=self.pool.data_ptr() + self.entry * pages * 2 * per_kv * esz,
+            page_stride=2 * per_kv,
             v_offset=per_kv,
             block_table=self.block_table.data_ptr(),
             table_stride=self.block_table.shape[1],

@@ -198,7 +198,7 @@ def _paged(contexts, page_size, dtype, seed, entries=2, entry=1):
     order = np.random.default_rng(seed).permutation(total)
     width = max(need) + 2
     table = np.full((len(contexts), width), -1, dtype=np.int32)
-    pool = torch.zeros(total, entries, 2, kvh, page_size, hd, dtype=dtype)
+    pool = torch.full((entries, total, 2, kvh, page_size, hd), 37.0, dtype=dtype)   # rows that hold no key: finite, and loud if a mask lets one through
     at = 0
     for s, (k, v) in enumerate(contexts):
         for p in range(need[s]):
@@ -206,8 +206,8 @@ def _paged(contexts, page_size, dtype, seed, entries=2, entry=1):
             table[s, p] = page
             rows = slice(p * page_size, min((p + 1) * page_size, k.shape[0]))
             n = rows.stop - rows.start
-            pool[page, entry, 0, :, :n] = k[rows].transpose(0, 1).to(dtype)
-            pool[page, entry, 1, :, :n] = v[rows].transpose(0, 1).to(dtype)
+            pool[entry, page, 0, :, :n] = k[rows].transpose(0, 1).to(dtype)
+            pool[entry, page, 1, :, :n] = v[rows].transpose(0, 1).to(dtype)
     return KvLayerView(pool.to(DEV), entry, torch.from_numpy(table).to(DEV)), table
 
 
@@ -274,25 +274,64 @@ def test_attention_tensor_core_kernels(status, monkeypatch, hd, heads, kvh, page
 
 
 @pytest.mark.parametrize("tiles_per_slice", [1, 2, 8])
-@pytest.mark.parametrize("tma,page,hd", [(True, 16, 128), (True, 64, 64), (True, 8, 128), (False, 16, 128), (False, 24, 64)])
-def test_attention_decode_slices_of_several_tiles(status, monkeypatch, tiles_per_slice, tma, page, hd):
-    """The decode kernel walking 1, 2 or 8 tiles per CTA, windows starting inside a slice included,
-    with keys and values brought by TMA or by cp.async (a page size of 24 can only go the second way)."""
+@pytest.mark.parametrize("kernel,tma,page,hd", [("stream", False, 16, 128), ("stream", False, 64, 64), ("stream", False, 8, 128), ("stream", False, 128, 128),
+                                                ("stream", False, 32, 64), ("stream", False, 24, 64), ("split", True, 16, 128), ("split", True, 64, 64),
+                                                ("split", True, 8, 128), ("split", False, 16, 128), ("split", False, 24, 64), ("split", False, 128, 64)])
+def test_attention_decode_slices_of_several_tiles(status, monkeypatch, tiles_per_slice, kernel, tma, page, hd):
+    """Both decode kernels (CTAs that stay and a ring filled by TMA; one CTA per slice, filled by TMA
+    or by cp.async) walking 1, 2 or 8 tiles per slice, windows starting inside a slice included. A page
+    size of 24 can only be copied by cp.async, so it takes the kernel with one CTA per slice either way."""
     from inference_bench_b200.engine.context import Segment, build_context
     from inference_bench_b200.engine.runtime import Runtime
     from inference_bench_b200.kernels import attention
+    from inference_bench_b200.kernels import lib as L
     monkeypatch.setattr(attention, "decode_tiles_per_slice", lambda *a: tiles_per_slice)
+    monkeypatch.setattr(attention, "STREAM_TILES_PER_SLICE", tiles_per_slice)
+    monkeypatch.setattr(attention, "STREAM_ALWAYS", True)
+    monkeypatch.setattr(attention, "DECODE_KERNEL", kernel)
     monkeypatch.setattr(attention, "USE_TMA", tma)
+    called = []
+    real_call = L.call
+    monkeypatch.setattr(L, "call", lambda name, *a: (called.append(name), real_call(name, *a))[1])
     heads, kvh = 8, 2
-    shapes = [(1000, 1), (64, 1), (65, 1), (513, 1), (1, 1), (2047, 1)]
+    shapes = [(1000, 1), (64, 1), (65, 1), (513, 1), (1, 1), (2047, 1), (128, 1), (192, 1), (193, 1)]
     for window in (None, 300):
         q, view, pos, seg, ref, _ = _attention_case(torch.bfloat16, heads, kvh, hd, page, window, shapes, 21, needle=True)
         assert (view.tma()[0] is not None) == (page != 24)
         rt = Runtime(DEV, "bfloat16")
-        ctx = build_context(rt, [Segment(i, i, L - n, [0] * n) for i, (L, n) in enumerate(shapes)])
+        ctx = build_context(rt, [Segment(i, i, L_ - n, [0] * n) for i, (L_, n) in enumerate(shapes)])
         out = attention.paged_attention(ctx, q, view, heads, window, 1 / math.sqrt(hd))
         rt.check_status()
-        assert (out.cpu().double() - ref).abs().max() <= 1.5e-2 * ref.abs().max()
+        err = (out.cpu().double() - ref).abs()
+        assert err.max() <= 1.5e-2 * ref.abs().max(), f"row {int(err.max(dim=1).values.argmax())} is off by {err.max():.3e}"
+    assert called[-1] == ("ib_attention_decode_stream" if kernel == "stream" and page != 24 else "ib_attention_decode")
+
+
+def test_attention_decode_stream_many_units_per_cta(status, monkeypatch):
+    """More units than CTAs that fit the device, with contexts of very different lengths: every CTA
+    of the streaming kernel walks several units, and its ring runs across their ends."""
+    from inference_bench_b200.engine.context import Segment, build_context
+    from inference_bench_b200.engine.runtime import Runtime
+    from inference_bench_b200.kernels import attention
+    heads, kvh, hd, page = 8, 8, 128, 16
+    shapes = [(L_, 1) for L_ in (1500, 3, 700, 64, 1100, 129, 1, 900, 1300, 450, 31, 640)]
+    rt = Runtime(DEV, "bfloat16")
+    monkeypatch.setattr(attention, "STREAM_ALWAYS", True)
+    for fixed, window in ((1, None), (0, None), (0, 500), (0, 70)):   # slices of one tile at fixed places; each token's keys in equal parts
+        monkeypatch.setattr(attention, "STREAM_TILES_PER_SLICE", fixed)
+        q, view, pos, seg, ref, _ = _attention_case(torch.bfloat16, heads, kvh, hd, page, window, shapes, 22, needle=True)
+        ctx = build_context(rt, [Segment(i, i, L_ - n, [0] * n) for i, (L_, n) in enumerate(shapes)])
+        out = attention.paged_attention(ctx, q, view, heads, window, 1 / math.sqrt(hd))
+        rt.check_status()
+        err = (out.cpu().double() - ref).abs()
+        assert err.max() <= 1.5e-2 * ref.abs().max(), f"row {int(err.max(dim=1).values.argmax())} is off by {err.max():.3e}"
+
+
+@pytest.mark.parametrize("n_dec,kv_heads,max_keys,want", [(8, 8, 4096, 4), (1, 8, 2048, 16), (64, 8, 4096, 4), (1, 8, 100, 1), (300, 1, 4096, 6), (37, 8, 65536, 1)])
+def test_stream_slices(n_dec, kv_heads, max_keys, want):
+    from inference_bench_b200.kernels import attention
+    if torch.cuda.get_device_properties(DEV).multi_processor_count == 148:
+        assert attention.stream_slices(n_dec, kv_heads, max_keys, torch.device(DEV)) == want
 
 
 def test_attention_reports_missing_page(status):
@@ -340,9 +379,9 @@ def test_qk_norm_rope_kv(status, dtype, hd, rot):
     for t in range(T):
         p = pos0 + t
         pg = table[0, p // page]
-        assert (pool[pg, 1, 0, :, p % page] - k[t]).abs().max() <= tol * k.abs().max()
-        assert (pool[pg, 1, 1, :, p % page] - v[t]).abs().max() <= tol * v.abs().max()
-    assert pool[:, 0].abs().max() == 0   # the other layer's place in the pages is untouched
+        assert (pool[1, pg, 0, :, p % page] - k[t]).abs().max() <= tol * k.abs().max()
+        assert (pool[1, pg, 1, :, p % page] - v[t]).abs().max() <= tol * v.abs().max()
+    assert (pool[0] == 37.0).all()   # the other layer's place in the pages is untouched
 
 
 # ------------------------------------------------------------------------------------------ sampling

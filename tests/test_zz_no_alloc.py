@@ -28,7 +28,7 @@ def _case(seed, heads, kvh, hd, page, lengths):
     need = [-(-L // page) for L in lengths]
     total = sum(need) + 3
     order = np.random.default_rng(seed).permutation(total)
-    pool = (torch.randn(total, 1, 2, kvh, page, hd, generator=g)).to(torch.bfloat16)
+    pool = (torch.randn(1, total, 2, kvh, page, hd, generator=g)).to(torch.bfloat16)
     table = np.full((n, max(need) + 1), -1, dtype=np.int32)
     at = 0
     for s in range(n):
