@@ -23,7 +23,7 @@ constexpr int BM = 128;      // rows of W per CTA (256 per pair)
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
 constexpr int kThreads = 192;
-constexpr int EPI_STORE = 0, EPI_SWIGLU = 1;
+constexpr int EPI_STORE = 0, EPI_SWIGLU = 1, EPI_ADD = 2;   // float32 out; bfloat16 silu(gate) * up; float32 out += product
 constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;   // clears the bit that tells the two CTAs of a pair apart in a shared::cluster address
 
 // BN: tokens per tile = accumulator columns (each CTA loads half of them)
@@ -209,7 +209,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       sm100::tc_fence_after();
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      if constexpr (EPI == EPI_STORE) {
+      if constexpr (EPI == EPI_STORE || EPI == EPI_ADD) {
         float* dst = (float*)out_;
 #pragma unroll 1
         for (int m = 0; m < MT; m++) {
@@ -220,6 +220,13 @@ __global__ void __launch_bounds__(kThreads, 1)
             sm100::tmem_ld_32x32b_x32(lane_addr + b * MT * BN + m * BN + c0, r);
             sm100::tmem_ld_wait();
             if (n < N) {
+              if constexpr (EPI == EPI_ADD) {   // every element belongs to one thread of one CTA: a plain read, add, write
+                float old[32];
+#pragma unroll
+                for (int c = 0; c < 32; c++) old[c] = t0 + c0 + c < T ? dst[(size_t)(t0 + c0 + c) * N + n] : 0.f;
+#pragma unroll
+                for (int c = 0; c < 32; c++) r[c] = __float_as_uint(old[c] + __uint_as_float(r[c]));
+              }
 #pragma unroll
               for (int c = 0; c < 32; c++) {
                 const int t = t0 + c0 + c;
@@ -324,6 +331,12 @@ int launch(const void* x, const void* w, void* out, int T, int N, int K, int w_r
 extern "C" int ib_gemm_tcgen05_2cta(const void* x, const void* w, float* out, int T, int N, int K, unsigned* status, cudaStream_t stream) {
   if (T == 0 || N == 0) return 0;
   return launch<1, EPI_STORE, 256>(x, w, out, T, N, K, N, 0, status, stream);
+}
+
+// The same product added to what out [T, N] float32 holds (the residual stream), in place.
+extern "C" int ib_gemm_tcgen05_2cta_add(const void* x, const void* w, float* out, int T, int N, int K, unsigned* status, cudaStream_t stream) {
+  if (T == 0 || N == 0) return 0;
+  return launch<1, EPI_ADD, 256>(x, w, out, T, N, K, N, 0, status, stream);
 }
 
 // w [2*I, K] = gate rows then up rows -> act [T, I] bfloat16 = silu(x gate^T) * (x up^T), on CTA pairs.

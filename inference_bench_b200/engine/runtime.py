@@ -70,9 +70,11 @@ class Runtime:
         return self.upload(w, torch.float32)
 
     # ---------------------------------------------------------------- matrix product
-    def linear(self, x: torch.Tensor, lw: LinearWeights, allow_split: bool = True) -> torch.Tensor:
+    def linear(self, x: torch.Tensor, lw: LinearWeights, allow_split: bool = True, add_to: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """x [T, K] in the activation dtype -> partial products float32 [P, T, N]; their sum over P,
-        taken in order, is x @ W^T."""
+        taken in order, is x @ W^T. With `add_to` (float32 [T, N], the residual stream) a kernel that
+        can add the product in its epilogue does so in place and None is returned: nothing is left
+        to add. Otherwise the partial products come back as usual and `add_to` is untouched."""
         T = x.shape[0]
         if x.shape[1] != lw.k:
             raise L.KernelError(f"linear: x has {x.shape[1]} columns, the matrix has {lw.k}")
@@ -80,7 +82,7 @@ class Runtime:
         if use_tc:
             from ..kernels import gemm_tcgen05
             if gemm_tcgen05.supports(lw.k):
-                return gemm_tcgen05.linear(self, x, lw, allow_split)
+                return gemm_tcgen05.linear(self, x, lw, allow_split, add_to)
             if self.gemm == "tcgen05":
                 raise L.KernelError(f"linear: K={lw.k} is not a multiple of 8, which the tcgen05 kernel needs")
         out = self.empty((1, T, lw.n), torch.float32)

@@ -7,6 +7,8 @@ sizes of the product (T, N, K), never on which requests make up the batch.
 """
 from __future__ import annotations
 
+from typing import Optional
+
 import torch
 
 from . import lib as L
@@ -19,6 +21,7 @@ L.register("ib_gemm_tcgen05", [L._p, L._p, L._p, L._i, L._i, L._i, L._i, L._i, L
 L.register("ib_gemm_swiglu_tcgen05", [L._p, L._p, L._p, L._i, L._i, L._i, L._i, L._p, L._p])
 L.register("ib_gemm_tcgen05_2cta", [L._p, L._p, L._p, L._i, L._i, L._i, L._p, L._p])
 L.register("ib_gemm_swiglu_tcgen05_2cta", [L._p, L._p, L._p, L._i, L._i, L._i, L._p, L._p])
+L.register("ib_gemm_tcgen05_2cta_add", [L._p, L._p, L._p, L._i, L._i, L._i, L._p, L._p])
 
 PAIR_MIN_TOKENS = 256   # from here on the persistent CTA-pair kernels (csrc/gemm_tcgen05_2cta.cu) take over
 
@@ -67,19 +70,23 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bn: int, splits: i
     L.call("ib_gemm_tcgen05", x.data_ptr(), w.data_ptr(), out.data_ptr(), T, N, K, bn, splits, 1 if wide else 0, status.data_ptr(), ops._stream())
 
 
-def gemm_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> None:
-    """out [T, N] float32 = x [T, K] w[N, K]^T on CTA pairs (256 x 256 tiles, persistent)."""
+def gemm_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch.Tensor, add: bool = False) -> None:
+    """out [T, N] float32 = x [T, K] w[N, K]^T on CTA pairs (256 x 256 tiles, persistent); with `add`
+    the product is added to what out holds."""
     T, K = x.shape
     N = w.shape[0]
     ops._check("x", x, torch.bfloat16)
     ops._check("w", w, torch.bfloat16, (N, K))
     ops._check("out", out, torch.float32, (T, N))
-    L.call("ib_gemm_tcgen05_2cta", x.data_ptr(), w.data_ptr(), out.data_ptr(), T, N, K, status.data_ptr(), ops._stream())
+    L.call("ib_gemm_tcgen05_2cta_add" if add else "ib_gemm_tcgen05_2cta", x.data_ptr(), w.data_ptr(), out.data_ptr(), T, N, K, status.data_ptr(), ops._stream())
 
 
-def linear(rt, x: torch.Tensor, lw, allow_split: bool = True) -> torch.Tensor:
+def linear(rt, x: torch.Tensor, lw, allow_split: bool = True, add_to: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
     T = x.shape[0]
     if T >= PAIR_MIN_TOKENS:
+        if add_to is not None:
+            gemm_pair(x, lw.weight, add_to, rt.status, add=True)
+            return None
         out = rt.empty((1, T, lw.n), torch.float32)
         gemm_pair(x, lw.weight, out[0], rt.status)
         return out

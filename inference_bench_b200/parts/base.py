@@ -80,17 +80,23 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    adds_to_residual = False   # True: forward takes `residual=` and may add its contribution there itself
+
     def cache_need(self) -> CacheNeed:
         return None
 
     def forward(self, ctx: "StepContext", h: torch.Tensor, cache) -> torch.Tensor:
         """h: normalised activations [T, H]; cache: what the cache manager gave this execution
         (a KvLayerView for PagedKV, a StateView for FixedState, None otherwise).
-        Returns the residual contribution, float32 [P, T, H] (P partial sums, added in order)."""
+        Returns the residual contribution, float32 [P, T, H] (P partial sums, added in order).
+        A part with `adds_to_residual` is called with `residual=x` (float32 [T, H]) as well: it may
+        add its contribution to x in place and return None, or leave x alone and return the partial sums."""
         raise NotImplementedError
 
 
 class FeedForward(Part):
+    adds_to_residual = False   # as for a mixer
+
     def forward(self, ctx: "StepContext", h: torch.Tensor) -> torch.Tensor:
         """Returns the residual contribution, float32 [P, T, H]."""
         raise NotImplementedError

@@ -127,7 +127,9 @@ class Attention(base.Mixer):
                 self.k_norm = rt.vector(weights[f"{p}.k_norm.weight"])
         self.position.bind(weights, rt)
 
-    def forward(self, ctx, h, cache):
+    adds_to_residual = True   # the output projection may add to the residual stream in its epilogue
+
+    def forward(self, ctx, h, cache, residual=None):
         rt = ctx.rt
         qkv = rt.linear(h, self.wqkv)
         cos, sin = self.position.tables(ctx)
@@ -136,7 +138,7 @@ class Attention(base.Mixer):
                             rt.status, write_kv=self.own_kv)
         from ..kernels import attention
         out = attention.paged_attention(ctx, q, cache, self.heads, self.window, self.scale)
-        return rt.linear(out, self.wo)
+        return rt.linear(out, self.wo, add_to=residual)
 
 
 # ------------------------------------------------------------------------------------------ feed-forward
@@ -160,9 +162,11 @@ class SwiGLU(base.FeedForward):
         self.wgu = rt.matrix(torch.cat([weights[f"{p}.gate_proj.weight"], weights[f"{p}.up_proj.weight"]], dim=0))
         self.wd = rt.matrix(weights[f"{p}.down_proj.weight"])
 
-    def forward(self, ctx, h):
+    adds_to_residual = True   # the down projection may add to the residual stream in its epilogue
+
+    def forward(self, ctx, h, residual=None):
         rt = ctx.rt
-        return rt.linear(rt.gate_up_act(h, self.wgu), self.wd)
+        return rt.linear(rt.gate_up_act(h, self.wgu), self.wd, add_to=residual)
 
 
 # ------------------------------------------------------------------------------------------ embedding and head
@@ -215,6 +219,6 @@ class PreNormBlock(base.Block):
 
     def forward(self, ctx, x, pending, cache):
         h = self.mixer_norm.forward(ctx, x, pending)
-        a = self.mixer.forward(ctx, h, cache)
+        a = self.mixer.forward(ctx, h, cache, residual=x) if self.mixer.adds_to_residual else self.mixer.forward(ctx, h, cache)
         h = self.feed_forward_norm.forward(ctx, x, a)
-        return self.feed_forward.forward(ctx, h)
+        return self.feed_forward.forward(ctx, h, residual=x) if self.feed_forward.adds_to_residual else self.feed_forward.forward(ctx, h)

@@ -97,6 +97,11 @@ def test_gemm_tcgen05_cta_pairs(status, T, N, K):
     G.gemm_pair(x, w, out, status)
     ref = x.double() @ w.double().T
     assert status.item() == 0 and (out.double() - ref).abs().max() <= 2e-5 * ref.abs().max() + 1e-6
+    # the same product added to a residual stream in place
+    base = torch.randn(T, N, generator=_g(7)).to(DEV) * 3
+    acc = base.clone()
+    G.gemm_pair(x, w, acc, status, add=True)
+    assert status.item() == 0 and torch.equal(acc, base + out)
 
 
 @pytest.mark.parametrize("T,I,K", [(256, 128, 64), (300, 520, 264), (1000, 1000, 1024), (2048, 20000, 128)])
