@@ -42,10 +42,11 @@ class Engine:
     def __init__(self, model: Union[str, Path, Mapping[str, Any]], dtype: str = "bfloat16", max_ctx: Optional[int] = None,
                  page_size: int = 16, num_pages: Optional[int] = None, kv_gb: Optional[float] = None, max_num_seqs: int = 64,
                  max_batched_tokens: int = 8192, prefill_chunk: int = 2048, random_weights_seed: Optional[int] = None,
-                 device: str = "cuda:0", use_graphs: bool = True):
+                 device: str = "cuda:0", use_graphs: bool = True, pipeline: bool = True):
         """model: a folder with config.json and model.safetensors, or (with random_weights_seed) a raw
         config.json mapping whose weights are then made on the device. num_pages / kv_gb size the
-        cache pool; by default it holds max_num_seqs requests of max_ctx tokens, capped by free memory."""
+        cache pool; by default it holds max_num_seqs requests of max_ctx tokens, capped by free memory.
+        pipeline: keep decode steps one ahead of the host (see engine/scheduler.py)."""
         self.rt = Runtime(device, dtype)
         if isinstance(model, Mapping):
             if random_weights_seed is None:
@@ -70,7 +71,7 @@ class Engine:
                                   sources=self.decoder.cache_sources())
         self.runner = ModelRunner(self.decoder, self.cache, self.rt)
         self.executor = GpuExecutor(self.runner, use_graphs=use_graphs)
-        self.scheduler = Scheduler(self.cache, SchedulerConfig(max_num_seqs, max_batched_tokens, prefill_chunk, self.max_ctx))
+        self.scheduler = Scheduler(self.cache, SchedulerConfig(max_num_seqs, max_batched_tokens, prefill_chunk, self.max_ctx, pipeline))
         self._tokenizer = None
         self._next_id = 0
 

@@ -54,6 +54,12 @@ class _DecodeGraph:
         self.h_history = torch.zeros((RUN_AHEAD_MAX, B), dtype=torch.int32).pin_memory()
         self.tokens = torch.zeros(B, dtype=torch.int32, device=rt.device)
         self.h_out = torch.zeros(B, dtype=torch.int32).pin_memory()
+        # for steps launched without waiting (two may be in flight): a staging copy of the inputs, a place for the tokens and an event each
+        self.stages = [torch.zeros(self.n_ints, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self.h_outs = [torch.zeros(B, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self.events = [torch.cuda.Event() for _ in range(2)]
+        self.pending = [False, False]
+        self.turn = 0
         self.logits: Optional[torch.Tensor] = None
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self._pad_all()
@@ -115,14 +121,41 @@ class _DecodeGraph:
         torch.cuda.current_stream().synchronize()
         return self.h_out[:n].tolist()
 
-    def _fill(self, entries: list[StepEntry], sampling: list[tuple[SamplingParams, int]]) -> None:
+    def launch(self, entries: list[StepEntry], sampling: list[tuple[SamplingParams, int]], feed: bool) -> tuple[int, int]:
+        """Enqueue one step and return at once. With `feed` the input tokens stay what the step before
+        left on the device (its sampled tokens, row by row): everything but the tokens is copied."""
+        slot = self.turn
+        if self.pending[slot]:
+            raise RuntimeError("two decode steps are already in flight")
+        self.turn ^= 1
+        self._fill(entries, sampling, tokens=not feed)
+        stage = self.stages[slot]
+        stage.copy_(self.host)
+        if feed:
+            self.dev[self.rows:].copy_(stage[self.rows:], non_blocking=True)
+        else:
+            self.dev.copy_(stage, non_blocking=True)
+        self.graph.replay()
+        self.h_outs[slot].copy_(self.tokens, non_blocking=True)
+        self.events[slot].record()
+        self.pending[slot] = True
+        return slot, len(entries)
+
+    def collect(self, handle: tuple[int, int]) -> list[int]:
+        slot, n = handle
+        self.events[slot].synchronize()
+        self.pending[slot] = False
+        return self.h_outs[slot][:n].tolist()
+
+    def _fill(self, entries: list[StepEntry], sampling: list[tuple[SamplingParams, int]], tokens: bool = True) -> None:
         cache = self.runner.cache
         n = len(entries)
         if n < self.rows:
             self._pad_all()
         reqs = [cache._get(e.request) for e in entries]
         pos = [r.length for r in reqs]
-        self.h_tokens[:n] = [e.tokens[0] for e in entries]
+        if tokens:
+            self.h_tokens[:n] = [e.tokens[0] for e in entries]
         self.h_pos[:n] = pos
         self.h_pos0[:n] = pos
         self.h_slot[:n] = [r.slot for r in reqs]
@@ -166,6 +199,37 @@ class GpuExecutor:
         self.h2d_bytes += g.n_ints * 4
         self.d2h_bytes += steps * g.rows * 4
         return out
+
+    def launch_decode(self, entries: list[StepEntry], sampling: list[tuple[SamplingParams, int]], feed: bool = False):
+        """Enqueue a step of single decoded tokens without waiting for it; `collect` returns its tokens.
+        With `feed`, every row's input token is the one the step before sampled for it, taken on the
+        device. None when such a step cannot run as a graph. Raises OutOfPages with nothing changed."""
+        if not self.use_graphs or len(entries) > self.max_graph_rows:
+            return None
+        cache = self.runner.cache
+        if not feed:
+            for e in entries:
+                if not 0 <= e.tokens[0] < self.runner.vocab:
+                    raise ValueError(f"request {e.request!r}: token id {e.tokens[0]} is outside the vocabulary of {self.runner.vocab}")
+        g = self.graph_for(len(entries))
+        try:
+            for e in entries:
+                cache.extend(e.request, cache.length(e.request) + 1)
+        except Exception:
+            for e in entries:
+                cache.shrink_to_committed(e.request)
+            raise
+        handle = g.launch(entries, sampling, feed)
+        for e in entries:
+            cache.commit(e.request, cache.length(e.request) + 1)
+        self.steps += 1
+        self.h2d_bytes += (g.n_ints - (g.rows if feed else 0)) * 4
+        self.d2h_bytes += g.rows * 4
+        return g, handle
+
+    def collect(self, handle) -> list[int]:
+        g, h = handle
+        return g.collect(h)
 
     def execute(self, entries: list[StepEntry], sampling: list[tuple[SamplingParams, int]]) -> list[int]:
         self.steps += 1

@@ -16,6 +16,13 @@ Policy, after the reference's scheduler (crates/specrt/src/sched.rs; docs/specrt
   * the last portion of a prompt samples the first token (sched.rs:1496-1497);
   * a request finishes on a stop token (not emitted), at max_tokens, or at the context limit
     (sched.rs:1577-1589), and gives back its pages and slot at once.
+
+While every running request decodes and none waits, steps are kept one ahead (`pipeline`): an executor
+that can enqueue a decode step without waiting for it (`launch_decode` / `collect`) is given the next
+step, whose input tokens it takes from the step before on the device, before the tokens of the
+current step are read back; the host's share of a step then runs while the device computes. A
+request that stops on a token the host had not seen yet has computed one token too many, which is
+dropped. Every call of `step` still reports exactly one step.
 """
 from __future__ import annotations
 
@@ -38,6 +45,7 @@ class SchedulerConfig:
     max_batched_tokens: int = 8192    # tokens in one step, decode rows included (sched.rs:503-538)
     prefill_chunk: int = 2048         # longest portion of one prompt in one step (runtime.rs:801)
     max_ctx: int = 2048               # context limit: prompt + generated tokens (engine.rs:10)
+    pipeline: bool = True             # keep decode steps one ahead when the executor can launch without waiting
 
 
 @dataclass
@@ -90,6 +98,18 @@ class Executor(Protocol):
     def execute(self, entries: list[StepEntry], sampling: list[tuple[SamplingParams, int]]) -> list[int]:
         """Run one step; `sampling[i]` belongs to the i-th wanted row. Returns one token per wanted row."""
 
+    # Optional, for steps kept one ahead:
+    #   launch_decode(entries, sampling, feed) -> handle or None: enqueue a step of single decoded tokens
+    #     (cache extended and committed as `execute` does) without waiting; with `feed` the input tokens are
+    #     the tokens the step before sampled for the same rows, and entries[i].tokens is ignored. None: cannot.
+    #   collect(handle) -> list[int]: wait for that step and return its tokens. Handles are collected in order.
+
+
+@dataclass
+class _InFlight:
+    handle: Any
+    owners: list["Sequence_"]
+
 
 class Scheduler:
     def __init__(self, cache: CacheManager, config: SchedulerConfig):
@@ -98,6 +118,7 @@ class Scheduler:
         self.running: list[Sequence_] = []
         self._order = 0
         self.total_preemptions = 0
+        self._inflight: Optional[_InFlight] = None   # a launched decode step whose tokens have not been read
 
     # ------------------------------------------------------------------ submit / cancel
     def submit(self, req: Request) -> None:
@@ -133,6 +154,10 @@ class Scheduler:
 
     # ------------------------------------------------------------------ one step
     def step(self, executor: Executor) -> StepReport:
+        if self._inflight is not None or (self.cfg.pipeline and hasattr(executor, "launch_decode")):
+            ahead = self._step_ahead(executor)
+            if ahead is not None:
+                return ahead
         report = StepReport()
         self._grow_decoders(report)
         decoders = [s for s in self.running if s.decoding]
@@ -170,6 +195,47 @@ class Scheduler:
             s.computed += n
         for s, tok in zip(owners, tokens):
             self._accept(s, int(tok), report)
+        return report
+
+    # ------------------------------------------------------------------ steps kept one ahead
+    def _step_ahead(self, executor) -> Optional[StepReport]:
+        """One step's report while decode steps are kept one ahead; None when this step has to run the ordinary way."""
+        fl = self._inflight
+        steady = bool(self.running) and not self.waiting and all(s.decoding for s in self.running)
+        same = fl is not None and len(fl.owners) == len(self.running) and all(a is b for a, b in zip(fl.owners, self.running))
+        if fl is not None and not (steady and same):    # the batch changes: read what is in flight, start afresh next time
+            self._inflight = None
+            return self._collect(executor, fl)
+        if not steady:
+            return None
+        if fl is None:
+            fl = self._launch(executor, feed=False, ahead=0)
+            if fl is None:
+                return None
+        limit = min(self.cfg.max_ctx, self.cache.max_tokens_per_request)
+        goes_on = all(s.generated + 1 < s.req.max_tokens and len(s.tokens) + 1 < limit for s in fl.owners)
+        self._inflight = self._launch(executor, feed=True, ahead=1) if goes_on else None
+        return self._collect(executor, fl)
+
+    def _launch(self, executor, feed: bool, ahead: int) -> Optional[_InFlight]:
+        owners = list(self.running)
+        entries = [StepEntry(s.req.id, [0 if feed else s.tokens[-1]], [0]) for s in owners]
+        sampling = [(s.req.sampling, s.generated + ahead) for s in owners]
+        try:
+            handle = executor.launch_decode(entries, sampling, feed)
+        except OutOfPages:
+            return None
+        return None if handle is None else _InFlight(handle, owners)
+
+    def _collect(self, executor, fl: _InFlight) -> StepReport:
+        report = StepReport(decode_rows=len(fl.owners))
+        tokens = executor.collect(fl.handle)
+        if len(tokens) != len(fl.owners):
+            raise RuntimeError(f"the executor returned {len(tokens)} tokens for {len(fl.owners)} rows")
+        for s, tok in zip(fl.owners, tokens):
+            if any(s is r for r in self.running):       # else it stopped or was cancelled after the launch: the token is dropped
+                s.computed += 1
+                self._accept(s, int(tok), report)
         return report
 
     # ------------------------------------------------------------------ pieces of the policy

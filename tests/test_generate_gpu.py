@@ -115,3 +115,43 @@ def test_preemption_when_pages_run_out_gives_the_same_tokens(model_dirs):
     for i, (p, n) in enumerate(zip(prompts, news)):
         assert done[i] == plain.greedy(p, n), f"request {i}"
     assert eng.cache.used_pages() == [0]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_kept_one_ahead_change_no_token(model_dirs, dtype):
+    """Decode steps launched before the tokens of the step before are read back (the default) against
+    the same engine with that off: greedy and seeded sampling, different lengths, a stop token in the
+    middle of the run, a request that arrives later."""
+    from inference_bench_b200 import SamplingParams
+    name = "B"
+    vocab = CONFIGS[name]["config"]["vocab_size"]
+    prompts = [traces.prompt(90 + i, n, vocab) for i, n in enumerate((9, 21, 4, 30))]
+    sp = [SamplingParams(), SamplingParams(temperature=0.9, seed=3), SamplingParams(temperature=1.2, seed=4, top_k=20), SamplingParams()]
+    outs = {}
+    for pipeline in (False, True):
+        eng = _engine(model_dirs, name, dtype, pipeline=pipeline)
+        free = eng.generate(prompts, max_tokens=24, sampling=sp)
+        stop = free[0].tokens[10]                                # request 0 then stops at its 11th token at the latest
+        first = free[0].tokens.index(stop)
+        stopped = eng.generate(prompts, max_tokens=24, sampling=sp, stop_ids=[stop])
+        assert stopped[0].finish == "stop" and stopped[0].tokens == free[0].tokens[:first]
+        # submit / step by hand: a request that arrives while two steps are in flight
+        a = eng.submit(prompts[1], max_tokens=12, sampling=sp[1])
+        got = {a: []}
+        for i in range(60):
+            if i == 5:
+                b = eng.submit(prompts[3], max_tokens=7)
+                got[b] = []
+            rep = eng.step()
+            for rid, tok in rep.emitted:
+                got[rid].append(tok)
+            if eng.scheduler.idle():
+                break
+        if dtype == "float32":                                   # bfloat16 may round differently in another batch
+            assert got[a] == free[1].tokens[:12] and got[b] == free[3].tokens[:7]
+        assert len(got[a]) == 12 and len(got[b]) == 7
+        eng.rt.check_status()
+        eng.cache.check()
+        assert eng.cache.used_pages() == [0] * len(eng.cache.groups)
+        outs[pipeline] = ([r.tokens for r in free], [r.tokens for r in stopped], [r.finish for r in stopped], got[a], got[b])
+    assert outs[True] == outs[False]

@@ -64,11 +64,53 @@ class FakeExecutor:
         return out
 
 
-def make(pages=64, page=4, slots=8, **cfg):
+class AheadExecutor(FakeExecutor):
+    """A fake that can also take a decode step without answering at once. The cache is extended and
+    committed at the launch, as on the device; the "memory" is written and read when the step is
+    collected, in launch order, so a step fed from the one before sees that step's tokens."""
+
+    def __init__(self, cache, truth):
+        super().__init__(cache, truth)
+        self.queue = []
+        self.fed = {}            # request -> the token its last launched step sampled (what the device would feed)
+        self.launched = 0
+        self.wasted = 0
+
+    def launch_decode(self, entries, sampling, feed):
+        for e in entries:
+            self.cache.extend(e.request, self.cache.length(e.request) + 1)
+        rows = []
+        for e in entries:
+            start = self.cache.length(e.request)
+            rows.append((e.request, start, self.cache.table(0, e.request).copy(), None if feed else e.tokens[0]))
+            self.cache.commit(e.request, start + 1)
+        self.queue.append(rows)
+        self.launched += 1
+        self.steps.append([(e.request, 1) for e in entries])
+        return len(self.queue) - 1
+
+    def collect(self, handle):
+        assert handle == len(self.queue) - len([q for q in self.queue if q is not None]), "steps are collected in launch order"
+        rows, self.queue[handle] = self.queue[handle], None
+        out = []
+        for rid, start, table, tok in rows:
+            tok = self.fed[rid] if tok is None else tok
+            self.memory[table[start // self.cache.page_size], start % self.cache.page_size] = tok
+            seen = [self.memory[table[p // self.cache.page_size], p % self.cache.page_size] for p in range(start + 1)]
+            if self.cache.has(rid) and len(self.truth[rid].tokens) > start:
+                assert seen == list(self.truth[rid].tokens[:start + 1]), f"request {rid}: the cache does not hold its history"
+            else:
+                self.wasted += 1          # the request ended after this step was launched
+            self.fed[rid] = next_token(seen)
+            out.append(self.fed[rid])
+        return out
+
+
+def make(pages=64, page=4, slots=8, executor=FakeExecutor, **cfg):
     cache = CacheManager([PagedKV(1, 8, None)], page, pages, slots, cfg.get("max_ctx", 256))
     sched = Scheduler(cache, SchedulerConfig(**{"max_num_seqs": slots, "max_batched_tokens": 64, "prefill_chunk": 16, "max_ctx": 256, **cfg}))
     truth = {}
-    ex = FakeExecutor(cache, truth)
+    ex = executor(cache, truth)
 
     def submit(rid, prompt, n, **kw):
         sched.submit(Request(rid, prompt, n, **kw))
@@ -239,3 +281,61 @@ def test_random_load_under_page_pressure(seed):
     for i, (p, k) in reqs.items():
         assert done[i].tokens == alone(p, k), f"request {i}"
     assert cache.used_pages() == [0] and cache.free_slots() == 5
+
+
+# ------------------------------------------------------------------------------------------ steps kept one ahead
+def test_steps_one_ahead_give_the_same_tokens_and_waste_nothing_at_max_tokens():
+    reqs = {i: (prompt(40 + i, n), k) for i, (n, k) in enumerate([(5, 9), (20, 30), (17, 30), (3, 2), (33, 1)])}
+    cache, sched, ex, submit = make(executor=AheadExecutor)
+    for i, (p, k) in reqs.items():
+        submit(i, p, k)
+    done, reports = run(sched, ex)
+    for i, (p, k) in reqs.items():
+        assert done[i].tokens == alone(p, k) and done[i].finish == "length"
+    assert ex.launched > 20 and ex.wasted == 0          # most decode steps went ahead; none ran for a request that had ended by length
+    assert all(len(r.emitted) == r.decode_rows for r in reports if r.prefill_tokens == 0)   # every call reports exactly one step
+    assert cache.used_pages() == [0] and cache.free_slots() == 8
+
+
+def test_steps_one_ahead_with_stop_tokens_cancel_and_late_arrivals():
+    p0, p1, p2 = prompt(50, 12), prompt(51, 7), prompt(52, 9)
+    stop_tok = alone(p0, 8)[5]                          # request 0 stops at its sixth token
+    cache, sched, ex, submit = make(executor=AheadExecutor)
+    submit(0, p0, 40, stop_ids=(stop_tok,))
+    submit(1, p1, 25)
+    done = {}
+    for step in range(200):
+        if sched.idle():
+            break
+        if step == 9:
+            submit(2, p2, 10)                           # arrives while steps are in flight
+        if step == 14:
+            f = sched.cancel(1)
+            assert f is not None and f.finish == "cancelled" and f.tokens == alone(p1, 25)[:len(f.tokens)]
+        for f in sched.step(ex).finished:
+            done[f.id] = f
+        cache.check()
+    assert sched.idle()
+    assert done[0].finish == "stop" and done[0].tokens == alone(p0, 40, stop=(stop_tok,)) and len(done[0].tokens) == 5
+    assert done[2].tokens == alone(p2, 10)
+    assert ex.wasted >= 1                               # the step launched before the stop token was seen
+    assert cache.used_pages() == [0] and cache.free_slots() == 8
+
+
+def test_steps_one_ahead_fall_back_when_pages_run_out():
+    cache, sched, ex, submit = make(pages=10, page=4, executor=AheadExecutor)
+    reqs = {i: (prompt(60 + i, 6), 14) for i in range(3)}      # 3 x 20 tokens = 15 pages > 10: someone is preempted
+    for i, (p, k) in reqs.items():
+        submit(i, p, k)
+    done, reports = run(sched, ex)
+    for i, (p, k) in reqs.items():
+        assert done[i].tokens == alone(p, k)
+    assert sum(r.preemptions for r in reports) >= 1
+    assert cache.used_pages() == [0]
+
+
+def test_pipeline_off_never_launches_ahead():
+    cache, sched, ex, submit = make(executor=AheadExecutor, pipeline=False)
+    submit(0, prompt(70, 5), 6)
+    done, _ = run(sched, ex)
+    assert done[0].tokens == alone(prompt(70, 5), 6) and ex.launched == 0
