@@ -30,7 +30,7 @@ QWEN3_8B = dict(
     tie_word_embeddings=False, max_position_embeddings=40960, hidden_act="silu", attention_bias=False, torch_dtype="bfloat16")
 CONTEXT = 4096          # benchmark context length
 PROMPT = 2048           # prefill length, and the context each decode request starts from
-PAGE = 16
+PAGE = 64           # keys per cache page: one TMA box of 64 rows per page, plane and half head (the attention kernels take 8 to 256)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 

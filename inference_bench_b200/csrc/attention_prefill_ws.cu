@@ -1,0 +1,371 @@
+// Causal attention for prompt portions on the sm_100a tensor cores, bfloat16, with the work of a CTA
+// divided among warps that do one thing each:
+//   warps 0-3  softmax: thread i owns query row i = lane i of tensor memory. It reads its row of S
+//              (64 keys) from tensor memory, keeps the running maximum and sum (float32, base 2), and
+//              writes P = 2^(S - m) as bfloat16 back into tensor memory over the first half of S.
+//   warp 4     issues the MMAs: S_j = Q K_j^T (A = Q, B = K, both from shared memory) one tile ahead,
+//              O += P_j V_j (A = P from tensor memory, B = V from shared memory), and the commits
+//              that free the K and V buffers and tell the softmax threads that S or O is ready.
+//   warp 5     copies: K and V tiles through the block table by TMA box copies (one per page, plane
+//              and 64 values of the head dimension) into two buffers each, as soon as one is free.
+// Nobody waits at a CTA-wide barrier inside the loop: the roles meet at mbarriers only, so the
+// tensor core works on S_{j+1} while the softmax threads are busy with tile j, and the copies run
+// ahead of both. O is rescaled (in tensor memory, by the softmax threads) only when a row's maximum
+// grows by more than 2^8, so most tiles touch O by MMA alone. Two CTAs share an SM.
+// Needs the tensor map of the cache pool (ib_make_kv_map): page sizes that are a multiple of 8 and
+// divide 64, or a multiple of 64. Reference design: crates/kir/src/cuda/attention/flash_mma.rs.
+#include <cuda.h>
+
+#include "kv_view.cuh"
+#include "mma_tiles.cuh"
+#include "sm100.cuh"
+
+namespace {
+
+constexpr int BM = 128, BN = 64;
+constexpr int kSoftmaxWarps = 4, kThreads = (kSoftmaxWarps + 2) * 32;
+constexpr float kRescaleThreshold = 8.f;  // log2 units
+
+__device__ __forceinline__ uint32_t blk_offset(int rows, int r, int cc) {  // 16-byte chunk cc of row r in [rows][64]-element blocks, 128-byte swizzle
+  return (uint32_t)((cc >> 3) * rows * 128 + r * 128 + (((cc & 7) ^ (r & 7)) << 4));
+}
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// 2^x on the FMA and integer pipes (relative error below 3e-6), for x <= 8 or so; see attention_prefill_tc.cu
+__device__ __forceinline__ float ex2_poly(float x) {
+  x = fmaxf(x, -125.f);
+  const float t = x + 12582912.f;
+  const float f = x - (t - 12582912.f);
+  float p = fmaf(f, 1.3333558e-3f, 9.6181291e-3f);
+  p = fmaf(p, f, 5.5504109e-2f);
+  p = fmaf(p, f, 2.4022651e-1f);
+  p = fmaf(p, f, 6.9314718e-1f);
+  p = fmaf(p, f, 1.f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
+__device__ __forceinline__ uint32_t pack_bf16_int(float lo, float hi) {
+  return __byte_perm(__float_as_uint(lo) + 0x8000u, __float_as_uint(hi) + 0x8000u, 0x7632);
+}
+__device__ __forceinline__ void bar_sync_softmax() { asm volatile("bar.sync 1, %0;" ::"n"(kSoftmaxWarps * 32) : "memory"); }
+
+template <int HD>
+struct Smem {
+  static constexpr int kQ = BM * HD * 2, kKV = BN * HD * 2;
+  static constexpr int oQ = 0, oK = kQ, oV = kQ + 2 * kKV, oBar = kQ + 4 * kKV;
+  // barriers: k_full[2] k_empty[2] v_full[2] v_empty[2] s_full[2] p_full[2] o_full q_full; then the tmem slot and the flag
+  static constexpr int kBars = 14;
+  static constexpr int kBytes = oBar + kBars * 8 + 16;
+  static_assert(kBytes <= 113 * 1024, "two CTAs must fit one SM");
+};
+
+template <int HD>
+__global__ void __launch_bounds__(kThreads, 2)
+    prefill_ws_kernel(const __nv_bfloat16* __restrict__ q, IbKvView kv, const int* __restrict__ tile_seg, const int* __restrict__ tile_row0,
+                      const int* __restrict__ seg_start, const int* __restrict__ seg_pos0, int window, float scale_log2e,
+                      __nv_bfloat16* __restrict__ out, int heads, const __grid_constant__ CUtensorMap kv_map, long long view_row0,
+                      unsigned* __restrict__ status) {
+  using SM = Smem<HD>;
+  constexpr int CPR = HD / 8, HB = HD / 64;
+  constexpr int kTmemCols = 256;            // S0 [0,64) | S1 [64,128) | O [128, 128+HD); P_j lies over the first 32 columns of S_j
+  extern __shared__ __align__(1024) uint8_t sm[];
+  if (sm100::smem_u32(sm) & 1023u) {
+    if (threadIdx.x == 0) atomicOr(status, IB_ERR_INTERNAL);
+    return;
+  }
+  const uint32_t q_s = sm100::smem_u32(sm + SM::oQ), k_s = sm100::smem_u32(sm + SM::oK), v_s = sm100::smem_u32(sm + SM::oV);
+  uint64_t* bars = (uint64_t*)(sm + SM::oBar);
+  uint64_t *k_full = bars, *k_empty = bars + 2, *v_full = bars + 4, *v_empty = bars + 6, *s_full = bars + 8, *p_full = bars + 10,
+           *o_full = bars + 12, *q_full = bars + 13;
+  uint32_t* tmem_slot = (uint32_t*)(bars + SM::kBars);
+  volatile int* gave_up = (volatile int*)(tmem_slot + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  ib::pdl_launch_dependents();
+  if (tid == 0) {
+    for (int i = 0; i < 2; i++) {
+      sm100::mbar_init(&k_full[i], 1);
+      sm100::mbar_init(&k_empty[i], 1);
+      sm100::mbar_init(&v_full[i], 1);
+      sm100::mbar_init(&v_empty[i], 1);
+      sm100::mbar_init(&s_full[i], 1);
+      sm100::mbar_init(&p_full[i], kSoftmaxWarps);
+    }
+    sm100::mbar_init(o_full, 1);
+    sm100::mbar_init(q_full, 1);
+    *gave_up = 0;
+    sm100::fence_barrier_init();
+  }
+  if (warp == kSoftmaxWarps) {
+    sm100::tmem_alloc(tmem_slot, kTmemCols);
+    sm100::tmem_relinquish();
+  }
+  sm100::tc_fence_before();
+  __syncthreads();
+  sm100::tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  // heads vary fastest, and the caller lists the tiles with the most keys first
+  const int tile = blockIdx.y, h = blockIdx.x;
+  const int seg = tile_seg[tile], row0 = tile_row0[tile];
+  const int n = seg_start[seg + 1] - seg_start[seg];
+  const int rows = min(BM, n - row0);
+  const int t0 = seg_start[seg] + row0;
+  const int pos_first = seg_pos0[seg] + row0, pos_last = pos_first + rows - 1;
+  const int kvh = h / (heads / kv.kv_heads);
+  const int key_lo = window > 0 ? max(0, pos_first - window + 1) : 0;
+  const int kt_begin = key_lo / BN, kt_end = pos_last / BN + 1;
+  const int n_kt = kt_end - kt_begin;
+  // a wait that ran out: say so once, and from then on nobody waits (the results are void, the status says so)
+  auto wait = [&](uint64_t* bar, uint32_t parity) {
+    if (*gave_up) return;
+    if (!sm100::mbar_wait(bar, parity)) {
+      *gave_up = 1;
+      atomicOr(status, IB_ERR_WAIT_TIMEOUT);
+    }
+  };
+
+  if (warp == kSoftmaxWarps + 1) {
+    // ------------------------------------------------------------ the copying warp
+    ib::pdl_wait();   // the kernel before wrote this portion's keys and values
+    const int box_rows = min(kv.page_size, BN);
+    const int ppt = BN / box_rows;
+    const long long rows_per_page = kv.page_stride / HD, v_rows = kv.v_offset / HD;
+    int held = -2;
+    for (int j = 0; j < n_kt; j++) {
+      const int kt = kt_begin + j;
+      const int rel = j * ppt;
+      if ((rel & 31) == 0) {   // the pages of the next 32 boxes, one per lane
+        const int key0 = (kt_begin * ppt + rel + lane) * box_rows;
+        const int col = key0 / kv.page_size;
+        held = -2;
+        if (key0 <= pos_last && key0 + box_rows > key_lo) held = col < kv.table_stride ? kv.block_table[(size_t)seg * kv.table_stride + col] : -1;
+      }
+      const int my = (lane - rel) & 31;
+      const bool mine = my < ppt;
+      const bool valid = mine && held >= 0 && held < kv.num_pages;
+      if (mine && held != -2 && !valid) atomicOr(status, IB_ERR_BAD_PAGE);
+      const unsigned vmask = __ballot_sync(0xffffffffu, valid);
+      const int key0 = kt * BN + my * box_rows;
+      const long long row = (long long)held * rows_per_page + view_row0 + (long long)kvh * kv.page_size + key0 % kv.page_size;
+      const uint32_t bytes = (uint32_t)(__popc(vmask) * box_rows * 128 * HB);
+#pragma unroll 1
+      for (int plane = 0; plane < 2; plane++) {   // K of the tile, then V
+        uint64_t* full = plane ? &v_full[j & 1] : &k_full[j & 1];
+        uint64_t* empty = plane ? &v_empty[j & 1] : &k_empty[j & 1];
+        uint8_t* dst = sm + (plane ? SM::oV : SM::oK) + (j & 1) * SM::kKV;
+        if (lane == 0) wait(empty, ((j >> 1) & 1) ^ 1);
+        __syncwarp();
+        bool cleared = false;
+        for (int pg = 0; pg < ppt; pg++) {   // boxes that are not copied (no visible key, or no page) are cleared
+          if ((vmask >> ((rel + pg) & 31)) & 1) continue;
+          cleared = true;
+          for (int idx = lane; idx < box_rows * 8 * HB; idx += 32) {
+            const int hb = idx / (box_rows * 8), r3 = idx % (box_rows * 8);
+            mt::st_shared_zero16(sm100::smem_u32(dst + hb * BN * 128 + pg * box_rows * 128) + r3 * 16);
+          }
+        }
+        if (cleared) sm100::fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) sm100::mbar_arrive_expect_tx(full, bytes);
+        __syncwarp();
+        if (valid) {
+#pragma unroll
+          for (int hb = 0; hb < HB; hb++)
+            sm100::tma_load_2d(dst + hb * BN * 128 + my * box_rows * 128, &kv_map, hb * 64, (int)(row + (plane ? v_rows : 0)), full);
+        }
+      }
+    }
+  } else if (warp == kSoftmaxWarps) {
+    // ------------------------------------------------------------ the MMA warp (one lane issues)
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = sm100::idesc_bf16_f32(BM, BN);
+      constexpr uint32_t idesc_o = sm100::idesc_bf16_f32_b_mn(BM, HD);
+      auto issue_s = [&](int j) {  // S_j = Q K_j^T into S buffer j & 1; its commit frees the K buffer
+        wait(&k_full[j & 1], (j >> 1) & 1);
+        sm100::tc_fence_after();
+        const uint32_t kb = k_s + (j & 1) * SM::kKV;
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; kk++) {
+          const uint64_t da = sm100::smem_desc_sw128(q_s + (kk >> 2) * BM * 128) + 2 * (kk & 3);
+          const uint64_t db = sm100::smem_desc_sw128(kb + (kk >> 2) * BN * 128) + 2 * (kk & 3);
+          sm100::mma_bf16_ss(tmem + (j & 1) * BN, da, db, idesc_s, kk != 0);
+        }
+        sm100::mma_commit(&s_full[j & 1]);
+        sm100::mma_commit(&k_empty[j & 1]);
+      };
+      wait(q_full, 0);
+      issue_s(0);
+      for (int j = 0; j < n_kt; j++) {
+        if (j + 1 < n_kt) issue_s(j + 1);
+        wait(&p_full[j & 1], (j >> 1) & 1);
+        wait(&v_full[j & 1], (j >> 1) & 1);
+        sm100::tc_fence_after();
+        const uint32_t vb = v_s + (j & 1) * SM::kKV;
+#pragma unroll
+        for (int ks = 0; ks < BN / 16; ks++) {   // O += P_j V_j, P from tensor memory: 16 keys = 8 columns per step
+          const uint64_t db = sm100::smem_desc_sw128_mn(vb + ks * 16 * 128, BN * 128);
+          sm100::mma_bf16_ts(tmem + 2 * BN, tmem + (j & 1) * BN + ks * 8, db, idesc_o, (j | ks) != 0);
+        }
+        sm100::mma_commit(o_full);
+        sm100::mma_commit(&v_empty[j & 1]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ the softmax warps: thread = query row
+    const int row = tid;
+    const uint32_t t_lane = tmem + ((uint32_t)(warp * 32) << 16);
+    const int my_pos = pos_first + row;
+    ib::pdl_wait();   // q comes from the kernel before
+    for (int idx = tid; idx < BM * CPR; idx += kSoftmaxWarps * 32) {
+      const int r = idx / CPR, cc = idx % CPR;
+      const uint32_t d = q_s + blk_offset(BM, r, cc);
+      if (r < rows)
+        mt::cp_async16(d, q + ((size_t)(t0 + r) * heads + h) * HD + cc * 8);
+      else
+        mt::st_shared_zero16(d);
+    }
+    mt::cp_async_commit();
+    mt::cp_async_wait<0>();
+    sm100::fence_proxy_async();
+    bar_sync_softmax();
+    if (tid == 0) sm100::mbar_arrive(q_full);
+
+    float m_ref = -INFINITY, l = 0.f;
+    for (int j = 0; j < n_kt; j++) {
+      const int kt = kt_begin + j;
+      wait(&s_full[j & 1], (j >> 1) & 1);
+      sm100::tc_fence_after();
+      uint32_t sr[BN];
+      sm100::tmem_ld_32x32b_x32(t_lane + (j & 1) * BN, sr);
+      sm100::tmem_ld_32x32b_x32(t_lane + (j & 1) * BN + 32, sr + 32);
+      sm100::tmem_ld_wait();
+      const int key0 = kt * BN;
+      const bool need_mask = key0 + BN - 1 > pos_first || key0 < key_lo || (window > 0 && key0 <= pos_last - window);
+      if (need_mask) {
+#pragma unroll
+        for (int c = 0; c < BN; c++) {
+          const int key = key0 + c;
+          const bool live = key <= my_pos && key >= key_lo && (window <= 0 || key > my_pos - window);
+          if (!live) sr[c] = 0xff800000u;  // -inf
+        }
+      }
+      float tile_max = -INFINITY;   // of the raw products; the scale (positive) is applied once below
+#pragma unroll
+      for (int c = 0; c < BN; c++) tile_max = fmaxf(tile_max, __uint_as_float(sr[c]));
+      tile_max *= scale_log2e;
+      // the reference maximum moves only when a row's maximum grew a lot (or at the first tile); then O,
+      // which P V of the tile before may still be adding to, is rescaled once that MMA has finished
+      const bool grow = tile_max > m_ref + kRescaleThreshold || (m_ref == -INFINITY && tile_max > -INFINITY);
+      if (j == 0) {
+        m_ref = tile_max;
+      } else if (__any_sync(0xffffffffu, grow)) {
+        wait(o_full, (j - 1) & 1);
+        sm100::tc_fence_after();
+        const float m_new = grow ? fmaxf(m_ref, tile_max) : m_ref;
+        const float f = m_new == -INFINITY ? 1.f : ex2(m_ref - m_new);  // 1 for rows that keep their reference, 0 when it was -inf
+        l *= f;
+        m_ref = m_new;
+#pragma unroll 1
+        for (int c0 = 0; c0 < HD; c0 += 32) {
+          uint32_t o[32];
+          sm100::tmem_ld_32x32b_x32(t_lane + 2 * BN + c0, o);
+          sm100::tmem_ld_wait();
+#pragma unroll
+          for (int c = 0; c < 32; c++) o[c] = __float_as_uint(__uint_as_float(o[c]) * f);
+          sm100::tmem_st_32x32b_x32(t_lane + 2 * BN + c0, o);
+        }
+        sm100::tmem_st_wait();
+      }
+      const float mu = m_ref == -INFINITY ? 0.f : m_ref;
+      // P = 2^(S - m_ref) as bfloat16, two to a column, over the first 32 columns of S_j
+      uint32_t w[BN / 2];
+#pragma unroll
+      for (int c = 0; c < BN / 2; c++) {
+        const float p0 = ex2(fmaf(__uint_as_float(sr[2 * c]), scale_log2e, -mu));
+        const float p1 = ex2_poly(fmaf(__uint_as_float(sr[2 * c + 1]), scale_log2e, -mu));
+        l += p0 + p1;
+        w[c] = pack_bf16_int(p0, p1);
+      }
+      sm100::tmem_st_32x32b_x32(t_lane + (j & 1) * BN, w);
+      sm100::tmem_st_wait();
+      sm100::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) sm100::mbar_arrive(&p_full[j & 1]);
+    }
+    // ---- O / l -> out
+    wait(o_full, (n_kt - 1) & 1);
+    sm100::tc_fence_after();
+    if (!*gave_up) {
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      __nv_bfloat16* dst = out + ((size_t)(t0 + row) * heads + h) * HD;
+#pragma unroll 1
+      for (int c0 = 0; c0 < HD; c0 += 32) {
+        uint32_t o[32];
+        sm100::tmem_ld_32x32b_x32(t_lane + 2 * BN + c0, o);
+        sm100::tmem_ld_wait();
+        if (row < rows) {
+#pragma unroll
+          for (int c = 0; c < 32; c += 8) {
+            uint4 v;
+            v.x = mt::pack_bf16(__uint_as_float(o[c]) * inv, __uint_as_float(o[c + 1]) * inv);
+            v.y = mt::pack_bf16(__uint_as_float(o[c + 2]) * inv, __uint_as_float(o[c + 3]) * inv);
+            v.z = mt::pack_bf16(__uint_as_float(o[c + 4]) * inv, __uint_as_float(o[c + 5]) * inv);
+            v.w = mt::pack_bf16(__uint_as_float(o[c + 6]) * inv, __uint_as_float(o[c + 7]) * inv);
+            *(uint4*)(dst + c0 + c) = v;
+          }
+        }
+      }
+    }
+  }
+  // every role is done: the MMAs have finished (the softmax threads waited for the last one), copies have landed (every tile was used)
+  sm100::tc_fence_before();
+  __syncthreads();
+  if (warp == kSoftmaxWarps) {
+    __syncwarp();
+    sm100::tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
+template <int HD>
+int launch(const void* q, const IbKvView* kv, const int* tile_seg, const int* tile_row0, int n_tiles, const int* seg_start, const int* seg_pos0,
+           int window, float scale, void* out, int heads, const CUtensorMap* kv_map, long long view_row0, unsigned* status, cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(prefill_ws_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<HD>::kBytes);
+    IB_CHECK_ARG(e == cudaSuccess, "attention_prefill_ws: cannot reserve %d bytes of shared memory: %s", Smem<HD>::kBytes, cudaGetErrorString(e));
+    configured = true;
+  }
+  ib::launch(prefill_ws_kernel<HD>, dim3(heads, n_tiles), kThreads, Smem<HD>::kBytes, stream, (const __nv_bfloat16*)q, *kv, tile_seg, tile_row0,
+             seg_start, seg_pos0, window, scale * 1.4426950408889634f, (__nv_bfloat16*)out, heads, *kv_map, view_row0, status);
+  IB_CHECK_LAUNCH("attention_prefill_ws");
+  return 0;
+}
+
+}  // namespace
+
+// Attention for query tiles of 128 rows: tile i covers rows tile_row0[i].. of segment tile_seg[i]; list the
+// tiles that see the most keys first. kv_map: the tensor map of the view's pool (ib_make_kv_map), view_row0
+// the pool row where this view's keys of page 0, head 0 start.
+extern "C" int ib_attention_prefill_ws(const void* q, const IbKvView* kv, const int* tile_seg, const int* tile_row0, int n_tiles,
+                                       const int* seg_start, const int* seg_pos0, int window, float scale, void* out, int heads,
+                                       const void* kv_map, long long view_row0, unsigned* status, cudaStream_t stream) {
+  if (n_tiles == 0) return 0;
+  IB_CHECK_ARG(kv && kv->base && kv->block_table && kv_map, "attention_prefill_ws: the cache view or the tensor map is a null pointer");
+  IB_CHECK_ARG(kv->dtype == IB_BF16, "attention_prefill_ws: the cache must be bfloat16");
+  IB_CHECK_ARG(kv->page_size % 8 == 0 && (BN % kv->page_size == 0 || kv->page_size % BN == 0),
+               "attention_prefill_ws: page size %d is not a multiple of 8 that divides %d or a multiple of %d", kv->page_size, BN, BN);
+  IB_CHECK_ARG(kv->kv_heads > 0 && heads % kv->kv_heads == 0, "attention_prefill_ws: %d query heads are not a multiple of %d kv heads", heads,
+               kv->kv_heads);
+  IB_CHECK_ARG(n_tiles > 0 && n_tiles <= 65535, "attention_prefill_ws: %d query tiles (at most 65535 per launch)", n_tiles);
+  IB_CHECK_ARG(kv->page_stride % kv->head_dim == 0 && kv->v_offset % kv->head_dim == 0, "attention_prefill_ws: strides are not whole rows");
+  if (kv->head_dim == 128)
+    return launch<128>(q, kv, tile_seg, tile_row0, n_tiles, seg_start, seg_pos0, window, scale, out, heads, (const CUtensorMap*)kv_map, view_row0,
+                       status, stream);
+  if (kv->head_dim == 64)
+    return launch<64>(q, kv, tile_seg, tile_row0, n_tiles, seg_start, seg_pos0, window, scale, out, heads, (const CUtensorMap*)kv_map, view_row0,
+                      status, stream);
+  return ib_set_error("attention_prefill_ws: head_dim %d has no tensor-core kernel (64 and 128 have)", kv->head_dim);
+}

@@ -40,7 +40,7 @@ class Reply:
 
 class Engine:
     def __init__(self, model: Union[str, Path, Mapping[str, Any]], dtype: str = "bfloat16", max_ctx: Optional[int] = None,
-                 page_size: int = 16, num_pages: Optional[int] = None, kv_gb: Optional[float] = None, max_num_seqs: int = 64,
+                 page_size: int = 64, num_pages: Optional[int] = None, kv_gb: Optional[float] = None, max_num_seqs: int = 64,
                  max_batched_tokens: int = 8192, prefill_chunk: int = 2048, random_weights_seed: Optional[int] = None,
                  device: str = "cuda:0", use_graphs: bool = True, pipeline: bool = True):
         """model: a folder with config.json and model.safetensors, or (with random_weights_seed) a raw

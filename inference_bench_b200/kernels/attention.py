@@ -59,8 +59,9 @@ def stream_slices(n_dec: int, kv_heads: int, max_keys: int, device) -> int:
     return max(1, min(want, -(-tiles // 2)))
 
 
-QTILE = {"tcgen05": 128, "mma": 64}   # query rows per CTA of the prefill kernels (csrc/attention_prefill_tc.cu, attention_prefill.cu)
-PREFILL_KERNEL = "tcgen05"               # which one the engine uses; the other stays as a tested alternative
+QTILE = {"ws": 128, "tcgen05": 128, "mma": 64}   # query rows per CTA of the prefill kernels (csrc/attention_prefill_ws.cu, _tc.cu, attention_prefill.cu)
+PREFILL_KERNEL = "ws"   # which one the engine uses: "ws" (tcgen05, one job per warp, keys and values by TMA; falls back to "tcgen05" for
+                        # page sizes TMA cannot serve), "tcgen05" (every thread does everything, cp.async) or "mma" (mma.sync)
 
 L.register("ib_attention_decode", [L._p, C.POINTER(L.KvView), L._p, L._i, L._p, L._p, L._i, L._f, L._p, L._p, L._p, L._i, L._i, L._i, L._p, L._ll, L._p, L._p])
 L.register("ib_attention_decode_stream", [L._p, C.POINTER(L.KvView), L._p, L._i, L._p, L._p, L._i, L._f, L._p, L._p, L._p, L._i, L._i, L._i, L._p, L._ll, L._p, L._p])
@@ -71,6 +72,7 @@ USE_TMA = False  # decode keys and values by TMA box copies (one thread, one 2 K
                  # threads: measured slower at page size 16 (3.86 against 3.71 ms per step at batch 8), so off; kept and tested
 L.register("ib_attention_prefill", [L._p, C.POINTER(L.KvView), L._p, L._p, L._i, L._p, L._p, L._i, L._f, L._p, L._i, L._p, L._p])
 L.register("ib_attention_prefill_tc", [L._p, C.POINTER(L.KvView), L._p, L._p, L._i, L._p, L._p, L._i, L._f, L._p, L._i, L._p, L._p])
+L.register("ib_attention_prefill_ws", [L._p, C.POINTER(L.KvView), L._p, L._p, L._i, L._p, L._p, L._i, L._f, L._p, L._i, L._p, L._ll, L._p, L._p])
 
 
 def has_tensor_core_kernel(dtype: torch.dtype, head_dim: int, heads: int, kv_heads: int) -> bool:
@@ -135,7 +137,11 @@ def paged_attention(ctx, q: torch.Tensor, cache: ops.KvLayerView, heads: int, wi
                work["n_dec"], ctx.positions.data_ptr(), ctx.seg_of_token.data_ptr(), int(window or 0), float(scale), part_o.data_ptr(),
                part_ml.data_ptr(), out.data_ptr(), heads, max_slices, tps, kv_map, row0, rt.status.data_ptr(), stream)
     if work["n_tiles"]:
-        L.call("ib_attention_prefill_tc" if PREFILL_KERNEL == "tcgen05" else "ib_attention_prefill", q.data_ptr(), C.byref(view), work["tile_seg"].data_ptr(), work["tile_row0"].data_ptr(), work["n_tiles"],
-               ctx.seg_start.data_ptr(), ctx.seg_pos0.data_ptr(), int(window or 0), float(scale), out.data_ptr(), heads, rt.status.data_ptr(),
-               stream)
+        args = (q.data_ptr(), C.byref(view), work["tile_seg"].data_ptr(), work["tile_row0"].data_ptr(), work["n_tiles"], ctx.seg_start.data_ptr(),
+                ctx.seg_pos0.data_ptr(), int(window or 0), float(scale), out.data_ptr(), heads)
+        kv_map, row0 = cache.tma() if PREFILL_KERNEL == "ws" else (None, 0)
+        if kv_map:
+            L.call("ib_attention_prefill_ws", *args, kv_map, row0, rt.status.data_ptr(), stream)
+        else:
+            L.call("ib_attention_prefill" if PREFILL_KERNEL == "mma" else "ib_attention_prefill_tc", *args, rt.status.data_ptr(), stream)
     return out

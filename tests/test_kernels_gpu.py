@@ -253,7 +253,7 @@ def test_attention_generic(status, dtype, window):
 
 @pytest.mark.parametrize("hd,heads,kvh,page", [(128, 8, 2, 16), (64, 5, 1, 32), (128, 16, 1, 16), (64, 4, 4, 8)])
 @pytest.mark.parametrize("window", [None, 100])
-@pytest.mark.parametrize("prefill", ["tcgen05", "mma"])
+@pytest.mark.parametrize("prefill", ["ws", "tcgen05", "mma"])
 def test_attention_tensor_core_kernels(status, monkeypatch, hd, heads, kvh, page, window, prefill):
     """Decode slices and prefill tiles (either prefill kernel) through the engine's dispatch, against the plain reference."""
     from inference_bench_b200.engine.context import Segment, build_context
