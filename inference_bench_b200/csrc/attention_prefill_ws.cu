@@ -25,6 +25,8 @@ namespace {
 constexpr int BM = 128, BN = 64;
 constexpr int kSoftmaxWarps = 4, kThreads = (kSoftmaxWarps + 2) * 32;
 constexpr float kRescaleThreshold = 8.f;  // log2 units
+constexpr int KS = 2, VS = 3;             // buffers for K tiles and for V tiles (what two CTAs per SM leave room for)
+constexpr int kMufu = 4;                  // of every four exponentials, how many the special-function unit computes (0, 2 or 4)
 
 __device__ __forceinline__ uint32_t blk_offset(int rows, int r, int cc) {  // 16-byte chunk cc of row r in [rows][64]-element blocks, 128-byte swizzle
   return (uint32_t)((cc >> 3) * rows * 128 + r * 128 + (((cc & 7) ^ (r & 7)) << 4));
@@ -34,29 +36,41 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-// 2^x on the FMA and integer pipes (relative error below 3e-6), for x <= 8 or so; see attention_prefill_tc.cu
-__device__ __forceinline__ float ex2_poly(float x) {
-  x = fmaxf(x, -125.f);
-  const float t = x + 12582912.f;
-  const float f = x - (t - 12582912.f);
-  float p = fmaf(f, 1.3333558e-3f, 9.6181291e-3f);
-  p = fmaf(p, f, 5.5504109e-2f);
-  p = fmaf(p, f, 2.4022651e-1f);
-  p = fmaf(p, f, 6.9314718e-1f);
-  p = fmaf(p, f, 1.f);
-  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+// 2^x for two values on the FMA and integer pipes (relative error below 3e-6), for x <= 8 or so, with the
+// two-wide float32 instructions of sm_100: x = n + f with |f| <= 1/2, a degree-5 polynomial for 2^f, n added
+// into the exponent. The special-function unit is a bottleneck of this kernel, so part of the exponentials go this way.
+__device__ __forceinline__ float2 ex2_poly2(float2 x) {
+  x.x = fmaxf(x.x, -125.f);
+  x.y = fmaxf(x.y, -125.f);
+  const float2 big = make_float2(12582912.f, 12582912.f);   // 1.5 * 2^23: the integer nearest to x sits in the low mantissa bits
+  const float2 t = __fadd2_rn(x, big);
+  const float2 r = __fadd2_rn(t, make_float2(-12582912.f, -12582912.f));
+  const float2 f = __ffma2_rn(r, make_float2(-1.f, -1.f), x);
+  float2 p = __ffma2_rn(f, make_float2(1.3333558e-3f, 1.3333558e-3f), make_float2(9.6181291e-3f, 9.6181291e-3f));
+  p = __ffma2_rn(p, f, make_float2(5.5504109e-2f, 5.5504109e-2f));
+  p = __ffma2_rn(p, f, make_float2(2.4022651e-1f, 2.4022651e-1f));
+  p = __ffma2_rn(p, f, make_float2(6.9314718e-1f, 6.9314718e-1f));
+  p = __ffma2_rn(p, f, make_float2(1.f, 1.f));
+  return make_float2(__int_as_float(__float_as_int(p.x) + (__float_as_int(t.x) << 23)), __int_as_float(__float_as_int(p.y) + (__float_as_int(t.y) << 23)));
 }
-__device__ __forceinline__ uint32_t pack_bf16_int(float lo, float hi) {
-  return __byte_perm(__float_as_uint(lo) + 0x8000u, __float_as_uint(hi) + 0x8000u, 0x7632);
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {   // round to nearest even, one instruction
+  uint32_t d;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
 }
 __device__ __forceinline__ void bar_sync_softmax() { asm volatile("bar.sync 1, %0;" ::"n"(kSoftmaxWarps * 32) : "memory"); }
 
 template <int HD>
 struct Smem {
   static constexpr int kQ = BM * HD * 2, kKV = BN * HD * 2;
-  static constexpr int oQ = 0, oK = kQ, oV = kQ + 2 * kKV, oBar = kQ + 4 * kKV;
-  // barriers: k_full[2] k_empty[2] v_full[2] v_empty[2] s_full[2] p_full[2] o_full q_full; then the tmem slot and the flag
-  static constexpr int kBars = 14;
+  static constexpr int oQ = 0, oK = kQ, oV = kQ + KS * kKV, oBar = kQ + (KS + VS) * kKV;
+  // barriers: k_full[KS] k_empty[KS] v_full[VS] v_empty[VS] s_full[2] p_full[2] o_full q_full; then the tmem slot and the flag
+  static constexpr int kBars = 2 * KS + 2 * VS + 6;
   static constexpr int kBytes = oBar + kBars * 8 + 16;
   static_assert(kBytes <= 113 * 1024, "two CTAs must fit one SM");
 };
@@ -77,19 +91,23 @@ __global__ void __launch_bounds__(kThreads, 2)
   }
   const uint32_t q_s = sm100::smem_u32(sm + SM::oQ), k_s = sm100::smem_u32(sm + SM::oK), v_s = sm100::smem_u32(sm + SM::oV);
   uint64_t* bars = (uint64_t*)(sm + SM::oBar);
-  uint64_t *k_full = bars, *k_empty = bars + 2, *v_full = bars + 4, *v_empty = bars + 6, *s_full = bars + 8, *p_full = bars + 10,
-           *o_full = bars + 12, *q_full = bars + 13;
+  uint64_t *k_full = bars, *k_empty = bars + KS, *v_full = bars + 2 * KS, *v_empty = bars + 2 * KS + VS, *s_full = bars + 2 * KS + 2 * VS,
+           *p_full = s_full + 2, *o_full = s_full + 4, *q_full = s_full + 5;
   uint32_t* tmem_slot = (uint32_t*)(bars + SM::kBars);
   volatile int* gave_up = (volatile int*)(tmem_slot + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   ib::pdl_launch_dependents();
   if (tid == 0) {
-    for (int i = 0; i < 2; i++) {
+    for (int i = 0; i < KS; i++) {
       sm100::mbar_init(&k_full[i], 1);
       sm100::mbar_init(&k_empty[i], 1);
+    }
+    for (int i = 0; i < VS; i++) {
       sm100::mbar_init(&v_full[i], 1);
       sm100::mbar_init(&v_empty[i], 1);
+    }
+    for (int i = 0; i < 2; i++) {
       sm100::mbar_init(&s_full[i], 1);
       sm100::mbar_init(&p_full[i], kSoftmaxWarps);
     }
@@ -153,10 +171,11 @@ __global__ void __launch_bounds__(kThreads, 2)
       const uint32_t bytes = (uint32_t)(__popc(vmask) * box_rows * 128 * HB);
 #pragma unroll 1
       for (int plane = 0; plane < 2; plane++) {   // K of the tile, then V
-        uint64_t* full = plane ? &v_full[j & 1] : &k_full[j & 1];
-        uint64_t* empty = plane ? &v_empty[j & 1] : &k_empty[j & 1];
-        uint8_t* dst = sm + (plane ? SM::oV : SM::oK) + (j & 1) * SM::kKV;
-        if (lane == 0) wait(empty, ((j >> 1) & 1) ^ 1);
+        const int st = plane ? j % VS : j % KS, round = plane ? j / VS : j / KS;
+        uint64_t* full = plane ? &v_full[st] : &k_full[st];
+        uint64_t* empty = plane ? &v_empty[st] : &k_empty[st];
+        uint8_t* dst = sm + (plane ? SM::oV : SM::oK) + st * SM::kKV;
+        if (lane == 0) wait(empty, (round & 1) ^ 1);
         __syncwarp();
         bool cleared = false;
         for (int pg = 0; pg < ppt; pg++) {   // boxes that are not copied (no visible key, or no page) are cleared
@@ -184,9 +203,9 @@ __global__ void __launch_bounds__(kThreads, 2)
       constexpr uint32_t idesc_s = sm100::idesc_bf16_f32(BM, BN);
       constexpr uint32_t idesc_o = sm100::idesc_bf16_f32_b_mn(BM, HD);
       auto issue_s = [&](int j) {  // S_j = Q K_j^T into S buffer j & 1; its commit frees the K buffer
-        wait(&k_full[j & 1], (j >> 1) & 1);
+        wait(&k_full[j % KS], (j / KS) & 1);
         sm100::tc_fence_after();
-        const uint32_t kb = k_s + (j & 1) * SM::kKV;
+        const uint32_t kb = k_s + (j % KS) * SM::kKV;
 #pragma unroll
         for (int kk = 0; kk < HD / 16; kk++) {
           const uint64_t da = sm100::smem_desc_sw128(q_s + (kk >> 2) * BM * 128) + 2 * (kk & 3);
@@ -194,23 +213,23 @@ __global__ void __launch_bounds__(kThreads, 2)
           sm100::mma_bf16_ss(tmem + (j & 1) * BN, da, db, idesc_s, kk != 0);
         }
         sm100::mma_commit(&s_full[j & 1]);
-        sm100::mma_commit(&k_empty[j & 1]);
+        sm100::mma_commit(&k_empty[j % KS]);
       };
       wait(q_full, 0);
       issue_s(0);
       for (int j = 0; j < n_kt; j++) {
         if (j + 1 < n_kt) issue_s(j + 1);
         wait(&p_full[j & 1], (j >> 1) & 1);
-        wait(&v_full[j & 1], (j >> 1) & 1);
+        wait(&v_full[j % VS], (j / VS) & 1);
         sm100::tc_fence_after();
-        const uint32_t vb = v_s + (j & 1) * SM::kKV;
+        const uint32_t vb = v_s + (j % VS) * SM::kKV;
 #pragma unroll
         for (int ks = 0; ks < BN / 16; ks++) {   // O += P_j V_j, P from tensor memory: 16 keys = 8 columns per step
           const uint64_t db = sm100::smem_desc_sw128_mn(vb + ks * 16 * 128, BN * 128);
           sm100::mma_bf16_ts(tmem + 2 * BN, tmem + (j & 1) * BN + ks * 8, db, idesc_o, (j | ks) != 0);
         }
         sm100::mma_commit(o_full);
-        sm100::mma_commit(&v_empty[j & 1]);
+        sm100::mma_commit(&v_empty[j % VS]);
       }
     }
   } else {
@@ -252,10 +271,14 @@ __global__ void __launch_bounds__(kThreads, 2)
           if (!live) sr[c] = 0xff800000u;  // -inf
         }
       }
-      float tile_max = -INFINITY;   // of the raw products; the scale (positive) is applied once below
+      // the maximum of the raw products (the positive scale is applied once below): four chains of three-input maxima
+      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int c = 0; c < BN; c++) tile_max = fmaxf(tile_max, __uint_as_float(sr[c]));
-      tile_max *= scale_log2e;
+      for (int c = 0; c < BN; c += 8) {
+#pragma unroll
+        for (int e = 0; e < 4; e++) mx[e] = max3(mx[e], __uint_as_float(sr[c + 2 * e]), __uint_as_float(sr[c + 2 * e + 1]));
+      }
+      const float tile_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale_log2e;
       // the reference maximum moves only when a row's maximum grew a lot (or at the first tile); then O,
       // which P V of the tile before may still be adding to, is rescaled once that MMA has finished
       const bool grow = tile_max > m_ref + kRescaleThreshold || (m_ref == -INFINITY && tile_max > -INFINITY);
@@ -281,14 +304,22 @@ __global__ void __launch_bounds__(kThreads, 2)
       }
       const float mu = m_ref == -INFINITY ? 0.f : m_ref;
       // P = 2^(S - m_ref) as bfloat16, two to a column, over the first 32 columns of S_j
+      // (of every four keys, kMufu go through the special-function unit and the rest through the polynomial)
       uint32_t w[BN / 2];
+      const float2 sc2 = make_float2(scale_log2e, scale_log2e), nmu2 = make_float2(-mu, -mu);
+      float2 la = make_float2(0.f, 0.f), lb = make_float2(0.f, 0.f);
 #pragma unroll
-      for (int c = 0; c < BN / 2; c++) {
-        const float p0 = ex2(fmaf(__uint_as_float(sr[2 * c]), scale_log2e, -mu));
-        const float p1 = ex2_poly(fmaf(__uint_as_float(sr[2 * c + 1]), scale_log2e, -mu));
-        l += p0 + p1;
-        w[c] = pack_bf16_int(p0, p1);
+      for (int c = 0; c < BN; c += 4) {
+        const float2 a = __ffma2_rn(make_float2(__uint_as_float(sr[c]), __uint_as_float(sr[c + 1])), sc2, nmu2);
+        const float2 b = __ffma2_rn(make_float2(__uint_as_float(sr[c + 2]), __uint_as_float(sr[c + 3])), sc2, nmu2);
+        const float2 pa = kMufu >= 2 ? make_float2(ex2(a.x), ex2(a.y)) : ex2_poly2(a);
+        const float2 pb = kMufu >= 4 ? make_float2(ex2(b.x), ex2(b.y)) : ex2_poly2(b);
+        la = __fadd2_rn(la, pa);
+        lb = __fadd2_rn(lb, pb);
+        w[c / 2] = pack_bf16x2(pa.x, pa.y);
+        w[c / 2 + 1] = pack_bf16x2(pb.x, pb.y);
       }
+      l += (la.x + la.y) + (lb.x + lb.y);
       sm100::tmem_st_32x32b_x32(t_lane + (j & 1) * BN, w);
       sm100::tmem_st_wait();
       sm100::tc_fence_before();
