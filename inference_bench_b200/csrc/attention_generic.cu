@@ -81,81 +81,94 @@ __global__ void qk_norm_rope_kv_kernel(const float* __restrict__ qkv, int P, siz
 // The same for head sizes 64 and 128 with the whole head rotated (or none of it): a lane holds
 // HD/32 consecutive values, so loads and stores are 8 or 16 bytes wide, the norm is one warp sum,
 // and the rotation partner (d + HD/2) sits in lane ^ 16.
-template <int HD, typename A, typename C>
+template <int HD, typename A, typename C, int PER>
 __global__ void qk_norm_rope_kv_vec_kernel(const float* __restrict__ qkv, int P, size_t stride_p, const float* __restrict__ q_norm_w,
                                            const float* __restrict__ k_norm_w, float eps, const float* __restrict__ cos_t,
                                            const float* __restrict__ sin_t, const int* __restrict__ positions,
                                            const int* __restrict__ seg_of_token, A* __restrict__ q_out, IbKvView kv, int write_kv, int T,
                                            int heads, unsigned* __restrict__ status) {
+  // blockIdx.x is the token; a warp takes PER consecutive heads of it (q heads, then k heads, then v heads)
+  // and loads them all before it works on any: with many tokens (PER = 4) that keeps four loads per lane
+  // in flight; with few, PER = 1 keeps the chain short. No division anywhere: this kernel is bound by
+  // its instruction count as much as by memory.
   constexpr int E = HD / 32;
   ib::pdl_launch_dependents();
   ib::pdl_wait();
   const int kvh = kv.kv_heads, slots = heads + 2 * kvh;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const long long item = (long long)blockIdx.x * kWarps + warp;
-  if (item >= (long long)T * slots) return;
-  const int t = (int)(item / slots), j = (int)(item % slots);
-  const bool is_q = j < heads, is_k = !is_q && j < heads + kvh;
-  if (!is_q && !write_kv) return;
-  const float* src = qkv + (size_t)t * slots * HD + (size_t)j * HD + lane * E;
-  float v[E];
+  const int t = blockIdx.x;
+  const int j0 = (blockIdx.y * kWarps + warp) * PER;
+  float v[PER][E];
 #pragma unroll
-  for (int e = 0; e < E; e++) v[e] = 0.f;
-  for (int p = 0; p < P; p++) {
-    if constexpr (E == 4) {
-      const float4 a = *(const float4*)(src + p * stride_p);
-      v[0] += a.x, v[1] += a.y, v[2] += a.z, v[3] += a.w;
-    } else {
-      const float2 a = *(const float2*)(src + p * stride_p);
-      v[0] += a.x, v[1] += a.y;
-    }
-  }
-  const float* nw = is_q ? q_norm_w : (is_k ? k_norm_w : nullptr);
-  if (nw) {
-    float ss = 0.f;
+  for (int u = 0; u < PER; u++) {
 #pragma unroll
-    for (int e = 0; e < E; e++) ss += v[e] * v[e];
-    ss = ib::warp_sum(ss);
-    const float inv = rsqrtf(ss / (float)HD + eps);
-#pragma unroll
-    for (int e = 0; e < E; e++) v[e] = nw[lane * E + e] * (v[e] * inv);
-  }
-  if ((is_q || is_k) && cos_t) {
-    const float* c = cos_t + (size_t)t * (HD / 2) + (lane & 15) * E;
-    const float* sn = sin_t + (size_t)t * (HD / 2) + (lane & 15) * E;
-#pragma unroll
-    for (int e = 0; e < E; e++) {
-      const float other = __shfl_xor_sync(0xffffffffu, v[e], 16);
-      // d < HD/2: v cos - partner sin; d >= HD/2: v cos + partner sin
-      v[e] = lane < 16 ? v[e] * c[e] - other * sn[e] : v[e] * c[e] + other * sn[e];
-    }
-  }
-  auto store = [&](auto* dst) {
-    using D = std::remove_pointer_t<decltype(dst)>;
-    if constexpr (sizeof(D) == 4) {
-      if constexpr (E == 4) *(float4*)dst = make_float4(v[0], v[1], v[2], v[3]);
-      else *(float2*)dst = make_float2(v[0], v[1]);
-    } else {
-      __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]);
+    for (int e = 0; e < E; e++) v[u][e] = 0.f;
+    const int j = j0 + u;
+    if (j >= slots || (j >= heads && !write_kv)) continue;
+    const float* src = qkv + (size_t)t * slots * HD + (size_t)j * HD + lane * E;
+    for (int p = 0; p < P; p++) {
       if constexpr (E == 4) {
-        __nv_bfloat162 hi = __floats2bfloat162_rn(v[2], v[3]);
-        *(uint2*)dst = make_uint2(*(uint32_t*)&lo, *(uint32_t*)&hi);
+        const float4 a = *(const float4*)(src + p * stride_p);
+        v[u][0] += a.x, v[u][1] += a.y, v[u][2] += a.z, v[u][3] += a.w;
       } else {
-        *(uint32_t*)dst = *(uint32_t*)&lo;
+        const float2 a = *(const float2*)(src + p * stride_p);
+        v[u][0] += a.x, v[u][1] += a.y;
       }
     }
-  };
-  if (is_q) {
-    store(q_out + (size_t)t * heads * HD + (size_t)j * HD + lane * E);
-    return;
   }
-  const int head = is_k ? j - heads : j - heads - kvh;
-  const long long off = ib::kv_offset(kv, seg_of_token[t], positions[t], head);
-  if (off < 0) {
-    if (lane == 0) atomicOr(status, IB_ERR_BAD_PAGE);
-    return;
+#pragma unroll
+  for (int u = 0; u < PER; u++) {
+    const int j = j0 + u;
+    if (j >= slots) continue;
+    const bool is_q = j < heads, is_k = !is_q && j < heads + kvh;
+    if (!is_q && !write_kv) continue;
+    const float* nw = is_q ? q_norm_w : (is_k ? k_norm_w : nullptr);
+    if (nw) {
+      float ss = 0.f;
+#pragma unroll
+      for (int e = 0; e < E; e++) ss += v[u][e] * v[u][e];
+      ss = ib::warp_sum(ss);
+      const float inv = rsqrtf(ss / (float)HD + eps);
+#pragma unroll
+      for (int e = 0; e < E; e++) v[u][e] = nw[lane * E + e] * (v[u][e] * inv);
+    }
+    if ((is_q || is_k) && cos_t) {
+      const float* c = cos_t + (size_t)t * (HD / 2) + (lane & 15) * E;
+      const float* sn = sin_t + (size_t)t * (HD / 2) + (lane & 15) * E;
+#pragma unroll
+      for (int e = 0; e < E; e++) {
+        const float other = __shfl_xor_sync(0xffffffffu, v[u][e], 16);
+        // d < HD/2: v cos - partner sin; d >= HD/2: v cos + partner sin
+        v[u][e] = lane < 16 ? v[u][e] * c[e] - other * sn[e] : v[u][e] * c[e] + other * sn[e];
+      }
+    }
+    auto store = [&](auto* dst) {
+      using D = std::remove_pointer_t<decltype(dst)>;
+      if constexpr (sizeof(D) == 4) {
+        if constexpr (E == 4) *(float4*)dst = make_float4(v[u][0], v[u][1], v[u][2], v[u][3]);
+        else *(float2*)dst = make_float2(v[u][0], v[u][1]);
+      } else {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(v[u][0], v[u][1]);
+        if constexpr (E == 4) {
+          __nv_bfloat162 hi = __floats2bfloat162_rn(v[u][2], v[u][3]);
+          *(uint2*)dst = make_uint2(*(uint32_t*)&lo, *(uint32_t*)&hi);
+        } else {
+          *(uint32_t*)dst = *(uint32_t*)&lo;
+        }
+      }
+    };
+    if (is_q) {
+      store(q_out + (size_t)t * heads * HD + (size_t)j * HD + lane * E);
+      continue;
+    }
+    const int head = is_k ? j - heads : j - heads - kvh;
+    const long long off = ib::kv_offset(kv, seg_of_token[t], positions[t], head);
+    if (off < 0) {
+      if (lane == 0) atomicOr(status, IB_ERR_BAD_PAGE);
+      continue;
+    }
+    store((C*)kv.base + off + (is_k ? 0 : kv.v_offset) + lane * E);
   }
-  store((C*)kv.base + off + (is_k ? 0 : kv.v_offset) + lane * E);
 }
 
 // acc registers: lane owns dims lane, lane+32, ... (up to 8 for head_dim 256).
@@ -257,18 +270,28 @@ extern "C" int ib_qk_norm_rope_kv(const float* qkv, int P, long long stride_p, c
   const bool aligned = ((uintptr_t)qkv % 16 == 0) && (stride_p % 4 == 0) && ((uintptr_t)q_out % 16 == 0) && ((uintptr_t)kv->base % 16 == 0);
   const bool vec = (hd == 64 || hd == 128) && (rot_half == 0 || 2 * rot_half == hd) && aligned;
   const float* cs = rot_half ? cos_t : nullptr;
-  if (vec && act_dtype == IB_F32 && hd == 128)
-    ib::launch(qk_norm_rope_kv_vec_kernel<128, float, float>, blocks, kWarps * 32, 0, stream, qkv, P, (size_t)stride_p, q_norm_w, k_norm_w, eps, cs,
-               sin_t, positions, seg_of_token, (float*)q_out, *kv, write_kv, T, heads, status);
-  else if (vec && act_dtype == IB_F32)
-    ib::launch(qk_norm_rope_kv_vec_kernel<64, float, float>, blocks, kWarps * 32, 0, stream, qkv, P, (size_t)stride_p, q_norm_w, k_norm_w, eps, cs,
-               sin_t, positions, seg_of_token, (float*)q_out, *kv, write_kv, T, heads, status);
-  else if (vec && hd == 128)
-    ib::launch(qk_norm_rope_kv_vec_kernel<128, __nv_bfloat16, __nv_bfloat16>, blocks, kWarps * 32, 0, stream, qkv, P, (size_t)stride_p, q_norm_w,
-               k_norm_w, eps, cs, sin_t, positions, seg_of_token, (__nv_bfloat16*)q_out, *kv, write_kv, T, heads, status);
-  else if (vec)
-    ib::launch(qk_norm_rope_kv_vec_kernel<64, __nv_bfloat16, __nv_bfloat16>, blocks, kWarps * 32, 0, stream, qkv, P, (size_t)stride_p, q_norm_w,
-               k_norm_w, eps, cs, sin_t, positions, seg_of_token, (__nv_bfloat16*)q_out, *kv, write_kv, T, heads, status);
+  if (vec) {
+    const int slots = heads + 2 * kv->kv_heads;
+    auto go = [&](auto kernel, int per, auto* qo) {
+      const dim3 grid((unsigned)T, (unsigned)((slots + kWarps * per - 1) / (kWarps * per)));
+      ib::launch(kernel, grid, kWarps * 32, 0, stream, qkv, P, (size_t)stride_p, q_norm_w, k_norm_w, eps, cs, sin_t, positions, seg_of_token, qo, *kv,
+                 write_kv, T, heads, status);
+    };
+    const bool many = (long long)T * slots >= 8192;   // a prompt portion: four heads per warp; a few decoded tokens: one
+    if (act_dtype == IB_F32 && hd == 128) {
+      if (many) go(qk_norm_rope_kv_vec_kernel<128, float, float, 4>, 4, (float*)q_out);
+      else go(qk_norm_rope_kv_vec_kernel<128, float, float, 1>, 1, (float*)q_out);
+    } else if (act_dtype == IB_F32) {
+      if (many) go(qk_norm_rope_kv_vec_kernel<64, float, float, 4>, 4, (float*)q_out);
+      else go(qk_norm_rope_kv_vec_kernel<64, float, float, 1>, 1, (float*)q_out);
+    } else if (hd == 128) {
+      if (many) go(qk_norm_rope_kv_vec_kernel<128, __nv_bfloat16, __nv_bfloat16, 4>, 4, (__nv_bfloat16*)q_out);
+      else go(qk_norm_rope_kv_vec_kernel<128, __nv_bfloat16, __nv_bfloat16, 1>, 1, (__nv_bfloat16*)q_out);
+    } else {
+      if (many) go(qk_norm_rope_kv_vec_kernel<64, __nv_bfloat16, __nv_bfloat16, 4>, 4, (__nv_bfloat16*)q_out);
+      else go(qk_norm_rope_kv_vec_kernel<64, __nv_bfloat16, __nv_bfloat16, 1>, 1, (__nv_bfloat16*)q_out);
+    }
+  }
   else if (act_dtype == IB_F32)
     ib::launch(qk_norm_rope_kv_kernel<float, float>, blocks, kWarps * 32, 0, stream, qkv, P, (size_t)stride_p, q_norm_w, k_norm_w, eps, cos_t, sin_t,
                                                                             rot_half, positions, seg_of_token, (float*)q_out, *kv, write_kv,

@@ -6,6 +6,8 @@
 #include <stdarg.h>
 #include <stdio.h>
 
+#include <type_traits>
+
 #include "common.cuh"
 
 static thread_local char g_error[512] = "";
@@ -48,6 +50,12 @@ __global__ void embed_kernel(const W* __restrict__ table, const int* __restrict_
 //   out[r] = w * (v * rsqrt(mean(v^2) + eps))
 // The row lives in dynamic shared memory (H floats) between the two passes.
 // VEC = 4 when H is a multiple of 4 (16-byte loads), else 1.
+// Sum of squares of a row, in one fixed order whatever kernel computes it (so a token's norm does not
+// depend on how many rows share the launch): float4 number f of the row belongs to thread f % 1024 of
+// a block of 1024; a thread adds its float4s in rising order; the 1024 sums are added as 32 warps
+// (shuffle tree), then the 32 warp sums (the same tree). sq4 pins the order inside a float4.
+__device__ __forceinline__ float sq4(float4 v) { return __fmaf_rn(v.w, v.w, __fmaf_rn(v.z, v.z, __fmaf_rn(v.y, v.y, __fmul_rn(v.x, v.x)))); }
+
 template <typename O, int VEC>
 __global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, int P, size_t delta_stride,
                                    const float* __restrict__ w, O* __restrict__ out, const int* __restrict__ rows, int H, float eps,
@@ -83,7 +91,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restric
         if (write_x) *(float4*)(xr + i) = v;
       }
       *(float4*)(row + i) = v;
-      ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+      ss = __fadd_rn(ss, sq4(v));
     }
   } else {
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
@@ -98,7 +106,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restric
       ss += v * v;
     }
   }
-  ss = ib::block_sum(ss, scratch);
+  ss = ib::block_sum(ss, scratch);   // VEC == 4 runs with 1024 threads: the fixed order
   const float inv = rsqrtf(ss / (float)H + eps);
   O* o = out + (size_t)r * H;
   if constexpr (VEC == 4) {
@@ -114,6 +122,73 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restric
     }
   } else {
     for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = ib::from_f32<O>(w[i] * (row[i] * inv));
+  }
+}
+
+// The same for many rows at once (prompt portions): 128 threads per row, the row kept in registers
+// (NV float4 per thread, H <= 512 * NV), so that a thread has NV independent loads in flight and
+// sixteen rows share an SM; the one-CTA-of-1024-threads form above is the faster one for a few rows.
+template <typename O, int NV>
+__global__ void __launch_bounds__(128) add_rmsnorm_rows_kernel(float* __restrict__ x, const float* __restrict__ delta, int P, size_t delta_stride,
+                                                                const float* __restrict__ w, O* __restrict__ out, const int* __restrict__ rows,
+                                                                int H, float eps, int write_x) {
+  __shared__ float scratch[32];
+  ib::pdl_launch_dependents();
+  ib::pdl_wait();
+  const int r = blockIdx.x;
+  const int t = rows ? rows[r] : r;
+  float* xr = x + (size_t)t * H;
+  const float* dr = delta + (size_t)t * H;
+  float4 v[NV];
+#pragma unroll
+  for (int k = 0; k < NV; k++) {
+    const int i = (k * 128 + threadIdx.x) * 4;
+    v[k] = i < H ? *(const float4*)(xr + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  if (P > 0) {
+#pragma unroll
+    for (int k = 0; k < NV; k++) {
+      const int i = (k * 128 + threadIdx.x) * 4;
+      if (i >= H) continue;
+      float4 d = *(const float4*)(dr + i);
+      for (int p = 1; p < P; p++) {
+        const float4 a = *(const float4*)(dr + p * delta_stride + i);
+        d.x += a.x, d.y += a.y, d.z += a.z, d.w += a.w;
+      }
+      v[k].x += d.x, v[k].y += d.y, v[k].z += d.z, v[k].w += d.w;
+      if (write_x) *(float4*)(xr + i) = v[k];
+    }
+  }
+  // the fixed order: float4 k * 128 + tid is thread (k % 8) * 128 + tid of the block of 1024, so each of this
+  // block's warps holds, for every k < 8, exactly one warp of the 1024
+  float part[8];
+#pragma unroll
+  for (int k = 0; k < 8; k++) {
+    part[k] = (k < NV && (k * 128 + threadIdx.x) * 4 < H) ? sq4(v[k < NV ? k : 0]) : 0.f;
+    if (k + 8 < NV && ((k + 8) * 128 + threadIdx.x) * 4 < H) part[k] = __fadd_rn(part[k], sq4(v[k + 8 < NV ? k + 8 : 0]));
+    part[k] = ib::warp_sum(part[k]);
+  }
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) {
+#pragma unroll
+    for (int k = 0; k < 8; k++) scratch[4 * k + (threadIdx.x >> 5)] = part[k];
+  }
+  __syncthreads();
+  const float ss = ib::warp_sum(scratch[threadIdx.x & 31]);
+  const float inv = rsqrtf(ss / (float)H + eps);
+  O* o = out + (size_t)r * H;
+#pragma unroll
+  for (int k = 0; k < NV; k++) {
+    const int i = (k * 128 + threadIdx.x) * 4;
+    if (i >= H) continue;
+    const float4 g = *(const float4*)(w + i);
+    const float a = g.x * (v[k].x * inv), b = g.y * (v[k].y * inv), c = g.z * (v[k].z * inv), d = g.w * (v[k].w * inv);
+    if constexpr (sizeof(O) == 4) {
+      *(float4*)((float*)o + i) = make_float4(a, b, c, d);
+    } else {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+      *(uint2*)((__nv_bfloat16*)o + i) = make_uint2(*(uint32_t*)&lo, *(uint32_t*)&hi);
+    }
   }
 }
 
@@ -179,8 +254,24 @@ extern "C" int ib_add_rmsnorm(float* x, const float* delta, int P, long long del
   IB_CHECK_ARG(smem <= 200 * 1024, "add_rmsnorm: hidden size %d needs %zu bytes of shared memory, more than 200 KiB", H, smem);
   const bool vec = H % 4 == 0 && ((uintptr_t)x % 16 == 0) && (!delta || (uintptr_t)delta % 16 == 0) && ((uintptr_t)w % 16 == 0) &&
                    ((uintptr_t)out % 16 == 0) && (delta_stride % 4 == 0);
+  if (vec && n_rows >= 256 && H <= 8192) {   // many rows: the register form
+    auto go_rows = [&](auto* o) {
+      using O = std::remove_pointer_t<decltype(o)>;
+      const int nv = (H + 511) / 512;
+      if (nv <= 1) ib::launch(add_rmsnorm_rows_kernel<O, 1>, n_rows, 128, 0, stream, x, delta, P, (size_t)delta_stride, w, o, rows, H, eps, write_x);
+      else if (nv <= 2) ib::launch(add_rmsnorm_rows_kernel<O, 2>, n_rows, 128, 0, stream, x, delta, P, (size_t)delta_stride, w, o, rows, H, eps, write_x);
+      else if (nv <= 4) ib::launch(add_rmsnorm_rows_kernel<O, 4>, n_rows, 128, 0, stream, x, delta, P, (size_t)delta_stride, w, o, rows, H, eps, write_x);
+      else if (nv <= 8) ib::launch(add_rmsnorm_rows_kernel<O, 8>, n_rows, 128, 0, stream, x, delta, P, (size_t)delta_stride, w, o, rows, H, eps, write_x);
+      else ib::launch(add_rmsnorm_rows_kernel<O, 16>, n_rows, 128, 0, stream, x, delta, P, (size_t)delta_stride, w, o, rows, H, eps, write_x);
+    };
+    if (out_dtype == IB_F32) go_rows((float*)out);
+    else if (out_dtype == IB_BF16) go_rows((__nv_bfloat16*)out);
+    else return ib_set_error("add_rmsnorm: unknown output dtype %d", out_dtype);
+    IB_CHECK_LAUNCH("add_rmsnorm");
+    return 0;
+  }
   const int per = vec ? 4 : 1;
-  int threads = H / per >= 1024 ? 1024 : (H / per >= 512 ? 512 : (H / per >= 256 ? 256 : 128));
+  int threads = vec ? 1024 : (H >= 1024 ? 1024 : (H >= 512 ? 512 : (H >= 256 ? 256 : 128)));   // 16-byte form: always 1024, the fixed summation order
   auto go = [&](auto kernel, auto* o) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     ib::launch(kernel, n_rows, threads, smem, stream, x, delta, P, (size_t)delta_stride, w, o, rows, H, eps, write_x);
