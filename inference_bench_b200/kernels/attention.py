@@ -32,19 +32,6 @@ def decode_tiles_per_slice(n_dec: int, kv_heads: int, max_keys: int) -> int:
 _SM_COUNT: dict = {}
 
 
-def stream_pays(n_dec: int, kv_heads: int, device) -> bool:
-    """Whether the streaming decode kernel is the faster one: measured inside whole decode steps at
-    Qwen3-8B shape, it wins (by up to 6 % of the step) from 4 to 32 requests of 8 kv heads, where the
-    kernel with one CTA per slice runs a few short waves of CTAs; with fewer (token, kv head) pairs every
-    slice gets a CTA at once and the shorter start decides, and with more pairs than CTAs that stay, the
-    longer waves of the other kernel overlap better with the kernels around it."""
-    if STREAM_ALWAYS:
-        return True
-    if device not in _SM_COUNT:
-        _SM_COUNT[device] = torch.cuda.get_device_properties(device).multi_processor_count
-    return 24 <= n_dec * kv_heads <= 2 * _SM_COUNT[device]
-
-
 def stream_slices(n_dec: int, kv_heads: int, max_keys: int, device) -> int:
     """Into how many slices the streaming decode kernel cuts each token's keys. Its CTAs stay (two per
     SM) and take (slice, token, kv head) units in turn: with few tokens, as many slices as give every
@@ -65,8 +52,8 @@ PREFILL_KERNEL = "ws"   # which one the engine uses: "ws" (tcgen05, one job per 
 
 L.register("ib_attention_decode", [L._p, C.POINTER(L.KvView), L._p, L._i, L._p, L._p, L._i, L._f, L._p, L._p, L._p, L._i, L._i, L._i, L._p, L._ll, L._p, L._p])
 L.register("ib_attention_decode_stream", [L._p, C.POINTER(L.KvView), L._p, L._i, L._p, L._p, L._i, L._f, L._p, L._p, L._p, L._i, L._i, L._i, L._p, L._ll, L._p, L._p])
-DECODE_KERNEL = "stream"   # "stream": CTAs that stay and a ring that TMA fills (needs a page size TMA can serve); "split": one CTA per slice
-STREAM_ALWAYS = False        # tests set this to reach the streaming kernel at any batch size
+DECODE_KERNEL = "stream"   # "stream": CTAs that stay and a ring that TMA fills (needs a page size TMA can serve; measured inside whole decode steps
+                           # at Qwen3-8B shape and page size 64 it is the faster one from 1 to 128 requests, by 1 to 7 %); "split": one CTA per slice
 STREAM_TILES_PER_SLICE = 0   # 0: every token's visible keys in stream_slices() equal parts; n > 0: slices of n tiles at fixed positions
 USE_TMA = False  # decode keys and values by TMA box copies (one thread, one 2 KiB box per page and plane) instead of cp.async by all
                  # threads: measured slower at page size 16 (3.86 against 3.71 ms per step at batch 8), so off; kept and tested
@@ -119,7 +106,7 @@ def paged_attention(ctx, q: torch.Tensor, cache: ops.KvLayerView, heads: int, wi
     if work["n_dec"]:
         limit = view.table_stride * view.page_size
         max_keys = limit if work["max_pos"] is None else work["max_pos"] + 1
-        stream_map, stream_row0 = cache.tma() if DECODE_KERNEL == "stream" and stream_pays(work["n_dec"], view.kv_heads, q.device) else (None, 0)
+        stream_map, stream_row0 = cache.tma() if DECODE_KERNEL == "stream" else (None, 0)
         if stream_map:
             tps = STREAM_TILES_PER_SLICE
             max_slices = -(-max_keys // (tps * decode_tile())) if tps else stream_slices(work["n_dec"], view.kv_heads, max_keys, q.device)

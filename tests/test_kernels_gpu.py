@@ -292,7 +292,6 @@ def test_attention_decode_slices_of_several_tiles(status, monkeypatch, tiles_per
     from inference_bench_b200.kernels import lib as L
     monkeypatch.setattr(attention, "decode_tiles_per_slice", lambda *a: tiles_per_slice)
     monkeypatch.setattr(attention, "STREAM_TILES_PER_SLICE", tiles_per_slice)
-    monkeypatch.setattr(attention, "STREAM_ALWAYS", True)
     monkeypatch.setattr(attention, "DECODE_KERNEL", kernel)
     monkeypatch.setattr(attention, "USE_TMA", tma)
     called = []
@@ -321,7 +320,6 @@ def test_attention_decode_stream_many_units_per_cta(status, monkeypatch):
     heads, kvh, hd, page = 8, 8, 128, 16
     shapes = [(L_, 1) for L_ in (1500, 3, 700, 64, 1100, 129, 1, 900, 1300, 450, 31, 640)]
     rt = Runtime(DEV, "bfloat16")
-    monkeypatch.setattr(attention, "STREAM_ALWAYS", True)
     for fixed, window in ((1, None), (0, None), (0, 500), (0, 70)):   # slices of one tile at fixed places; each token's keys in equal parts
         monkeypatch.setattr(attention, "STREAM_TILES_PER_SLICE", fixed)
         q, view, pos, seg, ref, _ = _attention_case(torch.bfloat16, heads, kvh, hd, page, window, shapes, 22, needle=True)
