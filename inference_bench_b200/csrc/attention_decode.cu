@@ -399,9 +399,27 @@ constexpr int kMeta = 256;   // decoded tokens whose row, position and segment a
 
 __device__ __forceinline__ void bar_sync_compute() { asm volatile("bar.sync 1, %0;" ::"n"(kWarps * 32) : "memory"); }
 
-template <int HD>
+// What the fused form works from instead of finished queries: the products of the q/k/v projection as the
+// matrix-product kernel left them (float32 partial sums [P][T][(heads + 2 kv_heads) * head_dim]), the
+// per-head norm scales (or null) and the step's rotation tables (or null). The kernel then norms and turns
+// the queries itself, and the CTA whose slice holds a token's own position does the same for its key,
+// stores key and value in the cache (write_kv) and attends to them from shared memory: the own position
+// is never read back from the cache, so nothing this kernel copies depends on the kernel before it.
+struct RawQkv {
+  const float* qkv;
+  int P;
+  long long stride_p;
+  const float* q_norm_w;
+  const float* k_norm_w;
+  float eps;
+  const float* cos_t;
+  const float* sin_t;
+  int write_kv;
+};
+
+template <int HD, bool FUSED>
 __global__ void __launch_bounds__((kWarps + 1) * 32, 2)
-    decode_stream_kernel(const __nv_bfloat16* __restrict__ q, IbKvView kv, const int* __restrict__ dec_tokens, const int* __restrict__ positions,
+    decode_stream_kernel(const __nv_bfloat16* __restrict__ q, RawQkv raw, IbKvView kv, const int* __restrict__ dec_tokens, const int* __restrict__ positions,
                          const int* __restrict__ seg_of_token, int window, float scale_log2e, float* __restrict__ part_o,
                          float* __restrict__ part_ml, int heads, int n_dec, int max_slices, int tiles_per_slice,
                          const __grid_constant__ CUtensorMap kv_map, long long view_row0, unsigned* __restrict__ status) {
@@ -419,6 +437,9 @@ __global__ void __launch_bounds__((kWarps + 1) * 32, 2)
   uint64_t* empty = full + kRing;
   volatile int* gave_up = (volatile int*)(empty + kRing);
   int* meta = (int*)(empty + kRing) + 2;   // [kMeta][3]
+  float* k_own = (float*)(meta + 3 * kMeta);   // fused form: the token's own key and value (bfloat16 values), and its scores per head
+  float* v_own = k_own + HD;
+  float* s_own = v_own + HD;                   // [16]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if ((mt::smem_u32(smem) & 1023u) != 0) {   // the swizzle of the box copies counts from 1024-byte boundaries
     if (tid == 0) atomicOr(status, IB_ERR_INTERNAL);
@@ -448,6 +469,7 @@ __global__ void __launch_bounds__((kWarps + 1) * 32, 2)
   __syncthreads();
   // unit -> what it covers; false when it holds no visible key
   int kvh, item, slice, t, pos, seg, k_begin, k_end;
+  bool has_own = false;   // fused form: the unit's slice holds the token's own position
   auto open_unit = [&](int u) {
     kvh = u % kv.kv_heads;
     const int r = u / kv.kv_heads;
@@ -466,6 +488,11 @@ __global__ void __launch_bounds__((kWarps + 1) * 32, 2)
     slice_plan(pos, window, max_slices, tiles_per_slice, lo, tile_lo, tps);
     k_begin = max(lo, (tile_lo + slice * tps) * kTile);
     k_end = min(pos + 1, (tile_lo + (slice + 1) * tps) * kTile);
+    if constexpr (FUSED) {   // the own position comes from the projection, not from the cache
+      has_own = k_begin < k_end && k_end == pos + 1;
+      if (has_own) k_end = pos;
+      return has_own || k_begin < k_end;
+    }
     return k_begin < k_end;
   };
   auto next_unit = [&](int u) {   // the first unit from u on, in this CTA's stride, that holds a visible key; opened
@@ -482,7 +509,7 @@ __global__ void __launch_bounds__((kWarps + 1) * 32, 2)
     bool waited = false;   // the kernel before this one writes only the rows of the tokens' own positions
     bool ok = true;
     for (int u = next_unit(blockIdx.x); u < n_units && ok; u = next_unit(u + gridDim.x)) {
-      const int tile_begin = k_begin / kTile, tile_end = (k_end - 1) / kTile + 1;
+      const int tile_begin = k_begin / kTile, tile_end = k_begin < k_end ? (k_end - 1) / kTile + 1 : tile_begin;
       int held = -2;       // page of box (tile_begin * ppt + base + lane), looked up 32 boxes at a time
       for (int tile = tile_begin; tile < tile_end; tile++, n++) {
         const int rel = (tile - tile_begin) * ppt;
@@ -497,7 +524,7 @@ __global__ void __launch_bounds__((kWarps + 1) * 32, 2)
         const bool valid = mine && held >= 0 && held < kv.num_pages;
         if (mine && held != -2 && !valid) atomicOr(status, IB_ERR_BAD_PAGE);
         const unsigned vmask = __ballot_sync(0xffffffffu, valid);
-        if (!waited && pos >= tile * kTile && pos < (tile + 1) * kTile) {
+        if (!FUSED && !waited && pos >= tile * kTile && pos < (tile + 1) * kTile) {
           ib::pdl_wait();
           waited = true;
         }
@@ -558,19 +585,116 @@ __global__ void __launch_bounds__((kWarps + 1) * 32, 2)
     }
     mt::cp_async_commit();
   };
+  // ---- the fused form: one head of the projection's output -> summed, normed, turned; E values per lane
+  constexpr int E = HD / 32;
+  const int R = (heads + 2 * kv.kv_heads) * HD;
+  auto load_head = [&](int j, float (&v)[E]) {   // the sum, in order, of the partial products of head j
+    const float* src = raw.qkv + (size_t)t * R + (size_t)j * HD + lane * E;
+#pragma unroll
+    for (int e = 0; e < E; e++) v[e] = 0.f;
+    for (int p = 0; p < raw.P; p++) {
+      if constexpr (E == 4) {
+        const float4 a = *(const float4*)(src + p * raw.stride_p);
+        v[0] += a.x, v[1] += a.y, v[2] += a.z, v[3] += a.w;
+      } else {
+        const float2 a = *(const float2*)(src + p * raw.stride_p);
+        v[0] += a.x, v[1] += a.y;
+      }
+    }
+  };
+  auto finish_head = [&](const float* norm_w, bool turn, float (&v)[E]) {   // norm and rotation
+    if (norm_w) {
+      float ss = 0.f;
+#pragma unroll
+      for (int e = 0; e < E; e++) ss += v[e] * v[e];
+      ss = ib::warp_sum(ss);
+      const float inv = rsqrtf(ss / (float)HD + raw.eps);
+#pragma unroll
+      for (int e = 0; e < E; e++) v[e] = norm_w[lane * E + e] * (v[e] * inv);
+    }
+    if (turn && raw.cos_t) {
+      const float* c = raw.cos_t + (size_t)t * (HD / 2) + (lane & 15) * E;
+      const float* sn = raw.sin_t + (size_t)t * (HD / 2) + (lane & 15) * E;
+#pragma unroll
+      for (int e = 0; e < E; e++) {
+        const float other = __shfl_xor_sync(0xffffffffu, v[e], 16);
+        v[e] = lane < 16 ? v[e] * c[e] - other * sn[e] : v[e] * c[e] + other * sn[e];
+      }
+    }
+  };
+  auto q_row_addr = [&](int row) { return q_s + mt::tile_offset<HD, 16>(row, lane * E / 8) + (lane * E * 2) % 16; };   // this lane's E values of a Q row
+  auto make_unit_inputs = [&]() {   // the opened unit's query rows, and its own key and value if its slice holds them
+    const bool own_mine = has_own && warp < 2;   // warp 0: the key (normed and turned); warp 1: the value
+    float vo[E];
+    if (own_mine) load_head(warp == 0 ? heads + kvh : heads + kv.kv_heads + kvh, vo);   // requested together with the first query row
+    for (int row = warp; row < group; row += kWarps) {
+      float v[E];
+      load_head(kvh * group + row, v);
+      finish_head(raw.q_norm_w, true, v);
+      if constexpr (E == 4)
+        asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(q_row_addr(row)), "r"(mt::pack_bf16(v[0], v[1])), "r"(mt::pack_bf16(v[2], v[3])) : "memory");
+      else
+        asm volatile("st.shared.b32 [%0], %1;" ::"r"(q_row_addr(row)), "r"(mt::pack_bf16(v[0], v[1])) : "memory");
+    }
+    if (own_mine) {
+      float (&v)[E] = vo;
+      finish_head(warp == 0 ? raw.k_norm_w : nullptr, warp == 0, v);
+      __nv_bfloat16 b[E];
+      float* own = warp == 0 ? k_own : v_own;
+#pragma unroll
+      for (int e = 0; e < E; e++) {
+        b[e] = __float2bfloat16_rn(v[e]);
+        own[lane * E + e] = __bfloat162float(b[e]);
+      }
+      if (raw.write_kv) {
+        const long long off = ib::kv_offset(kv, seg, pos, kvh);
+        if (off < 0) {
+          if (lane == 0) atomicOr(status, IB_ERR_BAD_PAGE);
+        } else {
+          __nv_bfloat16* dst = (__nv_bfloat16*)kv.base + off + (warp == 0 ? 0 : kv.v_offset) + lane * E;
+          if constexpr (E == 4)
+            *(uint2*)dst = *(const uint2*)b;
+          else
+            *(uint32_t*)dst = *(const uint32_t*)b;
+        }
+      }
+    }
+  };
+  auto own_scores = [&]() {   // s_own[row] = scale * q_row . k_own, from the rounded values the tensor core would see
+    for (int row = warp; row < group; row += kWarps) {
+      float dot = 0.f;
+      uint32_t w0, w1 = 0;
+      if constexpr (E == 4)
+        asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(w0), "=r"(w1) : "r"(q_row_addr(row)));
+      else
+        asm volatile("ld.shared.b32 %0, [%1];" : "=r"(w0) : "r"(q_row_addr(row)));
+      dot += __uint_as_float(w0 << 16) * k_own[lane * E] + __uint_as_float(w0 & 0xffff0000u) * k_own[lane * E + 1];
+      if constexpr (E == 4) dot += __uint_as_float(w1 << 16) * k_own[lane * E + 2] + __uint_as_float(w1 & 0xffff0000u) * k_own[lane * E + 3];
+      dot = ib::warp_sum(dot);
+      if (lane == 0) s_own[row] = dot * scale_log2e;
+    }
+  };
+
   int u = next_unit(blockIdx.x);
-  if (u < n_units) fetch_q();
+  if (!FUSED && u < n_units) fetch_q();
   while (u < n_units) {
-    mt::cp_async_wait<0>();
+    if constexpr (FUSED) {
+      bar_sync_compute();   // every warp is done with the last unit's Q tile and merge buffers
+      make_unit_inputs();
+    } else {
+      mt::cp_async_wait<0>();
+    }
     bar_sync_compute();   // the Q tile is whole; every warp is done with the last unit's merge buffers
     uint32_t qa[HD / 16][4];
 #pragma unroll
     for (int kk = 0; kk < HD / 16; kk++) mt::load_a_frag<HD, 16>(q_s, 0, kk, lane, qa[kk]);
-    bar_sync_compute();   // every warp holds its fragments: the Q tile is free for the next unit's rows, which travel during this unit
+    if (FUSED && has_own) own_scores();
+    if (!FUSED) bar_sync_compute();   // every warp holds its fragments: the Q tile is free for the next unit's rows, which travel during this unit
+    const bool own_here = has_own;
     const int u_next = next_unit(u + gridDim.x);
-    if (u_next < n_units) fetch_q();
+    if (!FUSED && u_next < n_units) fetch_q();
     open_unit(u);
-    const int tile_begin = k_begin / kTile, tile_end = (k_end - 1) / kTile + 1;
+    const int tile_begin = k_begin / kTile, tile_end = k_begin < k_end ? (k_end - 1) / kTile + 1 : tile_begin;
 
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
     float o[HD / 8][4];
@@ -681,6 +805,7 @@ __global__ void __launch_bounds__((kWarps + 1) * 32, 2)
       float M = -INFINITY;
 #pragma unroll
       for (int w = 0; w < kWarps; w++) M = fmaxf(M, ml_s[(w * 16 + row) * 2]);
+      if (FUSED && own_here) M = fmaxf(M, s_own[row]);
       float Lsum = 0.f, O = 0.f;
 #pragma unroll
       for (int w = 0; w < kWarps; w++) {
@@ -688,6 +813,11 @@ __global__ void __launch_bounds__((kWarps + 1) * 32, 2)
         const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
         Lsum += ml_s[(w * 16 + row) * 2 + 1] * f;
         O += o_s[(w * group + row) * HD + d] * f;
+      }
+      if (FUSED && own_here) {   // the token's own key and value, as one more partial result
+        const float f = exp2f(s_own[row] - M);
+        Lsum += f;
+        O += v_own[d] * f;
       }
       const size_t slot = ((size_t)item * heads + (size_t)kvh * group + row) * max_slices + slice;
       part_o[slot * HD + d] = O;
@@ -700,17 +830,18 @@ __global__ void __launch_bounds__((kWarps + 1) * 32, 2)
   }
 }
 
-template <int HD>
-int launch_stream(const void* q, const IbKvView* kv, const int* dec_tokens, int n_dec, const int* positions, const int* seg_of_token, int window,
-                  float scale, float* part_o, float* part_ml, void* out, int heads, int max_slices, int tiles_per_slice, const CUtensorMap* kv_map,
-                  long long view_row0, unsigned* status, cudaStream_t stream) {
+template <int HD, bool FUSED>
+int launch_stream(const void* q, const RawQkv* raw, const IbKvView* kv, const int* dec_tokens, int n_dec, const int* positions, const int* seg_of_token,
+                  int window, float scale, float* part_o, float* part_ml, void* out, int heads, int max_slices, int tiles_per_slice,
+                  const CUtensorMap* kv_map, long long view_row0, unsigned* status, cudaStream_t stream) {
   const int group = heads / kv->kv_heads;
-  const int smem = kRing * 2 * kTile * HD * 2 + 16 * HD * 2 + kWarps * 16 * 2 * 4 + kWarps * group * HD * 4 + 2 * kRing * 8 + 16 + kMeta * 12;
+  const int smem = kRing * 2 * kTile * HD * 2 + 16 * HD * 2 + kWarps * 16 * 2 * 4 + kWarps * group * HD * 4 + 2 * kRing * 8 + 16 + kMeta * 12 +
+                   (2 * HD + 16) * 4;
   static int reserved = 0, per_sm = 0, sms = 0;
   if (smem != reserved) {
-    cudaError_t e = cudaFuncSetAttribute(decode_stream_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(decode_stream_kernel<HD, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     IB_CHECK_ARG(e == cudaSuccess, "attention_decode_stream: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
-    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_stream_kernel<HD>, (kWarps + 1) * 32, smem);
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_stream_kernel<HD, FUSED>, (kWarps + 1) * 32, smem);
     IB_CHECK_ARG(e == cudaSuccess && per_sm >= 1, "attention_decode_stream: no CTA fits an SM with %d bytes of shared memory", smem);
     int dev = 0;
     cudaGetDevice(&dev);
@@ -720,8 +851,10 @@ int launch_stream(const void* q, const IbKvView* kv, const int* dec_tokens, int 
   const long long units = (long long)max_slices * n_dec * kv->kv_heads;
   IB_CHECK_ARG(units < (1ll << 31), "attention_decode_stream: %lld units", units);
   const int grid = (int)(units < (long long)sms * per_sm ? units : (long long)sms * per_sm);
-  ib::launch(decode_stream_kernel<HD>, grid, (kWarps + 1) * 32, smem, stream, (const __nv_bfloat16*)q, *kv, dec_tokens, positions, seg_of_token,
-             window, scale * 1.4426950408889634f, part_o, part_ml, heads, n_dec, max_slices, tiles_per_slice, *kv_map, view_row0, status);
+  const RawQkv none = {};
+  ib::launch(decode_stream_kernel<HD, FUSED>, grid, (kWarps + 1) * 32, smem, stream, (const __nv_bfloat16*)q, raw ? *raw : none, *kv, dec_tokens,
+             positions, seg_of_token, window, scale * 1.4426950408889634f, part_o, part_ml, heads, n_dec, max_slices, tiles_per_slice, *kv_map,
+             view_row0, status);
   IB_CHECK_LAUNCH("attention_decode_stream split");
   ib::launch(decode_combine_kernel<HD>, dim3(heads, n_dec), kCombineThreads, 0, stream, part_o, part_ml, dec_tokens, positions, window, (__nv_bfloat16*)out, heads,
              max_slices, tiles_per_slice);
@@ -807,13 +940,10 @@ extern "C" int ib_attention_decode(const void* q, const IbKvView* kv, const int*
   return ib_set_error("attention_decode: head_dim %d has no tensor-core kernel (64 and 128 have)", kv->head_dim);
 }
 
-// The streaming variant: the same arguments and scratch; kv_map is required, and the page size must be a
-// multiple of 8 that divides the tile or a multiple of the tile. tiles_per_slice = 0 cuts every token's
-// visible keys into max_slices equal slices (of two tiles at least) instead of slices at fixed positions.
-extern "C" int ib_attention_decode_stream(const void* q, const IbKvView* kv, const int* dec_tokens, int n_dec, const int* positions,
-                                          const int* seg_of_token, int window, float scale, float* part_o, float* part_ml, void* out,
-                                          int heads, int max_slices, int tiles_per_slice, const void* kv_map, long long view_row0,
-                                          unsigned* status, cudaStream_t stream) {
+namespace {
+int stream_entry(const void* q, const RawQkv* raw, const IbKvView* kv, const int* dec_tokens, int n_dec, const int* positions, const int* seg_of_token,
+                 int window, float scale, float* part_o, float* part_ml, void* out, int heads, int max_slices, int tiles_per_slice,
+                 const void* kv_map, long long view_row0, unsigned* status, cudaStream_t stream) {
   if (n_dec == 0) return 0;
   IB_CHECK_ARG(kv && kv->base && kv->block_table && kv_map, "attention_decode_stream: the cache view or the tensor map is a null pointer");
   IB_CHECK_ARG(kv->page_size % 8 == 0 && (kTile % kv->page_size == 0 || kv->page_size % kTile == 0),
@@ -824,13 +954,52 @@ extern "C" int ib_attention_decode_stream(const void* q, const IbKvView* kv, con
                "attention_decode_stream: %d query heads on %d kv heads (groups of up to 16 are supported)", heads, kv->kv_heads);
   IB_CHECK_ARG(n_dec > 0 && n_dec <= 65535 && max_slices > 0 && max_slices <= 65535, "attention_decode_stream: bad sizes n=%d slices=%d", n_dec, max_slices);
   IB_CHECK_ARG(kv->page_stride % kv->head_dim == 0 && kv->v_offset % kv->head_dim == 0, "attention_decode_stream: strides are not whole rows");
-  if (kv->head_dim == 128)
-    return launch_stream<128>(q, kv, dec_tokens, n_dec, positions, seg_of_token, window, scale, part_o, part_ml, out, heads, max_slices,
-                              tiles_per_slice, (const CUtensorMap*)kv_map, view_row0, status, stream);
-  if (kv->head_dim == 64)
-    return launch_stream<64>(q, kv, dec_tokens, n_dec, positions, seg_of_token, window, scale, part_o, part_ml, out, heads, max_slices,
-                             tiles_per_slice, (const CUtensorMap*)kv_map, view_row0, status, stream);
+  const CUtensorMap* map = (const CUtensorMap*)kv_map;
+  if (kv->head_dim == 128) {
+    if (raw) return launch_stream<128, true>(q, raw, kv, dec_tokens, n_dec, positions, seg_of_token, window, scale, part_o, part_ml, out, heads, max_slices,
+                                             tiles_per_slice, map, view_row0, status, stream);
+    return launch_stream<128, false>(q, raw, kv, dec_tokens, n_dec, positions, seg_of_token, window, scale, part_o, part_ml, out, heads, max_slices,
+                                     tiles_per_slice, map, view_row0, status, stream);
+  }
+  if (kv->head_dim == 64) {
+    if (raw) return launch_stream<64, true>(q, raw, kv, dec_tokens, n_dec, positions, seg_of_token, window, scale, part_o, part_ml, out, heads, max_slices,
+                                            tiles_per_slice, map, view_row0, status, stream);
+    return launch_stream<64, false>(q, raw, kv, dec_tokens, n_dec, positions, seg_of_token, window, scale, part_o, part_ml, out, heads, max_slices,
+                                    tiles_per_slice, map, view_row0, status, stream);
+  }
   return ib_set_error("attention_decode_stream: head_dim %d has no tensor-core kernel (64 and 128 have)", kv->head_dim);
+}
+}  // namespace
+
+// The streaming variant: the same arguments and scratch; kv_map is required, and the page size must be a
+// multiple of 8 that divides the tile or a multiple of the tile. tiles_per_slice = 0 cuts every token's
+// visible keys into max_slices equal slices (of two tiles at least) instead of slices at fixed positions.
+extern "C" int ib_attention_decode_stream(const void* q, const IbKvView* kv, const int* dec_tokens, int n_dec, const int* positions,
+                                          const int* seg_of_token, int window, float scale, float* part_o, float* part_ml, void* out,
+                                          int heads, int max_slices, int tiles_per_slice, const void* kv_map, long long view_row0,
+                                          unsigned* status, cudaStream_t stream) {
+  IB_CHECK_ARG(q || n_dec == 0, "attention_decode_stream: q is a null pointer");
+  return stream_entry(q, nullptr, kv, dec_tokens, n_dec, positions, seg_of_token, window, scale, part_o, part_ml, out, heads, max_slices,
+                      tiles_per_slice, kv_map, view_row0, status, stream);
+}
+
+// The same from the output of the q/k/v projection (float32 partial sums qkv [P][T][(heads + 2 kv_heads) * head_dim],
+// stride_p elements apart), for steps of decoded tokens only: sums the partial products, applies the per-head
+// norms (q_norm_w, k_norm_w: float32 [head_dim] or null) and the rotation (cos_t, sin_t: float32 [T][head_dim / 2]
+// or null) to queries and keys, stores every token's key and value at its position in the cache (write_kv) and
+// attends. It stands for ib_qk_norm_rope_kv followed by ib_attention_decode_stream.
+extern "C" int ib_attention_decode_fused(const float* qkv, int P, long long stride_p, const float* q_norm_w, const float* k_norm_w, float eps,
+                                         const float* cos_t, const float* sin_t, int write_kv, const IbKvView* kv, const int* dec_tokens,
+                                         int n_dec, const int* positions, const int* seg_of_token, int window, float scale, float* part_o,
+                                         float* part_ml, void* out, int heads, int max_slices, int tiles_per_slice, const void* kv_map,
+                                         long long view_row0, unsigned* status, cudaStream_t stream) {
+  if (n_dec == 0) return 0;
+  IB_CHECK_ARG(qkv && P >= 1 && stride_p > 0, "attention_decode_fused: no projection output (P=%d)", P);
+  IB_CHECK_ARG(((uintptr_t)qkv % 16) == 0 && stride_p % 4 == 0, "attention_decode_fused: the projection output must be 16-byte aligned");
+  IB_CHECK_ARG((cos_t == nullptr) == (sin_t == nullptr), "attention_decode_fused: cos and sin tables come together");
+  const RawQkv raw = {qkv, P, stride_p, q_norm_w, k_norm_w, eps, cos_t, sin_t, write_kv};
+  return stream_entry(nullptr, &raw, kv, dec_tokens, n_dec, positions, seg_of_token, window, scale, part_o, part_ml, out, heads, max_slices,
+                      tiles_per_slice, kv_map, view_row0, status, stream);
 }
 
 // ---------------------------------------------------------------- the variant that allocates nothing

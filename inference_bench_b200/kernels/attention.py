@@ -52,6 +52,11 @@ PREFILL_KERNEL = "ws"   # which one the engine uses: "ws" (tcgen05, one job per 
 
 L.register("ib_attention_decode", [L._p, C.POINTER(L.KvView), L._p, L._i, L._p, L._p, L._i, L._f, L._p, L._p, L._p, L._i, L._i, L._i, L._p, L._ll, L._p, L._p])
 L.register("ib_attention_decode_stream", [L._p, C.POINTER(L.KvView), L._p, L._i, L._p, L._p, L._i, L._f, L._p, L._p, L._p, L._i, L._i, L._i, L._p, L._ll, L._p, L._p])
+L.register("ib_attention_decode_fused", [L._p, L._i, L._ll, L._p, L._p, L._f, L._p, L._p, L._i, C.POINTER(L.KvView), L._p, L._i, L._p, L._p, L._i, L._f, L._p, L._p,
+                                         L._p, L._i, L._i, L._i, L._p, L._ll, L._p, L._p])
+FUSE_DECODE = True   # steps of decoded tokens only: q/k norm, rotation and the cache write inside the streaming decode kernel
+FUSE_DECODE_MAX_PAIRS = 128   # ... up to this many (token, kv head) pairs: every unit of the kernel prepares its queries again, which costs
+                              # more than the saved kernel from about 16 requests of 8 kv heads on (measured inside whole decode steps)
 DECODE_KERNEL = "stream"   # "stream": CTAs that stay and a ring that TMA fills (needs a page size TMA can serve; measured inside whole decode steps
                            # at Qwen3-8B shape and page size 64 it is the faster one from 1 to 128 requests, by 1 to 7 %); "split": one CTA per slice
 STREAM_TILES_PER_SLICE = 0   # 0: every token's visible keys in stream_slices() equal parts; n > 0: slices of n tiles at fixed positions
@@ -91,6 +96,53 @@ def _work_lists(ctx):
                     max_pos=int(ctx.h_positions[dec].max()) if nd else None)
     ctx.memo[key] = work
     return work
+
+
+def decode_fused(ctx, qkv: torch.Tensor, q_norm_w, k_norm_w, eps: float, cos, sin, cache: ops.KvLayerView, heads: int, window: Optional[int],
+                 scale: float, write_kv: bool) -> Optional[torch.Tensor]:
+    """Attention for a step of decoded tokens only, straight from the q/k/v projection's partial sums
+    qkv float32 [P, T, (heads + 2 kv_heads) * hd]: what `ops.qk_norm_rope_kv` and `paged_attention` do
+    together, in one kernel (csrc/attention_decode.cu, the fused form). Returns None when that kernel
+    cannot take the step (prompt portions in it, float32, a head size or page size it does not have,
+    a rotation over part of the head): the caller then runs the two steps."""
+    rt = ctx.rt
+    view = cache.c_view()
+    hd = view.head_dim
+    if not (FUSE_DECODE and DECODE_KERNEL == "stream" and rt.act_dtype == torch.bfloat16 and has_tensor_core_kernel(rt.act_dtype, hd, heads, view.kv_heads)):
+        return None
+    if cos is not None and 2 * cos.shape[1] != hd:
+        return None
+    work = _work_lists(ctx)
+    if work["n_tiles"] or not work["n_dec"]:
+        return None
+    kv_map, row0 = cache.tma()
+    if not kv_map or work["n_dec"] * view.kv_heads > FUSE_DECODE_MAX_PAIRS:
+        return None
+    P, T, R = qkv.shape
+    if R != (heads + 2 * view.kv_heads) * hd or T != ctx.n_tokens:
+        raise L.KernelError(f"decode_fused: qkv is {tuple(qkv.shape)}, expected [P, {ctx.n_tokens}, {(heads + 2 * view.kv_heads) * hd}]")
+    ops._check("qkv", qkv, torch.float32)
+    for name, w in (("q_norm", q_norm_w), ("k_norm", k_norm_w)):
+        if w is not None:
+            ops._check(name, w, torch.float32, (hd,))
+    if cos is not None:
+        ops._check("cos", cos, torch.float32, (T, hd // 2))
+        ops._check("sin", sin, torch.float32, (T, hd // 2))
+    out = rt.empty((T, heads * hd), rt.act_dtype)
+    limit = view.table_stride * view.page_size
+    max_keys = limit if work["max_pos"] is None else work["max_pos"] + 1
+    tps = STREAM_TILES_PER_SLICE
+    max_slices = -(-max_keys // (tps * decode_tile())) if tps else stream_slices(work["n_dec"], view.kv_heads, max_keys, qkv.device)
+    skey = ("decode_scratch", heads, hd, max_slices)
+    if skey not in ctx.memo:
+        n = work["n_dec"] * heads * max_slices
+        ctx.memo[skey] = (rt.empty((n * hd,), torch.float32), rt.empty((n * 2,), torch.float32))
+    part_o, part_ml = ctx.memo[skey]
+    L.call("ib_attention_decode_fused", qkv.data_ptr(), P, T * R, ops._ptr(q_norm_w), ops._ptr(k_norm_w), float(eps), ops._ptr(cos), ops._ptr(sin),
+           1 if write_kv else 0, C.byref(view), work["dec_tokens"].data_ptr(), work["n_dec"], ctx.positions.data_ptr(), ctx.seg_of_token.data_ptr(),
+           int(window or 0), float(scale), part_o.data_ptr(), part_ml.data_ptr(), out.data_ptr(), heads, max_slices, tps, kv_map, row0,
+           rt.status.data_ptr(), ops._stream())
+    return out
 
 
 def paged_attention(ctx, q: torch.Tensor, cache: ops.KvLayerView, heads: int, window: Optional[int], scale: float) -> torch.Tensor:

@@ -97,7 +97,7 @@ def register(name: str, argtypes: list) -> None:
 launches = 0   # kernels launched so far through `call`
 
 
-KERNELS_PER_CALL = {"ib_sample_rows": 3, "ib_attention_decode": 2, "ib_attention_decode_stream": 2}
+KERNELS_PER_CALL = {"ib_sample_rows": 3, "ib_attention_decode": 2, "ib_attention_decode_stream": 2, "ib_attention_decode_fused": 2}
 
 
 def call(name: str, *args) -> None:

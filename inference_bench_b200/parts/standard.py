@@ -133,11 +133,13 @@ class Attention(base.Mixer):
         rt = ctx.rt
         qkv = rt.linear(h, self.wqkv)
         cos, sin = self.position.tables(ctx)
-        q = rt.empty((ctx.n_tokens, self.heads * self.head_dim))
-        ops.qk_norm_rope_kv(qkv, self.q_norm, self.k_norm, self.norm_eps, cos, sin, ctx.positions, ctx.seg_of_token, q, cache, self.heads,
-                            rt.status, write_kv=self.own_kv)
         from ..kernels import attention
-        out = attention.paged_attention(ctx, q, cache, self.heads, self.window, self.scale)
+        out = attention.decode_fused(ctx, qkv, self.q_norm, self.k_norm, self.norm_eps, cos, sin, cache, self.heads, self.window, self.scale, self.own_kv)
+        if out is None:   # not a step of decoded tokens only, or sizes the fused kernel does not have
+            q = rt.empty((ctx.n_tokens, self.heads * self.head_dim))
+            ops.qk_norm_rope_kv(qkv, self.q_norm, self.k_norm, self.norm_eps, cos, sin, ctx.positions, ctx.seg_of_token, q, cache, self.heads,
+                                rt.status, write_kv=self.own_kv)
+            out = attention.paged_attention(ctx, q, cache, self.heads, self.window, self.scale)
         return rt.linear(out, self.wo, add_to=residual)
 
 

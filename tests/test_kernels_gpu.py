@@ -337,6 +337,51 @@ def test_stream_slices(n_dec, kv_heads, max_keys, want):
         assert attention.stream_slices(n_dec, kv_heads, max_keys, torch.device(DEV)) == want
 
 
+@pytest.mark.parametrize("hd,page,heads,kvh,parts,norms,rope,window", [(128, 16, 8, 2, 3, True, True, None), (64, 64, 6, 2, 1, True, True, 300),
+                                                                       (128, 64, 16, 1, 2, False, True, None), (64, 8, 4, 4, 2, True, False, 100)])
+def test_attention_decode_fused_equals_the_two_steps(status, monkeypatch, hd, page, heads, kvh, parts, norms, rope, window):
+    monkeypatch.setattr("inference_bench_b200.kernels.attention.FUSE_DECODE_MAX_PAIRS", 1 << 30)
+    """Decoded tokens through the fused kernel (norm, rotation, cache write and attention in one) against
+    the q/k kernel followed by the decode kernel, and the cache rows both leave behind."""
+    from inference_bench_b200.engine.context import Segment, build_context
+    from inference_bench_b200.engine.runtime import Runtime
+    from inference_bench_b200.kernels import attention, ops
+    lengths = [1000, 64, 65, 513, 1, 2047, 128, 193, 700]           # context lengths with the new token
+    shapes = [(L_, 1) for L_ in lengths]
+    _, view, pos, seg, _, _ = _attention_case(torch.bfloat16, heads, kvh, hd, page, window, shapes, 31)
+    T, R = len(lengths), (heads + 2 * kvh) * hd
+    qkv = (torch.randn(parts, T, R, generator=_g(32)) * 0.7).to(DEV)
+    qw = (1 + 0.1 * torch.randn(hd, generator=_g(33))).to(DEV) if norms else None
+    kw = (1 + 0.1 * torch.randn(hd, generator=_g(34))).to(DEV) if norms else None
+    rt = Runtime(DEV, "bfloat16")
+    ctx = build_context(rt, [Segment(i, i, L_ - 1, [0]) for i, L_ in enumerate(lengths)])
+    cos = sin = None
+    if rope:
+        inv = (1.0 / torch.pow(torch.tensor(1e4, dtype=torch.float64), torch.arange(0, hd, 2, dtype=torch.float64) / hd)).float().to(DEV)
+        cos, sin = torch.empty(T, hd // 2, device=DEV), torch.empty(T, hd // 2, device=DEV)
+        ops.rope_table(ctx.positions, inv, cos, sin)
+    scale = 1 / math.sqrt(hd)
+    view2 = ops.KvLayerView(view.pool.clone(), view.entry, view.block_table)
+    q = torch.empty(T, heads * hd, dtype=torch.bfloat16, device=DEV)
+    ops.qk_norm_rope_kv(qkv, qw, kw, 1e-5, cos, sin, ctx.positions, ctx.seg_of_token, q, view, heads, rt.status)
+    two = attention.paged_attention(ctx, q, view, heads, window, scale)
+    ctx.memo = {}
+    one = attention.decode_fused(ctx, qkv, qw, kw, 1e-5, cos, sin, view2, heads, window, scale, True)
+    rt.check_status()
+    assert one is not None
+    assert (one.float() - two.float()).abs().max() <= 2.0 ** -7 * two.float().abs().max()
+    a, b = view.pool.float(), view2.pool.float()
+    assert (a - b).abs().max() <= 2.0 ** -7 * a.abs().max() and not torch.equal(view.pool, _attention_case(torch.bfloat16, heads, kvh, hd, page, window, shapes, 31)[1].pool)
+    # a layer that reads another layer's cache writes nothing
+    view3 = ops.KvLayerView(view.pool.clone(), view.entry, view.block_table)
+    ctx.memo = {}
+    attention.decode_fused(ctx, qkv, qw, kw, 1e-5, cos, sin, view3, heads, window, scale, False)
+    assert torch.equal(view3.pool, view.pool)
+    # prompt portions in the step: the fused kernel declines
+    ctx2 = build_context(rt, [Segment(0, 0, 5, [0, 0, 0])])
+    assert attention.decode_fused(ctx2, qkv[:, :3].contiguous(), qw, kw, 1e-5, None if cos is None else cos[:3], None if sin is None else sin[:3], view, heads, window, scale, True) is None
+
+
 def test_attention_reports_missing_page(status):
     from inference_bench_b200.kernels import ops
     q, view, pos, seg, ref, _ = _attention_case(torch.float32, 2, 1, 16, 8, None, [(30, 1)], 13)
