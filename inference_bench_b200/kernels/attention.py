@@ -104,10 +104,13 @@ def decode_fused(ctx, qkv: torch.Tensor, q_norm_w, k_norm_w, eps: float, cos, si
     qkv float32 [P, T, (heads + 2 kv_heads) * hd]: what `ops.qk_norm_rope_kv` and `paged_attention` do
     together, in one kernel (csrc/attention_decode.cu, the fused form). Returns None when that kernel
     cannot take the step (prompt portions in it, float32, a head size or page size it does not have,
-    a rotation over part of the head): the caller then runs the two steps."""
+    a rotation over part of the head, or a layer that reads another layer's cache: its own position's
+    key and value are that layer's, not its own projection's): the caller then runs the two steps."""
     rt = ctx.rt
     view = cache.c_view()
     hd = view.head_dim
+    if not write_kv:
+        return None
     if not (FUSE_DECODE and DECODE_KERNEL == "stream" and rt.act_dtype == torch.bfloat16 and has_tensor_core_kernel(rt.act_dtype, hd, heads, view.kv_heads)):
         return None
     if cos is not None and 2 * cos.shape[1] != hd:

@@ -209,10 +209,10 @@ def _register_toy():
 TOY = dict(architectures=["ToyForCausalLM"], vocab_size=130, hidden_size=48, heads=4, kv_heads=2, head_dim=16, intermediate_size=56, eps=1e-5)
 
 
-def _toy_plain_logits(folder, tokens):
+def _toy_plain_logits(folder, tokens, hd=16):
     """The toy model evaluated whole with the plain functions."""
     w = {k: v.double() for k, v in P.read_safetensors(folder / "model.safetensors").items()}
-    cfg = {"heads": 4, "kv_heads": 2, "head_dim": 16, "eps": 1e-5, "theta": 1e4}
+    cfg = {"heads": 4, "kv_heads": 2, "head_dim": hd, "eps": 1e-5, "theta": 1e4}
     n = len(tokens)
     pos = torch.arange(n)
     x = P.embedding(w["model.embed_tokens.weight"], tokens)
@@ -225,8 +225,8 @@ def _toy_plain_logits(folder, tokens):
         h = P.rmsnorm(x, w["model.layers.0.input_layernorm.weight"], 1e-5)
         if first_kv is None:
             p = "model.layers.0.self_attn."
-            k = P.rope_neox(P.rmsnorm((h @ w[p + "k_proj.weight"].T).reshape(n, 2, 16), w[p + "k_norm.weight"], 1e-5), pos, 1e4)
-            first_kv = (k, (h @ w[p + "v_proj.weight"].T).reshape(n, 2, 16))
+            k = P.rope_neox(P.rmsnorm((h @ w[p + "k_proj.weight"].T).reshape(n, 2, hd), w[p + "k_norm.weight"], 1e-5), pos, 1e4)
+            first_kv = (k, (h @ w[p + "v_proj.weight"].T).reshape(n, 2, hd))
         x = mlp(0, x + P.attention_block(h, w, "model.layers.0.self_attn.", cfg, None))
         if run == 0:
             h = P.rmsnorm(x, w["model.layers.1.input_layernorm.weight"], 1e-5)
@@ -234,23 +234,23 @@ def _toy_plain_logits(folder, tokens):
             x = mlp(1, x + mean @ w["model.layers.1.mixer.mix.weight"].T)
     h = P.rmsnorm(x, w["model.layers.2.input_layernorm.weight"], 1e-5)      # queries of its own, keys and values of the first run
     p = "model.layers.2.self_attn."
-    q = P.rope_neox(P.rmsnorm((h @ w[p + "q_proj.weight"].T).reshape(n, 4, 16), w[p + "q_norm.weight"], 1e-5), pos, 1e4)
+    q = P.rope_neox(P.rmsnorm((h @ w[p + "q_proj.weight"].T).reshape(n, 4, hd), w[p + "q_norm.weight"], 1e-5), pos, 1e4)
     x = mlp(2, x + P.attention_scores(q, *first_kv) @ w[p + "o_proj.weight"].T)
     return (P.rmsnorm(x, w["model.norm.weight"], 1e-5) @ w["lm_head.weight"].T).float().numpy()
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_toy_mixer_with_state_layer_run_twice_and_shared_cache(tmp_path, dtype):
+@pytest.mark.parametrize("dtype,hd", [("float32", 16), ("bfloat16", 16), ("bfloat16", 64)])   # head size 64: the tensor-core attention kernels
+def test_toy_mixer_with_state_layer_run_twice_and_shared_cache(tmp_path, dtype, hd):
     from inference_bench_b200.trace import build_runner
     from inference_bench_b200.weights.random_init import write_random_model
     _register_toy()
-    folder = write_random_model(TOY, 5, tmp_path / "toy", std=0.08)
+    folder = write_random_model({**TOY, "head_dim": hd}, 5, tmp_path / "toy", std=0.08)
     runner = build_runner(folder, dtype, 512, page_size=8)
     cache = runner.cache
     assert len(cache.groups) == 1 and cache.groups[0].entries == [0, 2]       # two caches for the layer that runs twice
     assert cache.sources == [0, 1, 2, 0] and list(cache.states) == [1]        # entry 3 reads entry 0's cache; entry 1 has state
     reqs = {r: traces.prompt(300 + i, n, 130) for i, (r, n) in enumerate({"a": 23, "b": 5, "c": 41, "d": 12, "e": 30}.items())}
-    want = {r: _toy_plain_logits(folder, t) for r, t in reqs.items()}
+    want = {r: _toy_plain_logits(folder, t, hd) for r, t in reqs.items()}
     tol = {"float32": 1e-4, "bfloat16": 3e-2}[dtype]
     for cut in (traces.whole, traces.portions, traces.mixed):
         got = traces.run_steps(runner, cut(reqs))
