@@ -116,30 +116,48 @@ __global__ void qk_norm_rope_kv_vec_kernel(const float* __restrict__ qkv, int P,
       }
     }
   }
+  // what every head of the token shares, fetched once per warp with wide loads: norm scales, the token's
+  // rotation (the sine with the sign of this lane's half: d < HD/2: v cos - partner sin; d >= HD/2: v cos + partner sin)
+  float qw[E], kw[E], cs[E], sn[E];
+  auto load_vec = [&](const float* src, float (&dst)[E]) {
+    if constexpr (E == 4) {
+      const float4 a = *(const float4*)src;
+      dst[0] = a.x, dst[1] = a.y, dst[2] = a.z, dst[3] = a.w;
+    } else {
+      const float2 a = *(const float2*)src;
+      dst[0] = a.x, dst[1] = a.y;
+    }
+  };
+  if (q_norm_w) load_vec(q_norm_w + lane * E, qw);
+  if (k_norm_w) load_vec(k_norm_w + lane * E, kw);
+  if (cos_t) {
+    load_vec(cos_t + (size_t)t * (HD / 2) + (lane & 15) * E, cs);
+    load_vec(sin_t + (size_t)t * (HD / 2) + (lane & 15) * E, sn);
+    if (lane < 16) {
+#pragma unroll
+      for (int e = 0; e < E; e++) sn[e] = -sn[e];
+    }
+  }
 #pragma unroll
   for (int u = 0; u < PER; u++) {
     const int j = j0 + u;
     if (j >= slots) continue;
     const bool is_q = j < heads, is_k = !is_q && j < heads + kvh;
     if (!is_q && !write_kv) continue;
-    const float* nw = is_q ? q_norm_w : (is_k ? k_norm_w : nullptr);
-    if (nw) {
+    if (is_q ? q_norm_w != nullptr : (is_k && k_norm_w != nullptr)) {
       float ss = 0.f;
 #pragma unroll
       for (int e = 0; e < E; e++) ss += v[u][e] * v[u][e];
       ss = ib::warp_sum(ss);
       const float inv = rsqrtf(ss / (float)HD + eps);
 #pragma unroll
-      for (int e = 0; e < E; e++) v[u][e] = nw[lane * E + e] * (v[u][e] * inv);
+      for (int e = 0; e < E; e++) v[u][e] = (is_q ? qw[e] : kw[e]) * (v[u][e] * inv);
     }
     if ((is_q || is_k) && cos_t) {
-      const float* c = cos_t + (size_t)t * (HD / 2) + (lane & 15) * E;
-      const float* sn = sin_t + (size_t)t * (HD / 2) + (lane & 15) * E;
 #pragma unroll
       for (int e = 0; e < E; e++) {
         const float other = __shfl_xor_sync(0xffffffffu, v[u][e], 16);
-        // d < HD/2: v cos - partner sin; d >= HD/2: v cos + partner sin
-        v[u][e] = lane < 16 ? v[u][e] * c[e] - other * sn[e] : v[u][e] * c[e] + other * sn[e];
+        v[u][e] = __fmaf_rn(other, sn[e], __fmul_rn(v[u][e], cs[e]));
       }
     }
     auto store = [&](auto* dst) {
