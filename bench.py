@@ -30,7 +30,8 @@ QWEN3_8B = dict(
     tie_word_embeddings=False, max_position_embeddings=40960, hidden_act="silu", attention_bias=False, torch_dtype="bfloat16")
 CONTEXT = 4096          # benchmark context length
 PROMPT = 2048           # prefill length, and the context each decode request starts from
-PAGE = 64           # keys per cache page: one TMA box of 64 rows per page, plane and half head (the attention kernels take 8 to 256)
+PAGE = 16           # keys per cache page of the benchmark configuration
+PAGE_ENGINE = 64    # the engine's own default (one TMA box of 64 rows per page, plane and half head): measured too, as extra points
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -198,16 +199,21 @@ def measure_decode_e2e(engine, batch: int, steps: int, warmup: int) -> tuple[flo
     return (t1 - t0) * 1e3 / steps, h2d, d2h
 
 
+def make_engine(cfg: dict, page: int, big: int):
+    from inference_bench_b200 import Engine
+    return Engine(cfg, dtype="bfloat16", max_ctx=CONTEXT, page_size=page, num_pages=big * (CONTEXT // page) + 64, max_num_seqs=big,
+                  max_batched_tokens=8192, prefill_chunk=PROMPT, random_weights_seed=0)
+
+
 def run_ours(args) -> dict:
     import torch
-    from inference_bench_b200 import Engine
     pk, pk_src = peaks()
     cfg = dict(QWEN3_8B)
     full_layers = cfg["num_hidden_layers"]
     cfg["num_hidden_layers"] = layers = args.layers or full_layers
     big = max(args.batch, 64)
-    engine = Engine(cfg, dtype="bfloat16", max_ctx=CONTEXT, page_size=PAGE, num_pages=big * (CONTEXT // PAGE) + 64, max_num_seqs=big,
-                    max_batched_tokens=8192, prefill_chunk=PROMPT, random_weights_seed=0)
+    page = args.page_size
+    engine = make_engine(cfg, page, big)
     steps, warmup = args.steps, max(args.warmup, 3)
     if args.only == "prefill":   # one part alone, for profiling: a short report, not the benchmark line
         return {"only": "prefill", "layers": layers, "ms": measure_prefill(engine, args.steps, 1)}
@@ -223,6 +229,16 @@ def run_ours(args) -> dict:
     ms, launches = measure_decode_device(engine, args.batch, steps, warmup)
     clock_report = clocks.stop()
     e2e_ms, h2d, d2h = measure_decode_e2e(engine, args.batch, steps, warmup)
+    extra = {}
+    if page != PAGE_ENGINE:   # the same measurements at the engine's default page size
+        del engine
+        torch.cuda.empty_cache()
+        engine = make_engine(cfg, PAGE_ENGINE, big)
+        tag = f"_page{PAGE_ENGINE}"
+        extra["prefill" + tag] = PROMPT * 1e3 / measure_prefill(engine, 5, 3)
+        extra["decode_b1" + tag] = 1e3 / measure_decode_device(engine, 1, steps, warmup)[0]
+        extra["decode_b64" + tag] = 64e3 / measure_decode_device(engine, 64, min(steps, 64), warmup)[0]
+        extra[f"decode_b{args.batch}" + tag] = args.batch * 1e3 / measure_decode_device(engine, args.batch, steps, warmup)[0]
 
     B = args.batch
     avg_ctx = PROMPT + 1 + warmup + steps / 2
@@ -236,13 +252,13 @@ def run_ours(args) -> dict:
         "config": {"model": "Qwen3-8B shape", "layers": layers, "layers_full": full_layers, "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
                    "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"],
                    "vocab": cfg["vocab_size"], "global_batch": B, "seq_len": CONTEXT, "decode_context_start": PROMPT, "prefill_tokens": PROMPT,
-                   "page_size": PAGE, "weights": "random N(0,0.02) bf16 seed 0", "parallelism": "single_gpu",
+                   "page_size": page, "weights": "random N(0,0.02) bf16 seed 0", "parallelism": "single_gpu",
                    "l2": "inputs larger than L2 (weights read every step)", "peaks": pk_src},
         "e2e": {"value": B * 1e3 / e2e_ms, "unit": "tok/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": launches * steps,
         "prefill": {"value": PROMPT * 1e3 / prefill_ms, "tokens": PROMPT, "ms": prefill_ms, "frac": flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12)},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"]},
-        "points": {"decode_b1": 1e3 / b1_ms, "decode_b64": 64e3 / b64_ms},
+        "points": {"decode_b1": 1e3 / b1_ms, "decode_b64": 64e3 / b64_ms, **extra},
         "clocks": clock_report,
     }
 
@@ -253,6 +269,7 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--page-size", type=int, default=PAGE, help="keys per cache page (the benchmark configuration names 16)")
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (both numbers are reported)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--only", default="", choices=["", "prefill", "decode"], help="run one part alone (for profiling); prints a short report")
