@@ -12,15 +12,20 @@ get a tensor [slots, *shape], zeroed for a slot when a request is admitted to it
 (reference: crates/specrt/src/statepool.rs:7-80, crates/specrt/src/runtime/step.rs:133-135).
 
 The bookkeeping is host-only and runs without a device (tensors are made only when a device is given).
+Pools, block tables and slots live in the C++ core (csrc/host/cache_core.cpp); this class maps request
+ids to slots, owns the device tensors and hands the parts their views.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Any, Hashable, Optional, Sequence
+
+import ctypes as C
 
 import numpy as np
 
 from ..parts.base import FixedState, PagedKV
+from . import native
 from .pages import PagePool
 
 
@@ -44,11 +49,20 @@ class Group:
         return self.need.window
 
 
-@dataclass
 class _Request:
-    slot: int
-    length: int = 0                                   # positions whose state is in the cache
-    tables: list[np.ndarray] = field(default_factory=list)   # per group: page id per page index, -1 = none
+    """A live request as the core sees it: its slot, its committed length and, per group, its row of the block table."""
+    __slots__ = ("slot", "_mgr")
+
+    def __init__(self, slot: int, mgr: "CacheManager"):
+        self.slot, self._mgr = slot, mgr
+
+    @property
+    def length(self) -> int:                          # positions whose state is in the cache
+        return int(self._mgr._lib.ibh_cache_length(self._mgr._core, self.slot))
+
+    @property
+    def tables(self) -> list[np.ndarray]:             # per group: page id per page index, -1 = none (views of the core's memory)
+        return [t[self.slot] for t in self._mgr._tables]
 
 
 @dataclass
@@ -79,7 +93,7 @@ class CacheManager:
                 g = by_need.get(need)
                 if g is None:
                     g = by_need[need] = len(self.groups)
-                    self.groups.append(Group(need, [], PagePool(num_pages)))
+                    self.groups.append(Group(need, [], None))
                 self.place[i] = (g, len(self.groups[g].entries))
                 self.groups[g].entries.append(i)
             elif isinstance(need, FixedState):
@@ -87,6 +101,16 @@ class CacheManager:
             elif need is not None:
                 raise TypeError(f"schedule entry {i} asks the cache for {need!r}, which it does not know")
         self._fixed = {i: n for i, n in enumerate(needs) if isinstance(n, FixedState)}
+        self._lib = native.load()
+        windows = (C.c_int * max(1, len(self.groups)))(*[int(g.need.window or 0) for g in self.groups])
+        self._core = self._lib.ibh_cache_new(len(self.groups), windows, page_size, num_pages, max_requests, max_tokens_per_request)
+        if not self._core:
+            raise ValueError(native.last_error())
+        for gi, g in enumerate(self.groups):
+            g.pool = PagePool(0, _handle=self._lib.ibh_cache_pool(self._core, gi))
+        base = self._lib.ibh_cache_tables(self._core)
+        whole = np.ctypeslib.as_array(base, shape=(max(1, len(self.groups)), max_requests, self.table_width)) if self.groups else np.zeros((0, max_requests, self.table_width), np.int32)
+        self._tables = [whole[gi] for gi in range(len(self.groups))]     # per group: int32 [max_requests, table_width], the core's own memory
         if device is not None:
             import torch
             for g in self.groups:
@@ -97,7 +121,11 @@ class CacheManager:
                 # and one scratch slot more than requests can hold
                 self.states[i].tensor = torch.zeros((max_requests + 1, *n.shape), dtype=n.dtype, device=device)
         self._requests: dict[Hashable, _Request] = {}
-        self._free_slots = list(range(max_requests - 1, -1, -1))
+
+    def __del__(self):
+        core, self._core = getattr(self, "_core", None), None
+        if core:
+            self._lib.ibh_cache_free(core)
 
     @property
     def scratch_slot(self) -> int:
@@ -114,16 +142,16 @@ class CacheManager:
         return req in self._requests
 
     def free_slots(self) -> int:
-        return len(self._free_slots)
+        return int(self._lib.ibh_cache_free_slots(self._core))
 
     def admit(self, req: Hashable) -> int:
         """Give the request a state slot (zeroed) and empty block tables."""
         if req in self._requests:
             raise CacheError(f"request {req!r} is already admitted")
-        if not self._free_slots:
+        slot = int(self._lib.ibh_cache_admit(self._core))
+        if slot < 0:
             raise CacheError(f"no free slot: {self.max_requests} requests are live")
-        slot = self._free_slots.pop()
-        self._requests[req] = _Request(slot, 0, [np.full(self.table_width, -1, dtype=np.int32) for _ in self.groups])
+        self._requests[req] = _Request(slot, self)
         for view in self.states.values():
             if view.tensor is not None:
                 view.tensor[slot].zero_()
@@ -142,26 +170,13 @@ class CacheManager:
         return self._get(req).length
 
     # ------------------------------------------------------------------ pages
-    def _first_live_page(self, g: Group, length: int) -> int:
-        """Pages below this index hold only positions that no token at position >= length can see."""
-        if g.window is None:
-            return 0
-        return max(0, length - g.window + 1) // self.page_size
-
     def pages_missing(self, req: Optional[Hashable], new_length: int, length: int = 0) -> list[int]:
         """Per group, the pages that must be allocated before the request holds `new_length` positions.
         For a request not yet admitted pass req=None and the length it would start from."""
-        out = []
         r = self._requests.get(req) if req is not None else None
-        cur = r.length if r is not None else length
-        for gi, g in enumerate(self.groups):
-            first = self._first_live_page(g, cur)
-            last = -(-new_length // self.page_size)
-            if r is None:
-                out.append(max(0, last - first))
-            else:
-                out.append(int(np.count_nonzero(r.tables[gi][first:last] < 0)))
-        return out
+        out = (C.c_int * max(1, len(self.groups)))()
+        self._lib.ibh_cache_pages_missing(self._core, r.slot if r is not None else -1, int(new_length), int(length), out)
+        return [int(out[gi]) for gi in range(len(self.groups))]
 
     def can_extend(self, req: Optional[Hashable], new_length: int, length: int = 0, reserve: int = 0) -> bool:
         if new_length > self.max_tokens_per_request:
@@ -171,53 +186,28 @@ class CacheManager:
     def extend(self, req: Hashable, new_length: int) -> None:
         """Allocate, in every group, the pages for positions up to new_length - 1. All or nothing."""
         r = self._get(req)
-        if new_length > self.max_tokens_per_request:
+        code = self._lib.ibh_cache_extend(self._core, r.slot, int(new_length))
+        if code == 1:
+            raise OutOfPages(f"request {req!r} {native.last_error()}")
+        if code == 2:
             raise OutOfPages(f"request {req!r} would hold {new_length} tokens, more than the limit of {self.max_tokens_per_request}")
-        taken: list[tuple[int, int]] = []
-        for gi, g in enumerate(self.groups):
-            first = self._first_live_page(g, r.length)
-            last = -(-new_length // self.page_size)
-            for p in (np.nonzero(r.tables[gi][first:last] < 0)[0] + first).tolist():
-                page = g.pool.allocate()
-                if page is None:
-                    for gj, pj in taken:
-                        self.groups[gj].pool.release(int(r.tables[gj][pj]))
-                        r.tables[gj][pj] = -1
-                    raise OutOfPages(f"request {req!r} needs a page for positions {p * self.page_size}.. but group {gi} has none free "
-                                     f"({g.pool.num_pages} pages, all in use)")
-                r.tables[gi][p] = page
-                taken.append((gi, p))
+        if code:
+            raise CacheError(native.last_error())
 
     def shrink_to_committed(self, req: Hashable) -> None:
         """Undo an `extend` that no `commit` followed: free the pages beyond the committed length."""
-        r = self._get(req)
-        keep = -(-r.length // self.page_size)
-        for gi, g in enumerate(self.groups):
-            row = r.tables[gi]
-            for p in np.nonzero(row[keep:] >= 0)[0] + keep:
-                g.pool.release(int(row[p]))
-                row[p] = -1
+        if self._lib.ibh_cache_shrink_to_committed(self._core, self._get(req).slot):
+            raise CacheError(native.last_error())
 
     def commit(self, req: Hashable, new_length: int) -> None:
         """The request now holds new_length positions; windowed groups give back pages that passed."""
-        r = self._get(req)
-        r.length = new_length
-        for gi, g in enumerate(self.groups):
-            if g.window is None:
-                continue
-            first = self._first_live_page(g, new_length)
-            row = r.tables[gi]
-            for p in np.nonzero(row[:first] >= 0)[0]:
-                g.pool.release(int(row[p]))
-                row[p] = -1
+        if self._lib.ibh_cache_commit(self._core, self._get(req).slot, int(new_length)):
+            raise CacheError(native.last_error())
 
     def release(self, req: Hashable) -> None:
         """The request ends: all its pages and its slot are given back."""
-        r = self._get(req)
-        for gi, g in enumerate(self.groups):
-            for page in r.tables[gi][r.tables[gi] >= 0]:
-                g.pool.release(int(page))
-        self._free_slots.append(r.slot)
+        if self._lib.ibh_cache_release(self._core, self._get(req).slot):
+            raise CacheError(native.last_error())
         del self._requests[req]
 
     def table(self, group: int, req: Hashable) -> np.ndarray:
@@ -229,11 +219,23 @@ class CacheManager:
     def free_pages(self) -> list[int]:
         return [g.pool.free_pages for g in self.groups]
 
+    def fill_rows(self, reqs: Sequence[Hashable], positions: np.ndarray, tables: Sequence[np.ndarray]) -> list[int]:
+        """For a step of single decoded tokens: write the requests' committed lengths (their next positions)
+        into positions[:n] and their block tables into tables[g][:n] (int32, contiguous; typically the pinned
+        input block of a captured step), in one call into the core. Returns the requests' slots."""
+        n = len(reqs)
+        slots = [self._get(r).slot for r in reqs]
+        arr = (C.c_int * max(1, n))(*slots)
+        ptrs = (C.POINTER(C.c_int) * max(1, len(tables)))(*[t.ctypes.data_as(C.POINTER(C.c_int)) for t in tables])
+        if self._lib.ibh_cache_fill_rows(self._core, arr, n, positions.ctypes.data_as(C.POINTER(C.c_int)), ptrs):
+            raise CacheError(native.last_error())
+        return slots
+
     # ------------------------------------------------------------------ what a step hands to the parts
     def step_tables(self, reqs: Sequence[Hashable]) -> list[np.ndarray]:
         """Per group, the block tables of the step's segments, int32 [segments, table_width]."""
-        return [np.stack([self._get(r).tables[gi] for r in reqs]) if reqs else np.zeros((0, self.table_width), np.int32)
-                for gi in range(len(self.groups))]
+        slots = [self._get(r).slot for r in reqs]
+        return [t[slots] if slots else np.zeros((0, self.table_width), np.int32) for t in self._tables]
 
     def views(self, device_tables: Sequence[Any]) -> list[Any]:
         """Per schedule entry, what its mixer gets this step: a KvLayerView on its group's tensor
@@ -254,15 +256,8 @@ class CacheManager:
     def check(self) -> None:
         """No page lost, held twice or freed twice: every pool is consistent and a page's reference
         count equals the number of table entries that name it."""
-        for gi, g in enumerate(self.groups):
-            g.pool.check()
-            counts = np.zeros(g.pool.num_pages, dtype=np.int64)
-            for r in self._requests.values():
-                held = r.tables[gi][r.tables[gi] >= 0]
-                np.add.at(counts, held, 1)
-            for p in range(g.pool.num_pages):
-                if counts[p] != g.pool.refcount(p):
-                    raise CacheError(f"group {gi}: page {p} is named by {counts[p]} table entries but has reference count {g.pool.refcount(p)}")
+        if self._lib.ibh_cache_check(self._core):
+            raise CacheError(native.last_error())
         slots = [r.slot for r in self._requests.values()]
-        if len(set(slots)) != len(slots) or set(slots) & set(self._free_slots) or len(slots) + len(self._free_slots) != self.max_requests:
+        if len(set(slots)) != len(slots) or len(slots) + self.free_slots() != self.max_requests:
             raise CacheError("state slots are inconsistent: a slot is lost, held twice or both held and free")

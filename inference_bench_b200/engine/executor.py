@@ -152,17 +152,12 @@ class _DecodeGraph:
         n = len(entries)
         if n < self.rows:
             self._pad_all()
-        reqs = [cache._get(e.request) for e in entries]
-        pos = [r.length for r in reqs]
+        slots = cache.fill_rows([e.request for e in entries], self.h_pos, self.h_tables)   # positions and block tables, straight into the pinned block
         if tokens:
             self.h_tokens[:n] = [e.tokens[0] for e in entries]
-        self.h_pos[:n] = pos
-        self.h_pos0[:n] = pos
-        self.h_slot[:n] = [r.slot for r in reqs]
+        self.h_pos0[:n] = self.h_pos[:n]
+        self.h_slot[:n] = slots
         self.h_params[:n] = [p.row(step) for p, step in sampling]
-        for g, t in enumerate(self.h_tables):
-            for i, r in enumerate(reqs):
-                t[i] = r.tables[g]
 
 
 class GpuExecutor:

@@ -147,10 +147,54 @@ def build(verbose: bool = True) -> Path:
             os.replace(tmp_lib, lib)
             if verbose:
                 _say(f"built {lib.name} in {time.time() - t0:.0f} s")
-            # Drop libraries and objects of older source versions.
-            keep = {lib.name, ".lock", *[o.name for _, o in todo]}
+            # Drop this library's files of older source versions (the host library's are its own business).
+            keep = {lib.name, *[o.name for _, o in todo]}
+            stems = {s.stem for s in srcs}
             for f in out.iterdir():
-                if f.name not in keep and (f.suffix in (".o", ".so")) and ".tmp" not in f.name:
+                mine = f.name.endswith("-" + LIB_NAME) or (f.suffix == ".o" and f.name.rsplit("-", 1)[0] in stems)
+                if mine and f.name not in keep and ".tmp" not in f.name:
+                    try:
+                        f.unlink()
+                    except OSError:
+                        pass
+            return lib
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+
+
+HOST_LIB_NAME = "libib200_host.so"
+HOST_FLAGS = ["-std=c++17", "-O2", "-fPIC", "-shared", "-Wall"]
+
+
+def build_host(verbose: bool = True) -> Path:
+    """The host-side library (`csrc/host/*.cpp`: cache bookkeeping and scheduling decisions), built with
+    the C++ compiler alone: it needs neither nvcc nor a GPU."""
+    srcs = sorted((CSRC / "host").glob("*.cpp"))
+    if not srcs:
+        raise BuildError(f"no C++ sources under {CSRC / 'host'}")
+    out = build_dir()
+    key = _digest([*(s.read_bytes() for s in srcs), " ".join(HOST_FLAGS).encode()])
+    lib = out / f"{key}-{HOST_LIB_NAME}"
+    if lib.is_file():
+        return lib
+    cxx = os.environ.get("CXX") or shutil.which("g++") or shutil.which("c++") or shutil.which("clang++")
+    if not cxx:
+        raise BuildError("no C++ compiler was found (g++, c++, clang++ or $CXX); the host library cannot be built")
+    with open(out / ".lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if lib.is_file():
+                return lib
+            t0 = time.time()
+            tmp_lib = lib.with_suffix(f".tmp{os.getpid()}.so")
+            r = subprocess.run([cxx, *HOST_FLAGS, "-o", str(tmp_lib), *map(str, srcs)], capture_output=True, text=True)
+            if r.returncode != 0:
+                raise BuildError(f"compiling {HOST_LIB_NAME} failed:\n{r.stdout}\n{r.stderr}")
+            os.replace(tmp_lib, lib)
+            if verbose:
+                _say(f"built {lib.name} in {time.time() - t0:.0f} s")
+            for f in out.iterdir():
+                if f.name.endswith("-" + HOST_LIB_NAME) and f.name != lib.name and ".tmp" not in f.name:
                     try:
                         f.unlink()
                     except OSError:
@@ -161,4 +205,5 @@ def build(verbose: bool = True) -> Path:
 
 
 if __name__ == "__main__":
+    print(build_host())
     print(build())
