@@ -28,6 +28,12 @@ QWEN3_8B = dict(
     architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=151936, hidden_size=4096, intermediate_size=12288,
     num_hidden_layers=36, num_attention_heads=32, num_key_value_heads=8, head_dim=128, rms_norm_eps=1e-6, rope_theta=1000000.0,
     tie_word_embeddings=False, max_position_embeddings=40960, hidden_act="silu", attention_bias=False, torch_dtype="bfloat16")
+# The two larger shapes the baseline names (same architecture; --shape 14b / 32b): not the default run.
+SHAPES = {
+    "8b": QWEN3_8B,
+    "14b": dict(QWEN3_8B, hidden_size=5120, intermediate_size=17408, num_hidden_layers=40, num_attention_heads=40),
+    "32b": dict(QWEN3_8B, hidden_size=5120, intermediate_size=25600, num_hidden_layers=64, num_attention_heads=64),
+}
 CONTEXT = 4096          # benchmark context length
 PROMPT = 2048           # prefill length, and the context each decode request starts from
 PAGE = 16           # keys per cache page of the benchmark configuration
@@ -208,7 +214,7 @@ def make_engine(cfg: dict, page: int, big: int):
 def run_ours(args) -> dict:
     import torch
     pk, pk_src = peaks()
-    cfg = dict(QWEN3_8B)
+    cfg = dict(SHAPES[args.shape])
     full_layers = cfg["num_hidden_layers"]
     cfg["num_hidden_layers"] = layers = args.layers or full_layers
     big = max(args.batch, 64)
@@ -246,10 +252,10 @@ def run_ours(args) -> dict:
     achieved = step_bytes / (ms * 1e-3) / 1e9
     flops = prefill_flops(cfg, layers, PROMPT)
     return {
-        "metric": "decode tok/s at batch 8 (Qwen3-8B shape, random bf16 weights, context 2048 growing toward 4096)",
+        "metric": f"decode tok/s at batch {B} (Qwen3-{args.shape.upper()} shape, random bf16 weights, context 2048 growing toward 4096)",
         "value": B * 1e3 / ms, "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": ms,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"model": "Qwen3-8B shape", "layers": layers, "layers_full": full_layers, "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
+        "config": {"model": f"Qwen3-{args.shape.upper()} shape", "layers": layers, "layers_full": full_layers, "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
                    "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"],
                    "vocab": cfg["vocab_size"], "global_batch": B, "seq_len": CONTEXT, "decode_context_start": PROMPT, "prefill_tokens": PROMPT,
                    "page_size": page, "weights": "random N(0,0.02) bf16 seed 0", "parallelism": "single_gpu",
@@ -269,6 +275,7 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--shape", default="8b", choices=sorted(SHAPES), help="layer sizes: the benchmark's Qwen3-8B, or the larger shapes the baseline names")
     ap.add_argument("--page-size", type=int, default=PAGE, help="keys per cache page (the benchmark configuration names 16)")
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (both numbers are reported)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])

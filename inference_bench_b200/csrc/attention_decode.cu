@@ -421,19 +421,19 @@ template <int HD, bool FUSED>
 __global__ void __launch_bounds__((kWarps + 1) * 32, 2)
     decode_stream_kernel(const __nv_bfloat16* __restrict__ q, RawQkv raw, IbKvView kv, const int* __restrict__ dec_tokens, const int* __restrict__ positions,
                          const int* __restrict__ seg_of_token, int window, float scale_log2e, float* __restrict__ part_o,
-                         float* __restrict__ part_ml, int heads, int n_dec, int max_slices, int tiles_per_slice,
+                         float* __restrict__ part_ml, int heads, int n_dec, int max_slices, int tiles_per_slice, int merge_cols,
                          const __grid_constant__ CUtensorMap kv_map, long long view_row0, unsigned* __restrict__ status) {
   constexpr int CPR = HD / 8;
   constexpr int TILE = kTile * HD * 2;
   constexpr int HB = HD / 64;
   extern __shared__ __align__(1024) uint8_t smem[];
   const int group = heads / kv.kv_heads;
-  // layout: kRing x (K tile, V tile) | Q tile [16][HD] | (max, sum) [warps][16] | O [warps][group][HD] | barriers | flag | token table
+  // layout: kRing x (K tile, V tile) | Q tile [16][HD] | (max, sum) [warps][16] | O [warps][group][merge_cols] | barriers | flag | token table | own key, value, scores
   uint8_t* ring = smem;
   const uint32_t q_s = mt::smem_u32(smem + kRing * 2 * TILE);
   float* ml_s = (float*)(smem + kRing * 2 * TILE + 16 * HD * 2);
   float* o_s = ml_s + kWarps * 16 * 2;
-  uint64_t* full = (uint64_t*)(o_s + kWarps * group * HD);
+  uint64_t* full = (uint64_t*)(o_s + kWarps * group * merge_cols);
   uint64_t* empty = full + kRing;
   volatile int* gave_up = (volatile int*)(empty + kRing);
   int* meta = (int*)(empty + kRing) + 2;   // [kMeta][3]
@@ -548,14 +548,14 @@ __global__ void __launch_bounds__((kWarps + 1) * 32, 2)
         __syncwarp();
         if (lane == 0) sm100::mbar_arrive_expect_tx(&full[stage], (uint32_t)(__popc(vmask) * box_rows * 128 * HB * 2));
         __syncwarp();
-        if (valid) {
-          const int key0 = tile * kTile + my * box_rows;
-          const long long row = (long long)held * rows_per_page + view_row0 + (long long)kvh * kv.page_size + key0 % kv.page_size;
-#pragma unroll
-          for (int hb = 0; hb < HB; hb++) {
-            uint8_t* dk = k_t + hb * kTile * 128 + my * box_rows * 128;
-            sm100::tma_load_2d(dk, &kv_map, hb * 64, (int)row, &full[stage]);
-            sm100::tma_load_2d(dk + TILE, &kv_map, hb * 64, (int)(row + v_rows), &full[stage]);
+        {   // one box per lane (page, plane, 64-value block), so that the boxes of a tile are issued side by side
+          const int b_pg = lane / (HB * 2), b_plane = (lane / HB) & 1, b_hb = lane % HB;
+          const int holder = (rel + b_pg) & 31;
+          const int page = __shfl_sync(0xffffffffu, held, holder);
+          if (lane < ppt * HB * 2 && ((vmask >> holder) & 1)) {
+            const int key0 = tile * kTile + b_pg * box_rows;
+            const long long row = (long long)page * rows_per_page + view_row0 + (long long)kvh * kv.page_size + key0 % kv.page_size + b_plane * v_rows;
+            sm100::tma_load_2d(k_t + b_plane * TILE + b_hb * kTile * 128 + b_pg * box_rows * 128, &kv_map, b_hb * 64, (int)row, &full[stage]);
           }
         }
       }
@@ -793,15 +793,19 @@ __global__ void __launch_bounds__((kWarps + 1) * 32, 2)
       ml_s[(warp * 16 + g + 8) * 2] = m[1];
       ml_s[(warp * 16 + g + 8) * 2 + 1] = l[1];
     }
+    // (the O buffer holds merge_cols of the head's values at a time, so that large groups do not cost the second CTA of the SM)
+    for (int c0 = 0; c0 < HD; c0 += merge_cols) {
+    if (c0) bar_sync_compute();   // every warp is done reading the pass before
 #pragma unroll
     for (int i = 0; i < HD / 8; i++) {
-      const int d = 8 * i + 2 * tq;
-      if (g < group) *(float2*)&o_s[(warp * group + g) * HD + d] = make_float2(o[i][0], o[i][1]);
-      if (g + 8 < group) *(float2*)&o_s[(warp * group + g + 8) * HD + d] = make_float2(o[i][2], o[i][3]);
+      const int d = 8 * i + 2 * tq - c0;
+      if (d < 0 || d >= merge_cols) continue;
+      if (g < group) *(float2*)&o_s[(warp * group + g) * merge_cols + d] = make_float2(o[i][0], o[i][1]);
+      if (g + 8 < group) *(float2*)&o_s[(warp * group + g + 8) * merge_cols + d] = make_float2(o[i][2], o[i][3]);
     }
     bar_sync_compute();
-    for (int idx = tid; idx < group * HD; idx += kWarps * 32) {
-      const int row = idx / HD, d = idx % HD;
+    for (int idx = tid; idx < group * merge_cols; idx += kWarps * 32) {
+      const int row = idx / merge_cols, dl = idx % merge_cols, d = c0 + dl;
       float M = -INFINITY;
 #pragma unroll
       for (int w = 0; w < kWarps; w++) M = fmaxf(M, ml_s[(w * 16 + row) * 2]);
@@ -812,7 +816,7 @@ __global__ void __launch_bounds__((kWarps + 1) * 32, 2)
         const float mw = ml_s[(w * 16 + row) * 2];
         const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
         Lsum += ml_s[(w * 16 + row) * 2 + 1] * f;
-        O += o_s[(w * group + row) * HD + d] * f;
+        O += o_s[(w * group + row) * merge_cols + dl] * f;
       }
       if (FUSED && own_here) {   // the token's own key and value, as one more partial result
         const float f = exp2f(s_own[row] - M);
@@ -826,8 +830,17 @@ __global__ void __launch_bounds__((kWarps + 1) * 32, 2)
         part_ml[slot * 2 + 1] = Lsum;
       }
     }
+    }
     u = u_next;
   }
+}
+
+// Values of a head that the merge buffer of the streaming kernel holds at a time: all of them while
+// four warps' rows of the group fit 8 KiB (groups up to 4 at head size 128), else a half, a quarter, ...
+inline int stream_merge_cols(int group, int hd) {
+  int w = hd;
+  while (w > 8 && kWarps * group * w * 4 > 8192) w >>= 1;
+  return w;
 }
 
 template <int HD, bool FUSED>
@@ -835,7 +848,8 @@ int launch_stream(const void* q, const RawQkv* raw, const IbKvView* kv, const in
                   int window, float scale, float* part_o, float* part_ml, void* out, int heads, int max_slices, int tiles_per_slice,
                   const CUtensorMap* kv_map, long long view_row0, unsigned* status, cudaStream_t stream) {
   const int group = heads / kv->kv_heads;
-  const int smem = kRing * 2 * kTile * HD * 2 + 16 * HD * 2 + kWarps * 16 * 2 * 4 + kWarps * group * HD * 4 + 2 * kRing * 8 + 16 + kMeta * 12 +
+  const int merge_cols = stream_merge_cols(group, HD);
+  const int smem = kRing * 2 * kTile * HD * 2 + 16 * HD * 2 + kWarps * 16 * 2 * 4 + kWarps * group * merge_cols * 4 + 2 * kRing * 8 + 16 + kMeta * 12 +
                    (2 * HD + 16) * 4;
   static int reserved = 0, per_sm = 0, sms = 0;
   if (smem != reserved) {
@@ -853,8 +867,8 @@ int launch_stream(const void* q, const RawQkv* raw, const IbKvView* kv, const in
   const int grid = (int)(units < (long long)sms * per_sm ? units : (long long)sms * per_sm);
   const RawQkv none = {};
   ib::launch(decode_stream_kernel<HD, FUSED>, grid, (kWarps + 1) * 32, smem, stream, (const __nv_bfloat16*)q, raw ? *raw : none, *kv, dec_tokens,
-             positions, seg_of_token, window, scale * 1.4426950408889634f, part_o, part_ml, heads, n_dec, max_slices, tiles_per_slice, *kv_map,
-             view_row0, status);
+             positions, seg_of_token, window, scale * 1.4426950408889634f, part_o, part_ml, heads, n_dec, max_slices, tiles_per_slice, merge_cols,
+             *kv_map, view_row0, status);
   IB_CHECK_LAUNCH("attention_decode_stream split");
   ib::launch(decode_combine_kernel<HD>, dim3(heads, n_dec), kCombineThreads, 0, stream, part_o, part_ml, dec_tokens, positions, window, (__nv_bfloat16*)out, heads,
              max_slices, tiles_per_slice);

@@ -190,10 +190,15 @@ __global__ void __launch_bounds__(kThreads, 2)
         __syncwarp();
         if (lane == 0) sm100::mbar_arrive_expect_tx(full, bytes);
         __syncwarp();
-        if (valid) {
-#pragma unroll
-          for (int hb = 0; hb < HB; hb++)
-            sm100::tma_load_2d(dst + hb * BN * 128 + my * box_rows * 128, &kv_map, hb * 64, (int)(row + (plane ? v_rows : 0)), full);
+        {   // one box per lane (page, 64-value block), so that the boxes of a tile are issued side by side
+          const int b_pg = lane / HB, b_hb = lane % HB;
+          const int holder = (rel + b_pg) & 31;
+          const int page = __shfl_sync(0xffffffffu, held, holder);
+          if (lane < ppt * HB && ((vmask >> holder) & 1)) {
+            const int bkey0 = kt * BN + b_pg * box_rows;
+            const long long brow = (long long)page * rows_per_page + view_row0 + (long long)kvh * kv.page_size + bkey0 % kv.page_size + (plane ? v_rows : 0);
+            sm100::tma_load_2d(dst + b_hb * BN * 128 + b_pg * box_rows * 128, &kv_map, b_hb * 64, (int)brow, full);
+          }
         }
       }
     }

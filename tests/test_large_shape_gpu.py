@@ -1,5 +1,6 @@
-"""Two layers at Qwen3-8B layer sizes (random weights made on the device): the bfloat16 path with
-its tensor-core kernels against the true 32-bit path of the same weights, whole prompt and decode."""
+"""Two layers at the layer sizes of Qwen3-8B, 14B and 32B (random weights made on the device): the
+bfloat16 path with its tensor-core kernels against the true 32-bit path of the same weights, prompt
+portions and decode (groups of 4, 5 and 8 query heads per kv head; 32B: heads * head_dim != hidden)."""
 from __future__ import annotations
 
 import numpy as np
@@ -14,14 +15,23 @@ QWEN3_8B_2L = dict(
     tie_word_embeddings=False, max_position_embeddings=40960, hidden_act="silu", attention_bias=False, torch_dtype="bfloat16")
 
 
-def test_bfloat16_against_float32_at_8b_layer_sizes():
+SHAPES = {
+    "8b": QWEN3_8B_2L,
+    "14b": dict(QWEN3_8B_2L, hidden_size=5120, intermediate_size=17408, num_attention_heads=40),
+    "32b": dict(QWEN3_8B_2L, hidden_size=5120, intermediate_size=25600, num_attention_heads=64),
+}
+
+
+@pytest.mark.parametrize("shape,page", [("8b", 16), ("14b", 64), ("32b", 16)])
+def test_bfloat16_against_float32_at_large_layer_sizes(shape, page):
     from inference_bench_b200 import Engine
     from inference_bench_b200.engine.step import StepEntry
+    QWEN3_8B_2L = SHAPES[shape]
     rng = np.random.default_rng(0)
     prompt = rng.integers(0, 151936, 300).tolist()
     logits = {}
     for dtype in ("float32", "bfloat16"):
-        eng = Engine(QWEN3_8B_2L, dtype=dtype, max_ctx=512, page_size=16, num_pages=64, max_num_seqs=2, random_weights_seed=0)
+        eng = Engine(QWEN3_8B_2L, dtype=dtype, max_ctx=512, page_size=page, num_pages=64, max_num_seqs=2, random_weights_seed=0)
         eng.cache.admit("r")
         rows = [eng.runner.step([StepEntry("r", prompt[:257], [0, 100, 256])]).cpu()]         # a portion that crosses query tiles
         rows.append(eng.runner.step([StepEntry("r", prompt[257:299], [41])]).cpu())              # a second portion
@@ -34,4 +44,4 @@ def test_bfloat16_against_float32_at_8b_layer_sizes():
     assert torch.isfinite(got).all()
     err = (got - ref).abs().max().item() / ref.abs().max().item()
     assert err <= 3e-2, f"bfloat16 differs from float32 by {err:.3e} of max|logit|"
-    print(f"8B layer sizes, 2 layers: bfloat16 vs float32 worst {err:.3e} of max|logit|")
+    print(f"{shape} layer sizes, 2 layers: bfloat16 vs float32 worst {err:.3e} of max|logit|")
