@@ -177,6 +177,46 @@ def measure_decode_device(engine, batch: int, steps: int, warmup: int) -> tuple[
     return ms, launches
 
 
+def measure_mixed_step(engine, steps: int) -> tuple[float, int]:
+    """Milliseconds for one step that holds 8 prompt portions of 512 tokens (starting 0, 512, ... 3,584 tokens into
+    their prompts) beside 56 decoded tokens of requests at contexts drawn uniformly from 1,024 to 4,096: the
+    mixed batch the baseline names for the 14B shape. Returns (median ms, rows in the step)."""
+    import numpy as np
+    import torch
+    from inference_bench_b200.engine.step import StepEntry
+    vocab = engine.decoder.plan.vocab_size
+    rng = np.random.default_rng(0)
+    contexts = rng.integers(1024, CONTEXT + 1, 56).tolist()
+
+    def fill(rid, n):   # bring a request to n tokens in the cache
+        engine.cache.admit(rid)
+        toks = _prompt(abs(hash(rid)) % 1000, n, vocab)
+        for a in range(0, n, PROMPT):
+            engine.runner.step([StepEntry(rid, toks[a:a + PROMPT], [])], check=False)
+
+    for i, c in enumerate(contexts):
+        fill(("mixed-d", i), c - 1)
+    for i in range(8):
+        fill(("mixed-p", i), 512 * i)
+    entries = [StepEntry(("mixed-d", i), [int(rng.integers(0, vocab))], [0]) for i in range(56)]
+    entries += [StepEntry(("mixed-p", i), _prompt(50 + i, 512, vocab), [511]) for i in range(8)]
+    times = []
+    for _ in range(steps + 2):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        engine.runner.step(entries, check=False)
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+        for e in entries:   # the same work again: forget the step's tokens
+            engine.cache.commit(e.request, engine.cache.length(e.request) - len(e.tokens))
+    for e in entries:
+        engine.cache.release(e.request)
+    engine.rt.check_status()
+    return statistics.median(times[2:]), sum(len(e.tokens) for e in entries)
+
+
 def measure_decode_e2e(engine, batch: int, steps: int, warmup: int) -> tuple[float, float, float]:
     """Milliseconds per decode step through Engine.submit / Engine.step: host token ids in (pinned
     staging, copied every step) and sampled token ids back on the host every step."""
@@ -223,6 +263,9 @@ def run_ours(args) -> dict:
     steps, warmup = args.steps, max(args.warmup, 3)
     if args.only == "prefill":   # one part alone, for profiling: a short report, not the benchmark line
         return {"only": "prefill", "layers": layers, "ms": measure_prefill(engine, args.steps, 1)}
+    if args.only == "mixed":
+        ms, rows = measure_mixed_step(engine, max(args.steps, 3) if args.steps < 16 else 5)
+        return {"only": "mixed", "layers": layers, "rows": rows, "ms": ms, "tok_s": rows * 1e3 / ms}
     if args.only == "decode":
         ms, launches = measure_decode_device(engine, args.batch, steps, warmup)
         return {"only": "decode", "layers": layers, "batch": args.batch, "ms_per_step": ms, "launches_per_step": launches}
@@ -279,7 +322,7 @@ def main() -> int:
     ap.add_argument("--page-size", type=int, default=PAGE, help="keys per cache page (the benchmark configuration names 16)")
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (both numbers are reported)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--only", default="", choices=["", "prefill", "decode"], help="run one part alone (for profiling); prints a short report")
+    ap.add_argument("--only", default="", choices=["", "prefill", "decode", "mixed"], help="run one part alone (for profiling); prints a short report")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "the reference is a Rust workspace (no setup.py/pyproject.toml): pip cannot install it and no Rust toolchain is present"}))
