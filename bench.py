@@ -33,6 +33,8 @@ SHAPES = {
     "8b": QWEN3_8B,
     "14b": dict(QWEN3_8B, hidden_size=5120, intermediate_size=17408, num_hidden_layers=40, num_attention_heads=40),
     "32b": dict(QWEN3_8B, hidden_size=5120, intermediate_size=25600, num_hidden_layers=64, num_attention_heads=64),
+    # the one size the reference published numbers for (on other hardware)
+    "0.6b": dict(QWEN3_8B, hidden_size=1024, intermediate_size=3072, num_hidden_layers=28, num_attention_heads=16, tie_word_embeddings=True),
 }
 CONTEXT = 4096          # benchmark context length
 PROMPT = 2048           # prefill length, and the context each decode request starts from

@@ -339,3 +339,53 @@ def test_pipeline_off_never_launches_ahead():
     submit(0, prompt(70, 5), 6)
     done, _ = run(sched, ex)
     assert done[0].tokens == alone(prompt(70, 5), 6) and ex.launched == 0
+
+
+@pytest.mark.parametrize("executor", [FakeExecutor, AheadExecutor])
+@pytest.mark.parametrize("seed", range(12))
+def test_random_traffic_gives_every_request_its_own_tokens(executor, seed):
+    """Requests of random lengths arriving at random steps, some with stop tokens, some cancelled, in a pool small
+    enough that requests are preempted: whatever the scheduler does (portions, preemption, steps kept one ahead),
+    every request ends with the tokens it would have had alone, and nothing is left held."""
+    rng = np.random.default_rng(1000 + seed)
+    pages = int(rng.integers(14, 40))
+    cache, sched, ex, submit = make(pages=pages, page=4, slots=int(rng.integers(2, 7)), executor=executor,
+                                    max_batched_tokens=int(rng.integers(8, 40)), prefill_chunk=int(rng.integers(3, 20)), max_ctx=pages * 4)
+    plans, arrivals, cancels = {}, {}, {}
+    for rid in range(int(rng.integers(6, 14))):
+        n, k = int(rng.integers(1, 30)), int(rng.integers(1, 25))
+        if -(-(n + k) // 4) > pages:
+            continue
+        p = prompt(seed * 100 + rid, n)
+        full = alone(p, k)
+        stop = (full[int(rng.integers(0, len(full)))],) if rng.random() < 0.3 else ()
+        plans[rid] = (p, k, stop)
+        arrivals.setdefault(int(rng.integers(0, 40)), []).append(rid)
+        if rng.random() < 0.2:
+            cancels[rid] = int(rng.integers(0, 80))
+    done, cancelled, step = {}, {}, 0
+    while step < 5000:
+        for rid in arrivals.pop(step, []):
+            p, k, stop = plans[rid]
+            submit(rid, p, k, stop_ids=stop)
+        for rid, at in list(cancels.items()):
+            if at == step:
+                f = sched.cancel(rid)
+                if f is not None:
+                    cancelled[rid] = f
+                del cancels[rid]
+        if sched.idle() and not arrivals:
+            break
+        for f in sched.step(ex).finished:
+            done[f.id] = f
+        cache.check()
+        step += 1
+    assert sched.idle() and not arrivals
+    for rid, (p, k, stop) in plans.items():
+        want = alone(p, k, stop=stop)
+        if rid in cancelled:
+            assert cancelled[rid].tokens == alone(p, k)[:len(cancelled[rid].tokens)] and rid not in done
+        else:
+            assert done[rid].tokens == want, f"request {rid}"
+            assert done[rid].finish == ("stop" if len(want) < k else "length")
+    assert cache.used_pages() == [0] and cache.free_slots() == cache.max_requests
