@@ -252,7 +252,7 @@ def test_toy_mixer_with_state_layer_run_twice_and_shared_cache(tmp_path, dtype, 
     reqs = {r: traces.prompt(300 + i, n, 130) for i, (r, n) in enumerate({"a": 23, "b": 5, "c": 41, "d": 12, "e": 30}.items())}
     want = {r: _toy_plain_logits(folder, t, hd) for r, t in reqs.items()}
     tol = {"float32": 1e-4, "bfloat16": 3e-2}[dtype]
-    for cut in (traces.whole, traces.portions, traces.mixed):
+    for cut in (traces.whole, traces.tail_one_by_one, traces.portions, traces.mixed):
         got = traces.run_steps(runner, cut(reqs))
         assert len(got) == sum(len(t) for t in reqs.values())
         for (r, pos), row in got.items():
@@ -422,7 +422,7 @@ def test_toy_routed_feed_forward_and_own_position_encoding(tmp_path, dtype):
         gaps.append(gap)
     assert min(gaps) > 0.3, "a token sits near a tie of the router: pick other seeds, the comparison would test rounding luck"
     tol = {"float32": 1e-4, "bfloat16": 3e-2}[dtype]
-    for cut in (traces.whole, traces.portions, traces.mixed):
+    for cut in (traces.whole, traces.tail_one_by_one, traces.portions, traces.mixed):
         got = traces.run_steps(runner, cut(reqs))
         assert len(got) == sum(len(t) for t in reqs.values())
         for (r, pos), row in got.items():
