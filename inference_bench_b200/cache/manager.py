@@ -157,6 +157,19 @@ class CacheManager:
                 view.tensor[slot].zero_()
         return slot
 
+    def _adopt(self, req: Hashable, slot: int) -> None:
+        """The scheduler's core admitted this request to `slot` itself: take note, and zero its fixed-size state."""
+        if req in self._requests:
+            raise CacheError(f"request {req!r} is already admitted")
+        self._requests[req] = _Request(slot, self)
+        for view in self.states.values():
+            if view.tensor is not None:
+                view.tensor[slot].zero_()
+
+    def _forget(self, req: Hashable) -> None:
+        """The scheduler's core gave back what this request held: drop it from the map."""
+        self._requests.pop(req, None)
+
     def _get(self, req: Hashable) -> _Request:
         try:
             return self._requests[req]

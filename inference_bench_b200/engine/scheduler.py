@@ -1,6 +1,9 @@
 """The scheduler: admits requests, cuts prompts into portions under a token budget, keeps every
 decoding request decoding, finishes and frees. It knows the cache manager's bookkeeping but nothing
-about the device: what runs a step is an `Executor`.
+about the device: what runs a step is an `Executor`. The decisions themselves (admission, preemption,
+the rows of a step, finishing) are made by the C++ core (csrc/host/sched_core.cpp) on integer
+handles; this class holds what the core does not need (token values, sampling parameters, request
+ids), drives the executor and keeps the cache manager's map of request ids in step.
 
 Policy, after the reference's scheduler (crates/specrt/src/sched.rs; docs/specrt-scheduler.md):
   * submit refuses what can never run: an empty prompt, max_tokens 0, prompt + max_tokens beyond the
@@ -26,10 +29,11 @@ dropped. Every call of `step` still reports exactly one step.
 """
 from __future__ import annotations
 
-from collections import deque
+import ctypes as C
 from dataclasses import dataclass, field
 from typing import Any, Hashable, Optional, Protocol, Sequence
 
+from ..cache import native
 from ..cache.manager import CacheManager, OutOfPages
 from ..sampling.params import GREEDY, SamplingParams
 from .step import StepEntry
@@ -57,14 +61,33 @@ class Request:
     stop_ids: Sequence[int] = ()
 
 
-@dataclass
 class Sequence_:
-    req: Request
-    tokens: list[int]                  # prompt + generated
-    generated: int = 0                 # tokens generated so far (also the sampling step number)
-    computed: int = 0                  # positions whose state is in the cache
-    order: int = 0                     # admission order, for preemption
-    preemptions: int = 0
+    """A request the scheduler knows: its tokens live here, its counters in the core."""
+    __slots__ = ("req", "tokens", "_h", "_sched")
+
+    def __init__(self, req: Request, tokens: list[int], handle: int, sched: "Scheduler"):
+        self.req, self.tokens, self._h, self._sched = req, tokens, handle, sched   # tokens: prompt + generated
+
+    def _get(self, i: int) -> int:
+        out = (C.c_longlong * 7)()
+        self._sched._lib.ibh_sched_get(self._sched._core, self._h, out)
+        return int(out[i])
+
+    @property
+    def generated(self) -> int:       # tokens generated so far (also the sampling step number)
+        return self._get(1)
+
+    @property
+    def computed(self) -> int:        # positions whose state is in the cache
+        return self._get(2)
+
+    @property
+    def order(self) -> int:           # admission order, for preemption
+        return self._get(3)
+
+    @property
+    def preemptions(self) -> int:
+        return self._get(4)
 
     @property
     def decoding(self) -> bool:
@@ -114,11 +137,35 @@ class _InFlight:
 class Scheduler:
     def __init__(self, cache: CacheManager, config: SchedulerConfig):
         self.cache, self.cfg = cache, config
-        self.waiting: deque[Sequence_] = deque()
-        self.running: list[Sequence_] = []
-        self._order = 0
-        self.total_preemptions = 0
+        self._lib = native.load()
+        self._limit = min(config.max_ctx, cache.max_tokens_per_request)
+        self._core = self._lib.ibh_sched_new(cache._core, len(cache.groups), config.max_num_seqs, config.max_batched_tokens, config.prefill_chunk,
+                                             self._limit)
+        self._seqs: dict[int, Sequence_] = {}        # handle -> request, for everything waiting or running
         self._inflight: Optional[_InFlight] = None   # a launched decode step whose tokens have not been read
+
+    def __del__(self):
+        core, self._core = getattr(self, "_core", None), None
+        if core:
+            self._lib.ibh_sched_free(core)
+
+    def _handles(self, count_fn, fill_fn) -> list[int]:
+        n = int(count_fn(self._core))
+        out = (C.c_int * max(1, n))()
+        fill_fn(self._core, out)
+        return list(out[:n])
+
+    @property
+    def waiting(self) -> list[Sequence_]:
+        return [self._seqs[h] for h in self._handles(self._lib.ibh_sched_n_waiting, self._lib.ibh_sched_waiting)]
+
+    @property
+    def running(self) -> list[Sequence_]:
+        return [self._seqs[h] for h in self._handles(self._lib.ibh_sched_n_running, self._lib.ibh_sched_running)]
+
+    @property
+    def total_preemptions(self) -> int:
+        return int(self._lib.ibh_sched_total_preemptions(self._core))
 
     # ------------------------------------------------------------------ submit / cancel
     def submit(self, req: Request) -> None:
@@ -127,30 +174,30 @@ class Scheduler:
             raise Refused(f"request {req.id!r}: the prompt is empty")
         if req.max_tokens <= 0:
             raise Refused(f"request {req.id!r}: max_tokens must be positive")
-        limit = min(self.cfg.max_ctx, self.cache.max_tokens_per_request)
+        limit = self._limit
         if n + req.max_tokens > limit:
             raise Refused(f"request {req.id!r}: prompt ({n}) + max_tokens ({req.max_tokens}) exceeds the context limit {limit}")
         need = max(self.cache.pages_missing(None, n + req.max_tokens, 0), default=0)
         most = min((g.pool.num_pages for g in self.cache.groups), default=need)
         if need > most:
             raise Refused(f"request {req.id!r}: needs {need} cache pages but the pool has {most}")
-        if any(s.req.id == req.id for s in list(self.waiting) + self.running):
+        if any(s.req.id == req.id for s in self._seqs.values()):
             raise Refused(f"request {req.id!r} is already known")
-        self.waiting.append(Sequence_(req, list(req.prompt)))
+        h = int(self._lib.ibh_sched_submit(self._core, n, int(req.max_tokens)))
+        self._seqs[h] = Sequence_(req, list(req.prompt), h, self)
 
     def cancel(self, req_id: Hashable) -> Optional[Finished]:
-        for s in list(self.waiting):
+        for h, s in self._seqs.items():
             if s.req.id == req_id:
-                self.waiting.remove(s)
-                return self._finished(s, "cancelled")
-        for s in self.running:
-            if s.req.id == req_id:
-                self._release(s)
-                return self._finished(s, "cancelled")
+                was = int(self._lib.ibh_sched_cancel(self._core, h))
+                if was == 2:
+                    self.cache._forget(req_id)   # the core has given its pages and slot back
+                del self._seqs[h]
+                return self._finished(s, "cancelled") if was else None
         return None
 
     def idle(self) -> bool:
-        return not self.waiting and not self.running
+        return not self._seqs
 
     # ------------------------------------------------------------------ one step
     def step(self, executor: Executor) -> StepReport:
@@ -159,40 +206,33 @@ class Scheduler:
             if ahead is not None:
                 return ahead
         report = StepReport()
-        self._grow_decoders(report)
-        decoders = [s for s in self.running if s.decoding]
-        budget = max(0, self.cfg.max_batched_tokens - len(decoders))
-        budget = self._admit(budget)
+        cap = len(self._seqs) + 1
+        preempted, admitted, rows, counts = (C.c_int * cap)(), (C.c_int * (2 * cap))(), (C.c_int * (4 * cap))(), (C.c_int * 5)()
+        self._lib.ibh_sched_plan(self._core, preempted, admitted, rows, counts)
+        n_pre, n_adm, n_rows, report.decode_rows, report.prefill_tokens = (int(c) for c in counts)
+        report.preemptions = n_pre
+        for i in range(n_pre):                        # the core has freed what they held: the cache manager forgets them
+            self.cache._forget(self._seqs[preempted[i]].req.id)
+        for i in range(n_adm):                        # and has given these a slot and their pages
+            self.cache._adopt(self._seqs[admitted[2 * i]].req.id, int(admitted[2 * i + 1]))
         entries: list[StepEntry] = []
         sampling: list[tuple[SamplingParams, int]] = []
         owners: list[Sequence_] = []
         plan: list[tuple[Sequence_, int]] = []
-        for s in decoders:
-            entries.append(StepEntry(s.req.id, [s.tokens[-1]], [0]))
-            sampling.append((s.req.sampling, s.generated))
-            owners.append(s)
-            plan.append((s, 1))
-        left = self.cfg.max_batched_tokens - len(decoders)
-        for s in sorted((s for s in self.running if not s.decoding), key=lambda s: (s.remaining_prefill, s.order)):
-            if left <= 0:
-                break
-            n = min(s.remaining_prefill, self.cfg.prefill_chunk, left)
-            last = n == s.remaining_prefill
-            entries.append(StepEntry(s.req.id, s.tokens[s.computed:s.computed + n], [n - 1] if last else []))
-            if last:
+        for i in range(n_rows):
+            s, start, n, samples = self._seqs[rows[4 * i]], int(rows[4 * i + 1]), int(rows[4 * i + 2]), bool(rows[4 * i + 3])
+            entries.append(StepEntry(s.req.id, s.tokens[start:start + n], [n - 1] if samples else []))
+            if samples:
                 sampling.append((s.req.sampling, s.generated))
                 owners.append(s)
             plan.append((s, n))
-            left -= n
-            report.prefill_tokens += n
-        report.decode_rows = len(decoders)
         if not entries:
             return report
         tokens = executor.execute(entries, sampling)
         if len(tokens) != len(owners):
             raise RuntimeError(f"the executor returned {len(tokens)} tokens for {len(owners)} sampled rows")
         for s, n in plan:
-            s.computed += n
+            self._lib.ibh_sched_computed(self._core, s._h, n)
         for s, tok in zip(owners, tokens):
             self._accept(s, int(tok), report)
         return report
@@ -233,70 +273,23 @@ class Scheduler:
         if len(tokens) != len(fl.owners):
             raise RuntimeError(f"the executor returned {len(tokens)} tokens for {len(fl.owners)} rows")
         for s, tok in zip(fl.owners, tokens):
-            if any(s is r for r in self.running):       # else it stopped or was cancelled after the launch: the token is dropped
-                s.computed += 1
+            if self._seqs.get(s._h) is s:                # else it stopped or was cancelled after the launch: the token is dropped
+                self._lib.ibh_sched_computed(self._core, s._h, 1)
                 self._accept(s, int(tok), report)
         return report
 
-    # ------------------------------------------------------------------ pieces of the policy
-    def _grow_decoders(self, report: StepReport) -> None:
-        """Every decoder needs room for one more position; preempt the newest request until it has."""
-        for s in sorted((s for s in self.running if s.decoding), key=lambda s: s.order):
-            while s in self.running:
-                try:
-                    self.cache.extend(s.req.id, s.computed + 1)
-                    break
-                except OutOfPages:
-                    victim = max(self.running, key=lambda r: r.order)
-                    self._preempt(victim)
-                    report.preemptions += 1
-
-    def _preempt(self, s: Sequence_) -> None:
-        """Recompute later: everything the request holds is freed; tokens it has emitted stay emitted."""
-        self._release(s)
-        s.computed = 0
-        s.preemptions += 1
-        self.total_preemptions += 1
-        self.waiting.appendleft(s)
-
-    def _admit(self, budget: int) -> int:
-        planned = sum(min(s.remaining_prefill, self.cfg.prefill_chunk) for s in self.running if not s.decoding)
-        while self.waiting and planned < budget:
-            s = self.waiting[0]
-            if len(self.running) >= self.cfg.max_num_seqs or self.cache.free_slots() == 0:
-                break
-            pool = min((g.pool.num_pages for g in self.cache.groups), default=0)
-            reserve = max(1, pool // 100) if self.running else 0    # sched.rs:959-961
-            if not self.cache.can_extend(None, len(s.tokens) + 1, 0, reserve):
-                break
-            self.waiting.popleft()
-            self.cache.admit(s.req.id)
-            self.cache.extend(s.req.id, len(s.tokens) + 1)
-            s.order = self._order
-            self._order += 1
-            self.running.append(s)
-            planned += min(s.remaining_prefill, self.cfg.prefill_chunk)
-        return budget
-
+    # ------------------------------------------------------------------ a sampled token arrives
     def _accept(self, s: Sequence_, token: int, report: StepReport) -> None:
-        """A sampled token arrives (sched.rs:1577-1589)."""
-        if token in s.req.stop_ids:
-            self._release(s)
-            report.finished.append(self._finished(s, "stop"))
-            return
-        s.tokens.append(token)
-        s.generated += 1
-        report.emitted.append((s.req.id, token))
-        limit = min(self.cfg.max_ctx, self.cache.max_tokens_per_request)
-        if s.generated >= s.req.max_tokens or len(s.tokens) >= limit:
-            self._release(s)
-            report.finished.append(self._finished(s, "length"))
-
-    def _release(self, s: Sequence_) -> None:
-        if s in self.running:
-            self.running.remove(s)
-        if self.cache.has(s.req.id):
-            self.cache.release(s.req.id)
+        """The core counts the token and says whether the request goes on (sched.rs:1577-1589)."""
+        stop = token in s.req.stop_ids
+        verdict = int(self._lib.ibh_sched_accept(self._core, s._h, 1 if stop else 0))
+        if not stop:
+            s.tokens.append(token)
+            report.emitted.append((s.req.id, token))
+        if verdict:
+            self.cache._forget(s.req.id)             # the core has given its pages and slot back
+            del self._seqs[s._h]
+            report.finished.append(self._finished(s, "stop" if verdict == 1 else "length"))
 
     def _finished(self, s: Sequence_, why: str) -> Finished:
         n = len(s.req.prompt)
