@@ -19,7 +19,7 @@ _SIGNATURES = {
     "ibh_cache_release": (_i, [_p, _i]), "ibh_cache_fill_rows": (_i, [_p, C.POINTER(_i), _i, C.POINTER(_i), C.POINTER(C.POINTER(_i))]),
     "ibh_cache_check": (_i, [_p]),
     "ibh_sched_new": (_p, [_p, _i, _i, _i, _i, _i]), "ibh_sched_free": (None, [_p]), "ibh_sched_submit": (_i, [_p, _i, _i]),
-    "ibh_sched_cancel": (_i, [_p, _i]), "ibh_sched_n_waiting": (_i, [_p]), "ibh_sched_n_running": (_i, [_p]),
+    "ibh_sched_cancel": (_i, [_p, _i]), "ibh_sched_n_waiting": (_i, [_p]), "ibh_sched_n_running": (_i, [_p]), "ibh_sched_steady": (_i, [_p]),
     "ibh_sched_waiting": (None, [_p, C.POINTER(_i)]), "ibh_sched_running": (None, [_p, C.POINTER(_i)]),
     "ibh_sched_total_preemptions": (C.c_longlong, [_p]), "ibh_sched_get": (None, [_p, _i, C.POINTER(C.c_longlong)]),
     "ibh_sched_plan": (None, [_p, C.POINTER(_i), C.POINTER(_i), C.POINTER(_i), C.POINTER(_i)]), "ibh_sched_computed": (None, [_p, _i, _i]),

@@ -127,6 +127,15 @@ void ibh_sched_waiting(void* sp, int* out) { std::copy(((Sched*)sp)->waiting.beg
 void ibh_sched_running(void* sp, int* out) { std::copy(((Sched*)sp)->running.begin(), ((Sched*)sp)->running.end(), out); }
 long long ibh_sched_total_preemptions(void* sp) { return ((Sched*)sp)->total_preemptions; }
 
+// 1 when something runs, nothing waits and every running request decodes: the state in which steps can be kept one ahead.
+int ibh_sched_steady(void* sp) {
+  Sched* s = (Sched*)sp;
+  if (s->running.empty() || !s->waiting.empty()) return 0;
+  for (int h : s->running)
+    if (!s->seqs[h].decoding()) return 0;
+  return 1;
+}
+
 // out[0..6] = n_tokens, generated, computed, order, preemptions, slot, state
 void ibh_sched_get(void* sp, int h, long long* out) {
   const Seq& q = ((Sched*)sp)->seqs[h];

@@ -241,8 +241,9 @@ class Scheduler:
     def _step_ahead(self, executor) -> Optional[StepReport]:
         """One step's report while decode steps are kept one ahead; None when this step has to run the ordinary way."""
         fl = self._inflight
-        steady = bool(self.running) and not self.waiting and all(s.decoding for s in self.running)
-        same = fl is not None and len(fl.owners) == len(self.running) and all(a is b for a, b in zip(fl.owners, self.running))
+        steady = bool(self._lib.ibh_sched_steady(self._core))
+        running = self.running if fl is not None else None
+        same = fl is not None and len(fl.owners) == len(running) and all(a is b for a, b in zip(fl.owners, running))
         if fl is not None and not (steady and same):    # the batch changes: read what is in flight, start afresh next time
             self._inflight = None
             return self._collect(executor, fl)
