@@ -1,7 +1,7 @@
 // How kernels address one layer's keys and values inside a paged pool.
 //
-// A pool is [num_pages][entries][2 (K, V)][kv_heads][page_size][head_dim]; a view fixes the entry
-// (the layer's place inside the page), so
+// A pool is [entries][num_pages][2 (K, V)][kv_heads][page_size][head_dim] (one layer's pages lie together);
+// a view fixes the entry (the layer), so
 //   K(page, head, slot, d) = base + page * page_stride + (head * page_size + slot) * head_dim + d
 //   V(...)                 = the same + v_offset
 // The page of position p of segment s is block_table[s * table_stride + p / page_size].

@@ -389,6 +389,33 @@ def test_attention_reports_missing_page(status):
     status.zero_()
 
 
+@pytest.mark.parametrize("page", [16, 64])
+def test_tensor_core_attention_reports_missing_pages(status, page):
+    """A block table entry that is missing or out of range, under the TMA-fed kernels (decode, fused decode,
+    prompt portions): the status word says so, nothing is read through the bad entry, and the run goes on."""
+    from inference_bench_b200.engine.context import Segment, build_context
+    from inference_bench_b200.engine.runtime import DeviceStatusError, Runtime
+    from inference_bench_b200.kernels import attention, ops
+    heads, kvh, hd = 8, 2, 128
+    rt = Runtime(DEV, "bfloat16")
+    for shapes, bad in (([(300, 1), (200, 1)], -1), ([(300, 1), (200, 1)], 10 ** 6), ([(300, 300)], -1)):
+        q, view, pos, seg, ref, _ = _attention_case(torch.bfloat16, heads, kvh, hd, page, None, shapes, 41)
+        view.block_table[0, 1] = bad
+        ctx = build_context(rt, [Segment(i, i, L_ - n, [0] * n) for i, (L_, n) in enumerate(shapes)])
+        out = attention.paged_attention(ctx, q, view, heads, None, 1 / math.sqrt(hd))
+        with pytest.raises(DeviceStatusError, match="block table"):
+            rt.check_status()
+        assert torch.isfinite(out.float()).all()
+        if shapes[0][1] == 1:   # the fused decode kernel, whose own position lies on the missing page for the second request
+            view.block_table[1, (200 - 1) // page] = bad
+            qkv = torch.randn(1, len(shapes), (heads + 2 * kvh) * hd, device=DEV)
+            ctx.memo = {}
+            out = attention.decode_fused(ctx, qkv, None, None, 1e-5, None, None, view, heads, None, 1 / math.sqrt(hd), True)
+            assert out is not None
+            with pytest.raises(DeviceStatusError, match="block table"):
+                rt.check_status()
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("hd,rot,T", [(24, 24, 21), (64, 32, 21), (16, 0, 21), (64, 64, 21), (128, 128, 21), (128, 0, 21), (128, 128, 1031), (64, 64, 1100),
                                       (64, 0, 1025)])   # more than 8,192 (token, head) items: four per warp
