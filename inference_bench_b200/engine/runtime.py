@@ -42,6 +42,7 @@ class Runtime:
         if not torch.cuda.is_available():
             raise L.KernelLibraryError("no CUDA device is visible; the engine has no CPU path")
         L.load()
+        ops._device_index = self.device.index if self.device.index is not None else torch.cuda.current_device()   # whose current stream the kernels are launched on
         self.mode = "float32" if MODES[dtype] == torch.float32 else "bfloat16"
         self.act_dtype = MODES[dtype]
         self.gemm = gemm  # "auto" | "simt" | "tcgen05"

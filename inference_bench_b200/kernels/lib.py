@@ -100,10 +100,14 @@ launches = 0   # kernels launched so far through `call`
 KERNELS_PER_CALL = {"ib_sample_rows": 3, "ib_attention_decode": 2, "ib_attention_decode_stream": 2, "ib_attention_decode_fused": 2}
 
 
+_entry: dict = {}   # name -> (function, kernels it launches)
+
+
 def call(name: str, *args) -> None:
     global launches
-    lib = load()
-    launches += KERNELS_PER_CALL.get(name, 1)
-    rc = getattr(lib, name)(*args)
-    if rc != 0:
-        raise KernelError(lib.ib_last_error().decode(errors="replace"))
+    e = _entry.get(name)
+    if e is None:
+        e = _entry[name] = (getattr(load(), name), KERNELS_PER_CALL.get(name, 1))
+    launches += e[1]
+    if e[0](*args) != 0:
+        raise KernelError(load().ib_last_error().decode(errors="replace"))

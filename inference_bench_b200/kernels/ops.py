@@ -37,8 +37,18 @@ def _check(name: str, t: torch.Tensor, dtype=None, shape=None) -> None:
         raise L.KernelError(f"{name} must have shape {tuple(shape)}, got {tuple(t.shape)}")
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)   # the current stream's handle without building a Stream object
+_device_index: Optional[int] = None
+
+
 def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    """The handle of torch's current stream on the engine's device (every kernel is launched on it)."""
+    global _device_index
+    if _raw_stream is None:
+        return torch.cuda.current_stream().cuda_stream
+    if _device_index is None:
+        _device_index = torch.cuda.current_device()
+    return _raw_stream(_device_index)
 
 
 _KV_MAPS: dict = {}   # (pool address, shape) -> (buffer that owns the bytes, aligned address of the 128-byte tensor map) or None
