@@ -7,6 +7,7 @@ sizes of the product (T, N, K), never on which requests make up the batch.
 """
 from __future__ import annotations
 
+import functools
 from typing import Optional
 
 import torch
@@ -34,6 +35,7 @@ def supports(k: int) -> bool:
 _SHAPE_SPEED = {(256, True): 1.0, (256, False): 0.89, (128, True): 0.87, (128, False): 0.78}
 
 
+@functools.lru_cache(maxsize=4096)
 def choose(T: int, N: int, K: int, allow_split: bool = True) -> tuple[int, int, bool]:
     """(tokens per CTA, k-splits, wide). Up to 128 tokens: the smallest token tile that holds them,
     and the k-range split over CTAs until the GPU is full. More tokens: the 128/256-token tile, 128

@@ -87,6 +87,12 @@ class KvLayerView:
         return (m[1] if m else None), self.entry * pages * 2 * kv_heads * page_size
 
     def c_view(self) -> L.KvView:
+        cv = self.__dict__.get("_cv")   # made once per view: a layer asks for it several times a step
+        if cv is None:
+            cv = self.__dict__["_cv"] = self._make_c_view()
+        return cv
+
+    def _make_c_view(self) -> L.KvView:
         entries, pages, two, kv_heads, page_size, head_dim = self.pool.shape
         if two != 2:
             raise L.KernelError(f"a KV pool must be [entries, pages, 2, kv_heads, page_size, head_dim], got {tuple(self.pool.shape)}")
