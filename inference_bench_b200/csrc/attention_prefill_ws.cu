@@ -290,7 +290,7 @@ __global__ void __launch_bounds__(kThreads, 2)
       if (j == 0) {
         m_ref = tile_max;
       } else if (__any_sync(0xffffffffu, grow)) {
-        wait(o_full, (j - 1) & 1);
+        wait(o_full, (j - 1) & 1);   // (S_j is ready, so P V of tile j - 2, issued before it, has finished: the parity means tile j - 1)
         sm100::tc_fence_after();
         const float m_new = grow ? fmaxf(m_ref, tile_max) : m_ref;
         const float f = m_new == -INFINITY ? 1.f : ex2(m_ref - m_new);  // 1 for rows that keep their reference, 0 when it was -inf
@@ -329,7 +329,13 @@ __global__ void __launch_bounds__(kThreads, 2)
       sm100::tmem_st_wait();
       sm100::tc_fence_before();
       __syncwarp();
-      if (lane == 0) sm100::mbar_arrive(&p_full[j & 1]);
+      if (lane == 0) {
+        // A parity wait tells a phase from the one before it only, so no phase of o_full may go unseen: P V of tile
+        // j - 1 is waited for here, before P_j is handed over (P V of tile j cannot start, so the barrier is in phase
+        // j - 1 or j now). The MMAs run in order anyway: nothing waits here that would not have waited there.
+        if (j > 0) wait(o_full, (j - 1) & 1);
+        sm100::mbar_arrive(&p_full[j & 1]);
+      }
     }
     // ---- O / l -> out
     wait(o_full, (n_kt - 1) & 1);

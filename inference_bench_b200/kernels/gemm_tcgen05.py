@@ -24,7 +24,8 @@ L.register("ib_gemm_tcgen05_2cta", [L._p, L._p, L._p, L._i, L._i, L._i, L._p, L.
 L.register("ib_gemm_swiglu_tcgen05_2cta", [L._p, L._p, L._p, L._i, L._i, L._i, L._p, L._p])
 L.register("ib_gemm_tcgen05_2cta_add", [L._p, L._p, L._p, L._i, L._i, L._i, L._p, L._p])
 
-PAIR_MIN_TOKENS = 256   # from here on the persistent CTA-pair kernels (csrc/gemm_tcgen05_2cta.cu) take over
+PAIR_MIN_TOKENS = 129    # the fused gate/up product runs on the persistent CTA-pair kernel (csrc/gemm_tcgen05_2cta.cu) from here on
+PAIR_ALWAYS_TOKENS = 2048   # and every product from here on; between the two, `plan` decides by its cost model
 
 
 def supports(k: int) -> bool:
@@ -61,6 +62,43 @@ def choose(T: int, N: int, K: int, allow_split: bool = True) -> tuple[int, int, 
     return bn, 1, wide
 
 
+# Cost model for 129 to 2,048 tokens, fitted to timings of every variant below on the layer shapes of Qwen3-0.6B, 8B,
+# 14B and 32B at 160 to 1,536 tokens (the variant it picks is within 5 % of the fastest on all of them, 0.2 % on
+# average). A variant's time is waves of CTAs (or CTA pairs) times the longer of a CTA's MMA time and its copy time,
+# plus a fixed cost, plus the traffic of split-K partial sums. Units: FLOP/us, bytes/us, us.
+_MID = dict(rate=4.015e6, cap=250e3, t0=4.36, partial_bw=3.455e6, pair_rate=5.446e6, hbm=8.0e6, pair_cap=188e3,
+            speed={(256, True): 1.0, (256, False): 0.982, (128, True): 0.895, (128, False): 0.956})
+
+
+@functools.lru_cache(maxsize=4096)
+def plan(T: int, N: int, K: int) -> tuple:
+    """For 129 <= T <= 2048: ("pair",) or ("single", tokens per CTA, k-splits, wide), whichever the cost model
+    expects to be faster. Depends on the sizes only."""
+    m = _MID
+    tiles = -(-N // 256) * -(-T // 256)
+    active = min(tiles, SM_COUNT // 2) * 2
+    best = (-(-tiles // (SM_COUNT // 2)) * max(256 * 256 * K * 2 / (2 * m["pair_rate"]), 256 * K * 2 / min(m["pair_cap"], m["hbm"] / active)) + m["t0"],
+            ("pair",))
+    ktiles = -(-K // 64)
+    for bn in (128, 256):
+        for wide in (False, True):
+            rows = 256 if wide else 128
+            for sp in (1, 2, 3, 4, 6):
+                per = -(-ktiles // sp)
+                if sp > max(1, ktiles // 4) or -(-ktiles // per) != sp:
+                    continue
+                ctas = -(-N // rows) * -(-T // bn) * sp
+                if sp > 1 and ctas > 4 * SM_COUNT:
+                    continue
+                kc = per * 64
+                mma = rows * bn * kc * 2 / (m["rate"] * m["speed"][(bn, wide)])
+                copy = (rows + min(bn, T)) * kc * 2 / min(m["cap"], m["hbm"] / min(ctas, SM_COUNT))
+                t = -(-ctas // SM_COUNT) * max(mma, copy) + m["t0"] + (sp * T * N * 4 / m["partial_bw"] if sp > 1 else 0.0)
+                if t < best[0]:
+                    best = (t, ("single", bn, sp, wide))
+    return best[1]
+
+
 def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bn: int, splits: int, status: torch.Tensor, wide: bool = False) -> None:
     """out [splits, T, N] float32 = per-split partial products of x [T, K] and w [N, K] (bfloat16).
     wide: 256 rows of w per CTA instead of 128 (token tiles of 128 or 256 only)."""
@@ -85,7 +123,13 @@ def gemm_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch
 
 def linear(rt, x: torch.Tensor, lw, allow_split: bool = True, add_to: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
     T = x.shape[0]
-    if T >= PAIR_MIN_TOKENS:
+    how = ("pair",) if T >= PAIR_ALWAYS_TOKENS else (plan(T, lw.n, lw.k) if T > 128 else None)
+    if how is not None and how[0] == "single":
+        _, bn, splits, wide = how
+        out = rt.empty((splits, T, lw.n), torch.float32)
+        gemm(x, lw.weight, out, bn, splits, rt.status, wide)
+        return out
+    if how is not None:
         if add_to is not None:
             gemm_pair(x, lw.weight, add_to, rt.status, add=True)
             return None

@@ -45,3 +45,32 @@ def test_bfloat16_against_float32_at_large_layer_sizes(shape, page):
     err = (got - ref).abs().max().item() / ref.abs().max().item()
     assert err <= 3e-2, f"bfloat16 differs from float32 by {err:.3e} of max|logit|"
     print(f"{shape} layer sizes, 2 layers: bfloat16 vs float32 worst {err:.3e} of max|logit|")
+
+
+@pytest.mark.parametrize("shape,page,tokens", [("8b", 16, 257), ("32b", 16, 257), ("14b", 64, 321)])
+def test_a_prompt_portion_gives_the_same_bits_every_time(shape, page, tokens):
+    """Kernels that start while the kernel before them is still running (programmatic dependent launch) must give
+    what one kernel after the other gives, run after run: with every query tile released at the same moment, copies
+    land late, and a wait in the prefill attention kernel that took a barrier's phase for the one before it showed
+    here as a few rows of one layer's attention output that changed from run to run."""
+    from inference_bench_b200 import Engine
+    from inference_bench_b200.engine.step import StepEntry
+    from inference_bench_b200.kernels import lib as L
+    lib = L.load()
+    prompt = np.random.default_rng(1).integers(0, 151936, tokens).tolist()
+    eng = Engine(SHAPES[shape], dtype="bfloat16", max_ctx=512, page_size=page, num_pages=64, max_num_seqs=2, random_weights_seed=0)
+
+    def once():
+        eng.cache.admit("r")
+        out = eng.runner.step([StepEntry("r", prompt, [0, tokens // 3, tokens - 1])])
+        eng.cache.release("r")
+        return out
+
+    assert lib.ib_pdl_enabled() == 1
+    lib.ib_set_pdl(0)
+    try:
+        ref = once()
+    finally:
+        lib.ib_set_pdl(1)
+    different = sum(not torch.equal(once(), ref) for _ in range(60))
+    assert different == 0, f"{different} of 60 runs differ from the run with one kernel after the other"
