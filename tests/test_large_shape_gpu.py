@@ -74,3 +74,47 @@ def test_a_prompt_portion_gives_the_same_bits_every_time(shape, page, tokens):
         lib.ib_set_pdl(1)
     different = sum(not torch.equal(once(), ref) for _ in range(60))
     assert different == 0, f"{different} of 60 runs differ from the run with one kernel after the other"
+
+
+def test_mixed_steps_give_the_same_bits_every_time():
+    """One random schedule of mixed steps (portions of 2 to 257 tokens beside decoded tokens, four requests), replayed
+    with one kernel after the other and then eight times with kernels starting early: the same logits, bit for bit."""
+    from inference_bench_b200 import Engine
+    from inference_bench_b200.engine.step import StepEntry
+    from inference_bench_b200.kernels import lib as L
+    lib = L.load()
+    rng = np.random.default_rng(5)
+    names = ["r0", "r1", "r2", "r3"]
+    prompts = {k: rng.integers(0, 151936, int(rng.integers(40, 420))).tolist() for k in names}
+    done = dict.fromkeys(names, 0)
+    steps = []
+    while any(done[k] < len(prompts[k]) for k in names):
+        entries = []
+        for k in names:
+            left = len(prompts[k]) - done[k]
+            if left == 0 or rng.random() < 0.25:
+                continue
+            n = 1 if (done[k] > 0 and rng.random() < 0.5) else int(min(left, rng.choice([2, 17, 64, 128, 129, 200, 257])))
+            entries.append((k, prompts[k][done[k]:done[k] + n], [n - 1]))
+            done[k] += n
+        if entries:
+            steps.append(entries)
+    eng = Engine(SHAPES["8b"], dtype="bfloat16", max_ctx=512, page_size=16, num_pages=128, max_num_seqs=4, random_weights_seed=0)
+
+    def replay():
+        for k in names:
+            eng.cache.admit(k)
+        outs = [eng.runner.step([StepEntry(*e) for e in entries]) for entries in steps]
+        for k in names:
+            eng.cache.release(k)
+        return outs
+
+    lib.ib_set_pdl(0)
+    try:
+        ref = replay()
+    finally:
+        lib.ib_set_pdl(1)
+    for i in range(8):
+        got = replay()
+        diff = [j for j, (a, b) in enumerate(zip(ref, got)) if not torch.equal(a, b)]
+        assert not diff, f"replay {i}: the logits of steps {diff} of {len(steps)} differ from the run with one kernel after the other"
