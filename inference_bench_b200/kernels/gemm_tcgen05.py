@@ -32,34 +32,22 @@ def supports(k: int) -> bool:
     return k % 8 == 0
 
 
-# relative speed of the large-tile shapes at equal work, measured on Qwen3-8B layer shapes (2,048 tokens)
-_SHAPE_SPEED = {(256, True): 1.0, (256, False): 0.89, (128, True): 0.87, (128, False): 0.78}
-
-
 @functools.lru_cache(maxsize=4096)
 def choose(T: int, N: int, K: int, allow_split: bool = True) -> tuple[int, int, bool]:
-    """(tokens per CTA, k-splits, wide). Up to 128 tokens: the smallest token tile that holds them,
-    and the k-range split over CTAs until the GPU is full. More tokens: the 128/256-token tile, 128
-    or 256 rows of W per CTA, whichever needs the least time by waves of CTAs times work per CTA."""
+    """(tokens per CTA, k-splits, wide) for up to 128 tokens: the smallest token tile that holds them, and the
+    k-range split over CTAs until the GPU is full."""
+    if T > 128:
+        raise ValueError(f"choose is for up to 128 tokens, got {T}: see plan")
     ktiles = -(-K // 64)
-    if T <= 128:
-        bn = next(b for b in TOKEN_TILES if T <= b)
-        tiles = -(-N // 128)
-        slots = SM_COUNT * (2 if bn <= 64 else 1)      # CTAs resident at once (two per SM for the small token tiles)
-        splits = 1
-        if allow_split and tiles < slots:
-            splits = max(1, min(slots // tiles, ktiles // 4, 16))
-            per = -(-ktiles // splits)
-            splits = -(-ktiles // per)  # no empty split
-        return bn, splits, False
-
-    def cost(shape):
-        bn, wide = shape
-        rows = 256 if wide else 128
-        ctas = -(-N // rows) * -(-T // bn)
-        return -(-ctas // SM_COUNT) * rows * bn / _SHAPE_SPEED[shape]
-    bn, wide = min(_SHAPE_SPEED, key=cost)
-    return bn, 1, wide
+    bn = next(b for b in TOKEN_TILES if T <= b)
+    tiles = -(-N // 128)
+    slots = SM_COUNT * (2 if bn <= 64 else 1)      # CTAs resident at once (two per SM for the small token tiles)
+    splits = 1
+    if allow_split and tiles < slots:
+        splits = max(1, min(slots // tiles, ktiles // 4, 16))
+        per = -(-ktiles // splits)
+        splits = -(-ktiles // per)  # no empty split
+    return bn, splits, False
 
 
 # Cost model for 129 to 2,048 tokens, fitted to timings of every variant below on the layer shapes of Qwen3-0.6B, 8B,
@@ -70,9 +58,24 @@ _MID = dict(rate=4.015e6, cap=250e3, t0=4.36, partial_bw=3.455e6, pair_rate=5.44
             speed={(256, True): 1.0, (256, False): 0.982, (128, True): 0.895, (128, False): 0.956})
 
 
+def single_variants(T: int, N: int, K: int):
+    """The forms of the single-CTA kernel that `plan` weighs for more than 128 tokens: (tokens per CTA, k-splits, wide)."""
+    ktiles = -(-K // 64)
+    for bn in (128, 256):
+        for wide in (False, True):
+            for sp in (1, 2, 3, 4, 6):
+                per = -(-ktiles // sp)
+                if sp > max(1, ktiles // 4) or -(-ktiles // per) != sp:   # at least four k-tiles a split, and none empty
+                    continue
+                ctas = -(-N // (256 if wide else 128)) * -(-T // bn) * sp
+                if sp > 1 and ctas > 4 * SM_COUNT:
+                    continue
+                yield bn, sp, wide
+
+
 @functools.lru_cache(maxsize=4096)
 def plan(T: int, N: int, K: int) -> tuple:
-    """For 129 <= T <= 2048: ("pair",) or ("single", tokens per CTA, k-splits, wide), whichever the cost model
+    """For 129 <= T < 2048: ("pair",) or ("single", tokens per CTA, k-splits, wide), whichever the cost model
     expects to be faster. Depends on the sizes only."""
     m = _MID
     tiles = -(-N // 256) * -(-T // 256)
@@ -80,22 +83,15 @@ def plan(T: int, N: int, K: int) -> tuple:
     best = (-(-tiles // (SM_COUNT // 2)) * max(256 * 256 * K * 2 / (2 * m["pair_rate"]), 256 * K * 2 / min(m["pair_cap"], m["hbm"] / active)) + m["t0"],
             ("pair",))
     ktiles = -(-K // 64)
-    for bn in (128, 256):
-        for wide in (False, True):
-            rows = 256 if wide else 128
-            for sp in (1, 2, 3, 4, 6):
-                per = -(-ktiles // sp)
-                if sp > max(1, ktiles // 4) or -(-ktiles // per) != sp:
-                    continue
-                ctas = -(-N // rows) * -(-T // bn) * sp
-                if sp > 1 and ctas > 4 * SM_COUNT:
-                    continue
-                kc = per * 64
-                mma = rows * bn * kc * 2 / (m["rate"] * m["speed"][(bn, wide)])
-                copy = (rows + min(bn, T)) * kc * 2 / min(m["cap"], m["hbm"] / min(ctas, SM_COUNT))
-                t = -(-ctas // SM_COUNT) * max(mma, copy) + m["t0"] + (sp * T * N * 4 / m["partial_bw"] if sp > 1 else 0.0)
-                if t < best[0]:
-                    best = (t, ("single", bn, sp, wide))
+    for bn, sp, wide in single_variants(T, N, K):
+        rows = 256 if wide else 128
+        ctas = -(-N // rows) * -(-T // bn) * sp
+        kc = -(-ktiles // sp) * 64
+        mma = rows * bn * kc * 2 / (m["rate"] * m["speed"][(bn, wide)])
+        copy = (rows + min(bn, T)) * kc * 2 / min(m["cap"], m["hbm"] / min(ctas, SM_COUNT))
+        t = -(-ctas // SM_COUNT) * max(mma, copy) + m["t0"] + (sp * T * N * 4 / m["partial_bw"] if sp > 1 else 0.0)
+        if t < best[0]:
+            best = (t, ("single", bn, sp, wide))
     return best[1]
 
 

@@ -40,7 +40,8 @@ def test_gemm_simt_float32(T, N, K):
 
 @pytest.mark.parametrize("T,N,K,bn,splits", [
     (1, 128, 64, 16, 1), (5, 100, 96, 16, 1), (16, 136, 72, 16, 2), (17, 384, 1024, 32, 4), (33, 130, 520, 64, 3),
-    (100, 1000, 264, 128, 1), (300, 257, 2048, 256, 2), (513, 640, 4096, 256, 1), (8, 4096, 4096, None, None), (2048, 1536, 1024, None, None)])
+    (100, 1000, 264, 128, 1), (300, 257, 2048, 256, 2), (513, 640, 4096, 256, 1), (8, 4096, 4096, None, None), (128, 1536, 1024, None, None),
+    (2048, 1536, 1024, 256, 1)])
 def test_gemm_tcgen05_bfloat16(status, T, N, K, bn, splits):
     from inference_bench_b200.kernels import gemm_tcgen05 as G
     x = (torch.randn(T, K, generator=_g(3)) * 0.5).to(torch.bfloat16).to(DEV)
@@ -59,6 +60,33 @@ def test_gemm_tcgen05_bfloat16(status, T, N, K, bn, splits):
     simt = torch.empty(T, N, device=DEV)
     ops.gemm_simt(x, w, simt)
     assert (got - simt.double()).abs().max() <= 2e-5 * ref.abs().max() + 1e-6
+
+
+@pytest.mark.parametrize("T,N,K", [(257, 1100, 1544), (300, 264, 4096), (129, 2000, 520), (700, 520, 1024)])
+def test_gemm_tcgen05_every_form_above_128_tokens(status, T, N, K):
+    """Every (token tile, k-split, wide) that `plan` may choose between 129 and 2,047 tokens, the CTA-pair kernel and
+    what `plan` picks: all against the float64 product, and each the same bits when run twice."""
+    from inference_bench_b200.kernels import gemm_tcgen05 as G
+    x = (torch.randn(T, K, generator=_g(5)) * 0.5).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, K, generator=_g(6)) * 0.5).to(torch.bfloat16).to(DEV)
+    ref = x.double() @ w.double().T
+    tol = 2e-5 * ref.abs().max() + 1e-6
+    forms = list(G.single_variants(T, N, K))
+    assert len(forms) >= 6
+    for bn, sp, wide in forms:
+        outs = []
+        for _ in range(2):
+            out = torch.full((sp, T, N), float("nan"), device=DEV)
+            G.gemm(x, w, out, bn, sp, status, wide)
+            outs.append(out)
+        assert status.item() == 0
+        assert torch.equal(outs[0], outs[1]), (bn, sp, wide)
+        assert (outs[0].double().sum(0) - ref).abs().max() <= tol, (bn, sp, wide)
+    out = torch.full((T, N), float("nan"), device=DEV)
+    G.gemm_pair(x, w, out, status)
+    assert status.item() == 0 and (out.double() - ref).abs().max() <= tol
+    how = G.plan(T, N, K)
+    assert how == ("pair",) or tuple(how[1:]) in forms
 
 
 @pytest.mark.parametrize("T,N,K,bn", [(130, 300, 72, 128), (300, 520, 264, 256), (700, 1000, 1024, 256)])
