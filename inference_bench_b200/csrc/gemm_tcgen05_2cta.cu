@@ -14,6 +14,9 @@
 // The reference's equivalent is its mma.sync tile kernel (crates/kir/src/cuda/gemm/core.rs:14-155).
 #include <cuda.h>
 
+#include <cuda_bf16.h>
+
+#include "kv_view.cuh"
 #include "sm100.cuh"
 #include "tma_host.cuh"
 
@@ -24,6 +27,8 @@ constexpr int BK = 64;
 constexpr int UMMA_K = 16;
 constexpr int kThreads = 192;
 constexpr int EPI_STORE = 0, EPI_SWIGLU = 1, EPI_ADD = 2;   // float32 out; bfloat16 silu(gate) * up; float32 out += product
+constexpr int EPI_QKV = 3;   // the q/k/v projection finished in the epilogue: per-head norm, rotation, queries out, keys and values into the cache
+constexpr int kQkvHead = 128;   // head size of the EPI_QKV form: a head is 128 accumulator columns
 constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;   // clears the bit that tells the two CTAs of a pair apart in a shared::cluster address
 
 // BN: tokens per tile = accumulator columns (each CTA loads half of them)
@@ -32,10 +37,15 @@ struct Tile {
   static constexpr int kABytes = BM * BK * 2, kBBytes = (BN / 2) * BK * 2;
   static constexpr int kStageBytes = MT * kABytes + kBBytes;
   static constexpr int kStages = (200 * 1024) / kStageBytes;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */ + 1024 /* norm scales of EPI_QKV */;
   static constexpr int kAccSets = 512 / (MT * BN);   // accumulator sets that fit tensor memory
 };
 
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {   // round to nearest even
+  uint32_t d;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  return d;
+}
 __device__ __forceinline__ uint32_t cluster_rank() {
   uint32_t r;
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -79,6 +89,27 @@ __device__ __forceinline__ void arrive_on_leader(uint64_t* bar) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(sm100::smem_u32(bar) & kPeerBitMask) : "memory");
 }
 
+// What the EPI_QKV epilogue works with. The product is taken the other way round there: the tokens are the
+// rows of the MMA (tensor-memory lanes: a thread of the epilogue owns a token) and the rows of the fused
+// [q | k | v] weight are its columns, so that a head's 128 values of a token sit in one thread: the norm is a
+// sum inside the thread, the rotation partner (d + 64) is the thread's own, and a token's head goes out as one
+// contiguous row. What `qk_norm_rope_kv` computes from the stored product, with the same formulas:
+// per-head RMSNorm of q and k heads (scales or null), half rotation by the step's tables (or null), queries
+// as bfloat16 [tokens][heads * 128], keys and values into the paged cache at the token's position.
+struct QkvEpi {
+  const float* q_norm_w;
+  const float* k_norm_w;
+  float eps;
+  const float* cos_t;   // [tokens][64]
+  const float* sin_t;
+  const int* positions;
+  const int* seg_of_token;
+  __nv_bfloat16* q_out;
+  IbKvView kv;
+  int write_kv;
+  int heads;
+};
+
 // Persistent: each CTA pair walks tiles pair, pair + n_pairs, ... (token tiles vary fastest, so the
 // pairs that work at the same time share rows of W). The TMA warps run ahead into the next tile
 // while the accumulator of the last one is stored; with one accumulator per tile (MT = 1) tensor
@@ -86,7 +117,7 @@ __device__ __forceinline__ void arrive_on_leader(uint64_t* bar) {
 template <int MT, int EPI, int BN>
 __global__ void __launch_bounds__(kThreads, 1)
     gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, void* __restrict__ out_, int T, int N,
-                     int K, int token_tiles, int total_tiles, int second_off, unsigned* __restrict__ status) {
+                     int K, int token_tiles, int total_tiles, int second_off, unsigned* __restrict__ status, const QkvEpi qe) {
   using TL = Tile<MT, BN>;
   constexpr int STAGES = TL::kStages;
   constexpr int BNH = BN / 2;
@@ -99,6 +130,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   uint64_t* acc_full = empty + STAGES;   // [NBUF]
   uint64_t* acc_empty = acc_full + 2;    // [NBUF], used in the leader CTA
   uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+  float* norm_s = (float*)(tiles + STAGES * TL::kStageBytes + 256);   // EPI_QKV: q scales [128], k scales [128]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_rank();          // 0 = leader
@@ -121,6 +153,12 @@ __global__ void __launch_bounds__(kThreads, 1)
   if (warp == 1) {
     tmem_alloc2(tmem_slot, 512);
     tmem_relinquish2();
+  }
+  if constexpr (EPI == EPI_QKV) {   // the norm scales are weights: nothing earlier in the stream writes them
+    for (int i = threadIdx.x; i < 2 * kQkvHead; i += kThreads) {
+      const float* src = i < kQkvHead ? qe.q_norm_w : qe.k_norm_w;
+      norm_s[i] = src ? src[i % kQkvHead] : 1.f;
+    }
   }
   sm100::tc_fence_before();
   __syncthreads();
@@ -152,6 +190,10 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
           uint8_t* a = tiles + s * TL::kStageBytes;
           if (rank == 0) sm100::mbar_arrive_expect_tx(&full[s], 2 * TL::kStageBytes);   // the leader counts both CTAs' bytes
+          if (EPI == EPI_QKV && !waited) {   // there the rows are the tokens, which the kernel before wrote
+            ib::pdl_wait();
+            waited = true;
+          }
 #pragma unroll
           for (int m = 0; m < MT; m++) tma_load_2d_pair(a + m * TL::kABytes, &tmap_w, i * BK, w_row(rb, m), &full[s]);
           if (!waited) {   // the weights above do not depend on earlier kernels; x does
@@ -209,7 +251,96 @@ __global__ void __launch_bounds__(kThreads, 1)
       sm100::tc_fence_after();
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      if constexpr (EPI == EPI_STORE || EPI == EPI_ADD) {
+      if constexpr (EPI == EPI_QKV) {
+        // this thread's token, and the (up to) two heads of the tile: columns [0,128) and [128,256) of the accumulator
+        const int tok = n_pair + (int)rank * BM + q * 32 + lane;
+        const bool live = tok < N;
+        const int kvh = qe.kv.kv_heads;
+        int pos = 0, seg = 0;
+        if (live && qe.write_kv) {
+          pos = qe.positions[tok];
+          seg = qe.seg_of_token[tok];
+        }
+        const float* cs = qe.cos_t ? qe.cos_t + (size_t)tok * (kQkvHead / 2) : nullptr;
+        const float* sn = qe.sin_t ? qe.sin_t + (size_t)tok * (kQkvHead / 2) : nullptr;
+#pragma unroll 1
+        for (int hh = 0; hh < BN / kQkvHead; hh++) {
+          const int j = t0 / kQkvHead + hh;   // head slot: q heads, then k heads, then v heads
+          if (j * kQkvHead >= T) break;
+          const bool is_q = j < qe.heads, is_k = !is_q && j < qe.heads + kvh;
+          if (!is_q && !qe.write_kv) continue;
+          const uint32_t col0 = lane_addr + b * MT * BN + hh * kQkvHead;
+          const float* nw = is_q ? (qe.q_norm_w ? norm_s : nullptr) : (is_k && qe.k_norm_w ? norm_s + kQkvHead : nullptr);
+          float inv = 1.f;
+          if (nw) {   // sum of squares over the head, d rising (uniform branch: every lane of the warp reads tensor memory)
+            float ss = 0.f;
+#pragma unroll 1
+            for (int c0 = 0; c0 < kQkvHead; c0 += 32) {
+              uint32_t r[32];
+              sm100::tmem_ld_32x32b_x32(col0 + c0, r);
+              sm100::tmem_ld_wait();
+#pragma unroll
+              for (int c = 0; c < 32; c++) ss = __fmaf_rn(__uint_as_float(r[c]), __uint_as_float(r[c]), ss);
+            }
+            inv = rsqrtf(ss / (float)kQkvHead + qe.eps);
+          }
+          // destination row of this token's head
+          __nv_bfloat16* dst = nullptr;
+          if (live) {
+            if (is_q) {
+              dst = qe.q_out + ((size_t)tok * qe.heads + j) * kQkvHead;
+            } else {
+              const long long off = ib::kv_offset(qe.kv, seg, pos, is_k ? j - qe.heads : j - qe.heads - kvh);
+              if (off < 0)
+                atomicOr(status, IB_ERR_BAD_PAGE);
+              else
+                dst = (__nv_bfloat16*)qe.kv.base + off + (is_k ? 0 : qe.kv.v_offset);
+            }
+          }
+          const bool turn = (is_q || is_k) && cs != nullptr;
+#pragma unroll 1
+          for (int c0 = 0; c0 < kQkvHead / 2; c0 += 32) {   // values d = c0 + c and their rotation partners d + 64
+            uint32_t lo[32], hi[32];
+            sm100::tmem_ld_32x32b_x32(col0 + c0, lo);
+            sm100::tmem_ld_32x32b_x32(col0 + kQkvHead / 2 + c0, hi);
+            sm100::tmem_ld_wait();
+            if (dst) {
+#pragma unroll
+              for (int c4 = 0; c4 < 32; c4 += 4) {
+                float a[4], bb[4];
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                  a[e] = __uint_as_float(lo[c4 + e]);
+                  bb[e] = __uint_as_float(hi[c4 + e]);
+                  if (nw) {
+                    a[e] = nw[c0 + c4 + e] * (a[e] * inv);
+                    bb[e] = nw[kQkvHead / 2 + c0 + c4 + e] * (bb[e] * inv);
+                  }
+                }
+                if (turn) {
+                  const float4 c = *(const float4*)(cs + c0 + c4), sgn = *(const float4*)(sn + c0 + c4);
+                  const float cv[4] = {c.x, c.y, c.z, c.w}, sv[4] = {sgn.x, sgn.y, sgn.z, sgn.w};
+#pragma unroll
+                  for (int e = 0; e < 4; e++) {
+                    const float x0 = a[e], x1 = bb[e];
+                    a[e] = __fmaf_rn(x1, -sv[e], __fmul_rn(x0, cv[e]));
+                    bb[e] = __fmaf_rn(x0, sv[e], __fmul_rn(x1, cv[e]));
+                  }
+                }
+                lo[c4 / 2] = pack_bf16x2(a[0], a[1]);
+                lo[c4 / 2 + 1] = pack_bf16x2(a[2], a[3]);
+                hi[c4 / 2] = pack_bf16x2(bb[0], bb[1]);
+                hi[c4 / 2 + 1] = pack_bf16x2(bb[2], bb[3]);
+              }
+#pragma unroll
+              for (int v = 0; v < 4; v++) {
+                *(uint4*)(dst + c0 + 8 * v) = make_uint4(lo[4 * v], lo[4 * v + 1], lo[4 * v + 2], lo[4 * v + 3]);
+                *(uint4*)(dst + kQkvHead / 2 + c0 + 8 * v) = make_uint4(hi[4 * v], hi[4 * v + 1], hi[4 * v + 2], hi[4 * v + 3]);
+              }
+            }
+          }
+        }
+      } else if constexpr (EPI == EPI_STORE || EPI == EPI_ADD) {
         float* dst = (float*)out_;
 #pragma unroll 1
         for (int m = 0; m < MT; m++) {
@@ -283,7 +414,8 @@ int make_tmap(CUtensorMap* m, const void* ptr, int rows, int K, int box_rows) {
 }
 
 template <int MT, int EPI, int BN>
-int launch(const void* x, const void* w, void* out, int T, int N, int K, int w_rows, int second_off, unsigned* status, cudaStream_t stream) {
+int launch(const void* x, const void* w, void* out, int T, int N, int K, int w_rows, int second_off, unsigned* status, cudaStream_t stream,
+           const QkvEpi& qe = QkvEpi{}) {
   using TL = Tile<MT, BN>;
   IB_CHECK_ARG(T > 0 && N > 0 && K > 0 && K % 8 == 0, "gemm_tcgen05_2cta: bad sizes T=%d N=%d K=%d (K must be a multiple of 8)", T, N, K);
   IB_CHECK_ARG(((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0, "gemm_tcgen05_2cta: operands must be 16-byte aligned");
@@ -320,7 +452,7 @@ int launch(const void* x, const void* w, void* out, int T, int N, int K, int w_r
   attr[1].val.programmaticStreamSerializationAllowed = ib_pdl_enabled();
   cfg.attrs = attr;
   cfg.numAttrs = 2;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_2cta_kernel<MT, EPI, BN>, tw, tx, out, T, N, K, token_tiles, total_tiles, second_off, status);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_2cta_kernel<MT, EPI, BN>, tw, tx, out, T, N, K, token_tiles, total_tiles, second_off, status, qe);
   IB_CHECK_ARG(e == cudaSuccess, "gemm_tcgen05_2cta: launch failed: %s", cudaGetErrorString(e));
   return 0;
 }
@@ -343,4 +475,25 @@ extern "C" int ib_gemm_tcgen05_2cta_add(const void* x, const void* w, float* out
 extern "C" int ib_gemm_swiglu_tcgen05_2cta(const void* x, const void* w, void* act, int T, int I, int K, unsigned* status, cudaStream_t stream) {
   if (T == 0 || I == 0) return 0;
   return launch<2, EPI_SWIGLU, 128>(x, w, act, T, I, K, 2 * I, I, status, stream);
+}
+
+// The q/k/v projection with its epilogue: x [T, K] bfloat16 and w [(heads + 2 kv_heads) * 128, K] bfloat16 (q rows, k rows, v rows)
+// -> q_out [T, heads * 128] bfloat16 normed and turned, and (write_kv) keys and values of each token at its position
+// in the paged cache; what ib_gemm_tcgen05_2cta followed by ib_qk_norm_rope_kv gives, without the float32 product
+// in memory between them. Head size 128, a bfloat16 cache, the whole head turned (cos_t, sin_t [T, 64]) or none of it.
+extern "C" int ib_gemm_qkv_tcgen05_2cta(const void* x, const void* w, int T, int K, const float* q_norm_w, const float* k_norm_w, float eps,
+                                        const float* cos_t, const float* sin_t, const int* positions, const int* seg_of_token, void* q_out,
+                                        const IbKvView* kv, int write_kv, int heads, unsigned* status, cudaStream_t stream) {
+  if (T == 0) return 0;
+  IB_CHECK_ARG(kv && q_out && positions && seg_of_token, "gemm_qkv_tcgen05_2cta: a null pointer");
+  IB_CHECK_ARG(kv->head_dim == kQkvHead, "gemm_qkv_tcgen05_2cta: head size %d (this form has 128)", kv->head_dim);
+  IB_CHECK_ARG(!write_kv || (kv->base && kv->block_table && kv->dtype == IB_BF16), "gemm_qkv_tcgen05_2cta: the cache must be bfloat16");
+  IB_CHECK_ARG(heads > 0 && kv->kv_heads > 0, "gemm_qkv_tcgen05_2cta: %d heads, %d kv heads", heads, kv->kv_heads);
+  IB_CHECK_ARG((cos_t == nullptr) == (sin_t == nullptr), "gemm_qkv_tcgen05_2cta: one rotation table without the other");
+  IB_CHECK_ARG(((uintptr_t)q_out & 15) == 0 && ((uintptr_t)kv->base & 15) == 0 && ((uintptr_t)cos_t & 15) == 0 && ((uintptr_t)sin_t & 15) == 0,
+               "gemm_qkv_tcgen05_2cta: outputs and tables must be 16-byte aligned");
+  QkvEpi qe = {q_norm_w, k_norm_w, eps, cos_t, sin_t, positions, seg_of_token, (__nv_bfloat16*)q_out, *kv, write_kv, heads};
+  const int N = (heads + 2 * kv->kv_heads) * kQkvHead;
+  // the other way round: the tokens are the rows of the product, the weight's rows its columns
+  return launch<1, EPI_QKV, 256>(w, x, nullptr, N, T, K, T, 0, status, stream, qe);
 }

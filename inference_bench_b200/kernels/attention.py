@@ -98,6 +98,27 @@ def _work_lists(ctx):
     return work
 
 
+def project_qkv(ctx, h: torch.Tensor, lw, q_norm_w, k_norm_w, eps: float, cos, sin, cache: ops.KvLayerView, heads: int, write_kv: bool) -> Optional[torch.Tensor]:
+    """The q/k/v projection of h [T, K] by the fused [q | k | v] matrix with the per-head norms, the rotation and the
+    cache write in the matrix product's epilogue: returns the finished queries [T, heads * hd], or None when that
+    kernel does not take the step (float32, few tokens, a head size other than 128, a rotation over part of the
+    head): the caller then runs the product and `ops.qk_norm_rope_kv`."""
+    rt = ctx.rt
+    if rt.mode != "bfloat16" or rt.gemm == "simt" or h.dtype != torch.bfloat16:
+        return None
+    from . import gemm_tcgen05 as G
+    view = cache.c_view()
+    if view.head_dim != 128 or view.dtype != L.BF16 or not G.supports(lw.k) or lw.n != (heads + 2 * view.kv_heads) * 128:
+        return None
+    if cos is not None and 2 * cos.shape[1] != 128:
+        return None
+    if not G.qkv_in_epilogue(h.shape[0], lw.n, lw.k):
+        return None
+    q = rt.empty((h.shape[0], heads * 128))
+    G.gemm_qkv_pair(h, lw.weight, q, cache, heads, q_norm_w, k_norm_w, eps, cos, sin, ctx.positions, ctx.seg_of_token, write_kv, rt.status)
+    return q
+
+
 def decode_fused(ctx, qkv: torch.Tensor, q_norm_w, k_norm_w, eps: float, cos, sin, cache: ops.KvLayerView, heads: int, window: Optional[int],
                  scale: float, write_kv: bool) -> Optional[torch.Tensor]:
     """Attention for a step of decoded tokens only, straight from the q/k/v projection's partial sums

@@ -7,6 +7,7 @@ sizes of the product (T, N, K), never on which requests make up the batch.
 """
 from __future__ import annotations
 
+import ctypes as C
 import functools
 from typing import Optional
 
@@ -23,6 +24,7 @@ L.register("ib_gemm_swiglu_tcgen05", [L._p, L._p, L._p, L._i, L._i, L._i, L._i, 
 L.register("ib_gemm_tcgen05_2cta", [L._p, L._p, L._p, L._i, L._i, L._i, L._p, L._p])
 L.register("ib_gemm_swiglu_tcgen05_2cta", [L._p, L._p, L._p, L._i, L._i, L._i, L._p, L._p])
 L.register("ib_gemm_tcgen05_2cta_add", [L._p, L._p, L._p, L._i, L._i, L._i, L._p, L._p])
+L.register("ib_gemm_qkv_tcgen05_2cta", [L._p, L._p, L._i, L._i, L._p, L._p, L._f, L._p, L._p, L._p, L._p, L._p, C.POINTER(L.KvView), L._i, L._i, L._p, L._p])
 
 PAIR_MIN_TOKENS = 129    # the fused gate/up product runs on the persistent CTA-pair kernel (csrc/gemm_tcgen05_2cta.cu) from here on
 PAIR_ALWAYS_TOKENS = 2048   # and every product from here on; between the two, `plan` decides by its cost model
@@ -74,14 +76,13 @@ def single_variants(T: int, N: int, K: int):
 
 
 @functools.lru_cache(maxsize=4096)
-def plan(T: int, N: int, K: int) -> tuple:
-    """For 129 <= T < 2048: ("pair",) or ("single", tokens per CTA, k-splits, wide), whichever the cost model
-    expects to be faster. Depends on the sizes only."""
+def plan_costs(T: int, N: int, K: int) -> tuple:
+    """(expected us of the CTA-pair kernel, expected us of the best single-CTA form, that form) for 129 <= T < 2048."""
     m = _MID
     tiles = -(-N // 256) * -(-T // 256)
     active = min(tiles, SM_COUNT // 2) * 2
-    best = (-(-tiles // (SM_COUNT // 2)) * max(256 * 256 * K * 2 / (2 * m["pair_rate"]), 256 * K * 2 / min(m["pair_cap"], m["hbm"] / active)) + m["t0"],
-            ("pair",))
+    pair = -(-tiles // (SM_COUNT // 2)) * max(256 * 256 * K * 2 / (2 * m["pair_rate"]), 256 * K * 2 / min(m["pair_cap"], m["hbm"] / active)) + m["t0"]
+    best = (float("inf"), None)
     ktiles = -(-K // 64)
     for bn, sp, wide in single_variants(T, N, K):
         rows = 256 if wide else 128
@@ -91,8 +92,30 @@ def plan(T: int, N: int, K: int) -> tuple:
         copy = (rows + min(bn, T)) * kc * 2 / min(m["cap"], m["hbm"] / min(ctas, SM_COUNT))
         t = -(-ctas // SM_COUNT) * max(mma, copy) + m["t0"] + (sp * T * N * 4 / m["partial_bw"] if sp > 1 else 0.0)
         if t < best[0]:
-            best = (t, ("single", bn, sp, wide))
-    return best[1]
+            best = (t, (bn, sp, wide))
+    return pair, best[0], best[1]
+
+
+def plan(T: int, N: int, K: int) -> tuple:
+    """For 129 <= T < 2048: ("pair",) or ("single", tokens per CTA, k-splits, wide), whichever the cost model
+    expects to be faster. Depends on the sizes only."""
+    pair, single, form = plan_costs(T, N, K)
+    return ("pair",) if pair <= single else ("single",) + form
+
+
+QKV_EPILOGUE = True   # the q/k/v projection may finish norm, rotation and cache write in its epilogue (CTA-pair kernel, head size 128)
+
+
+def qkv_in_epilogue(T: int, N: int, K: int) -> bool:
+    """Whether the q/k/v projection of T tokens runs as the CTA-pair kernel with the q/k norm, the rotation and the
+    cache write in its epilogue: from 2,048 tokens always; from 129 when that is expected to take no longer than the
+    best plain product followed by the kernel it saves (about 3 us + 20 ns a token inside a step)."""
+    if not QKV_EPILOGUE or T <= 128:
+        return False
+    if T >= PAIR_ALWAYS_TOKENS:
+        return True
+    pair, single, _ = plan_costs(T, N, K)
+    return pair <= single + 3.0 + 0.02 * T
 
 
 def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bn: int, splits: int, status: torch.Tensor, wide: bool = False) -> None:
@@ -115,6 +138,31 @@ def gemm_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch
     ops._check("w", w, torch.bfloat16, (N, K))
     ops._check("out", out, torch.float32, (T, N))
     L.call("ib_gemm_tcgen05_2cta_add" if add else "ib_gemm_tcgen05_2cta", x.data_ptr(), w.data_ptr(), out.data_ptr(), T, N, K, status.data_ptr(), ops._stream())
+
+
+def gemm_qkv_pair(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, kv: "ops.KvLayerView", heads: int, q_norm_w: Optional[torch.Tensor],
+                  k_norm_w: Optional[torch.Tensor], eps: float, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], positions: torch.Tensor,
+                  seg_of_token: torch.Tensor, write_kv: bool, status: torch.Tensor) -> None:
+    """q_out [T, heads * 128] bfloat16 and the paged cache from x [T, K] and w [(heads + 2 kv_heads) * 128, K]: the
+    projection, the per-head norms, the rotation and the cache write in one kernel (csrc/gemm_tcgen05_2cta.cu)."""
+    T, K = x.shape
+    view = kv.c_view()
+    if view.head_dim != 128 or (cos is not None and cos.shape[1] != 64):
+        raise L.KernelError(f"gemm_qkv_pair: head size {view.head_dim} with a rotation over {None if cos is None else 2 * cos.shape[1]} values (128 and 128 or none)")
+    N = (heads + 2 * view.kv_heads) * 128
+    ops._check("x", x, torch.bfloat16)
+    ops._check("w", w, torch.bfloat16, (N, K))
+    ops._check("q_out", q_out, torch.bfloat16, (T, heads * 128))
+    ops._check("positions", positions, torch.int32, (T,))
+    ops._check("seg_of_token", seg_of_token, torch.int32, (T,))
+    for name, v in (("q_norm", q_norm_w), ("k_norm", k_norm_w)):
+        if v is not None:
+            ops._check(name, v, torch.float32, (128,))
+    if cos is not None:
+        ops._check("cos", cos, torch.float32, (T, 64))
+        ops._check("sin", sin, torch.float32, (T, 64))
+    L.call("ib_gemm_qkv_tcgen05_2cta", x.data_ptr(), w.data_ptr(), T, K, ops._ptr(q_norm_w), ops._ptr(k_norm_w), float(eps), ops._ptr(cos), ops._ptr(sin),
+           positions.data_ptr(), seg_of_token.data_ptr(), q_out.data_ptr(), C.byref(view), 1 if write_kv else 0, heads, status.data_ptr(), ops._stream())
 
 
 def linear(rt, x: torch.Tensor, lw, allow_split: bool = True, add_to: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:

@@ -131,9 +131,13 @@ class Attention(base.Mixer):
 
     def forward(self, ctx, h, cache, residual=None):
         rt = ctx.rt
-        qkv = rt.linear(h, self.wqkv)
         cos, sin = self.position.tables(ctx)
         from ..kernels import attention
+        q = attention.project_qkv(ctx, h, self.wqkv, self.q_norm, self.k_norm, self.norm_eps, cos, sin, cache, self.heads, self.own_kv)
+        if q is not None:   # many tokens: norm, rotation and cache write happened in the projection's epilogue
+            out = attention.paged_attention(ctx, q, cache, self.heads, self.window, self.scale)
+            return rt.linear(out, self.wo, add_to=residual)
+        qkv = rt.linear(h, self.wqkv)
         out = attention.decode_fused(ctx, qkv, self.q_norm, self.k_norm, self.norm_eps, cos, sin, cache, self.heads, self.window, self.scale, self.own_kv)
         if out is None:   # not a step of decoded tokens only, or sizes the fused kernel does not have
             q = rt.empty((ctx.n_tokens, self.heads * self.head_dim))

@@ -489,6 +489,69 @@ def test_qk_norm_rope_kv(status, dtype, hd, rot, T):
     assert (pool[0] == 37.0).all()   # the other layer's place in the pages is untouched
 
 
+@pytest.mark.parametrize("T,heads,kvh,K,norms,rope,write_kv", [(300, 3, 1, 200, True, True, True), (130, 4, 2, 264, False, True, True),
+                                                              (513, 2, 2, 1024, True, False, True), (257, 5, 1, 136, True, True, False)])
+def test_gemm_qkv_epilogue_equals_the_two_steps(status, T, heads, kvh, K, norms, rope, write_kv):
+    """The q/k/v projection with norm, rotation and cache write in its epilogue against the plain product followed by
+    `qk_norm_rope_kv`, and against the float64 formulas: two requests at different positions, a number of heads that
+    leaves the last tile half empty, a token count that is no multiple of the tile."""
+    from inference_bench_b200.kernels import gemm_tcgen05 as G, ops
+    hd, page, theta, eps = 128, 16, 1e4, 1e-5
+    N = (heads + 2 * kvh) * hd
+    x = (torch.randn(T, K, generator=_g(51)) * 0.5).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, K, generator=_g(52)) * 0.2).to(torch.bfloat16).to(DEV)
+    qw = (1 + 0.1 * torch.randn(hd, generator=_g(53))).to(DEV) if norms else None
+    kw = (1 + 0.1 * torch.randn(hd, generator=_g(54))).to(DEV) if norms else None
+    n0 = T // 3
+    lens = [(7 + n0, n0), (40 + T - n0, T - n0)]   # (context length after the step, tokens of the step)
+    positions = torch.cat([torch.arange(L_ - n, L_, dtype=torch.int32) for L_, n in lens]).to(DEV)
+    seg = torch.cat([torch.full((n,), i, dtype=torch.int32) for i, (L_, n) in enumerate(lens)]).to(DEV)
+    cos = sin = None
+    if rope:
+        inv = (1.0 / torch.pow(torch.tensor(theta, dtype=torch.float64), torch.arange(0, hd, 2, dtype=torch.float64) / hd)).float().to(DEV)
+        cos, sin = torch.empty(T, hd // 2, device=DEV), torch.empty(T, hd // 2, device=DEV)
+        ops.rope_table(positions, inv, cos, sin)
+    outs = []
+    for fused in (False, True):
+        view, table = _paged([(torch.zeros(L_, kvh, hd), torch.zeros(L_, kvh, hd)) for L_, _ in lens], page, torch.bfloat16, 55)
+        q = torch.full((T, heads * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+        before = view.pool.float().cpu()
+        if fused:
+            G.gemm_qkv_pair(x, w, q, view, heads, qw, kw, eps, cos, sin, positions, seg, write_kv, status)
+        else:
+            qkv = torch.empty(1, T, N, device=DEV)
+            G.gemm_pair(x, w, qkv[0], status)
+            ops.qk_norm_rope_kv(qkv, qw, kw, eps, cos, sin, positions, seg, q, view, heads, status, write_kv=write_kv)
+        assert status.item() == 0
+        outs.append((q.float().cpu(), view.pool.float().cpu(), table))
+    (q_a, pool_a, table), (q_b, pool_b, _) = outs
+    # the two ways differ by the order of a float32 sum at most: a bfloat16 value may round the other way
+    assert (q_a - q_b).abs().max() <= 2.0 ** -7 * q_a.abs().max()
+    assert (pool_a - pool_b).abs().max() <= 2.0 ** -7 * max(pool_a[1].abs().max(), 1.0)
+    assert (pool_b[0] == 37.0).all()
+    if not write_kv:
+        assert torch.equal(pool_a, before) and torch.equal(pool_b, before)
+    # and against the formulas in float64
+    s_ = x.cpu().double() @ w.cpu().double().T
+    qr = s_[:, :heads * hd].reshape(T, heads, hd)
+    kr = s_[:, heads * hd:(heads + kvh) * hd].reshape(T, kvh, hd)
+    vr = s_[:, (heads + kvh) * hd:].reshape(T, kvh, hd)
+    if norms:
+        qr, kr = P.rmsnorm(qr, qw.cpu().double(), eps), P.rmsnorm(kr, kw.cpu().double(), eps)
+    if rope:
+        c, sn = cos.cpu().double()[:, None, :], sin.cpu().double()[:, None, :]
+        turn = lambda z: torch.cat([z[..., :hd // 2] * c - z[..., hd // 2:] * sn, z[..., hd // 2:] * c + z[..., :hd // 2] * sn], -1)
+        qr, kr = turn(qr), turn(kr)
+    assert (q_b.double().reshape(T, heads, hd) - qr).abs().max() <= 2.0 ** -7 * qr.abs().max()
+    if write_kv:
+        pos = positions.cpu().tolist()
+        sg = seg.cpu().tolist()
+        for t in range(0, T, 7):
+            pg = table[sg[t], pos[t] // page]
+            assert (pool_b[1, pg, 0, :, pos[t] % page].double() - kr[t]).abs().max() <= 2.0 ** -7 * kr.abs().max()
+            assert (pool_b[1, pg, 1, :, pos[t] % page].double() - vr[t]).abs().max() <= 2.0 ** -7 * vr.abs().max()
+
+
 # ------------------------------------------------------------------------------------------ sampling
 def test_sample_rows_matches_plain():
     from inference_bench_b200.kernels import ops

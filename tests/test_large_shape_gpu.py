@@ -47,7 +47,35 @@ def test_bfloat16_against_float32_at_large_layer_sizes(shape, page):
     print(f"{shape} layer sizes, 2 layers: bfloat16 vs float32 worst {err:.3e} of max|logit|")
 
 
-@pytest.mark.parametrize("shape,page,tokens", [("8b", 16, 257), ("32b", 16, 257), ("14b", 64, 321)])
+@pytest.mark.parametrize("shape,page", [("8b", 64), ("32b", 16)])
+def test_a_long_portion_in_bfloat16_against_float32(shape, page):
+    """A portion of 2,100 tokens (the q/k/v projection then finishes norm, rotation and cache write in its epilogue,
+    and every matrix product runs on CTA pairs), a second portion and a decoded token that read what it cached."""
+    from inference_bench_b200 import Engine
+    from inference_bench_b200.engine.step import StepEntry
+    from inference_bench_b200.kernels import gemm_tcgen05 as G
+    cfg = SHAPES[shape]
+    assert G.qkv_in_epilogue(2100, (cfg["num_attention_heads"] + 2 * cfg["num_key_value_heads"]) * 128, cfg["hidden_size"])
+    prompt = np.random.default_rng(2).integers(0, 151936, 2300).tolist()
+    logits = {}
+    for dtype in ("float32", "bfloat16"):
+        eng = Engine(cfg, dtype=dtype, max_ctx=2560, page_size=page, num_pages=2560 // page + 4, max_num_seqs=2, random_weights_seed=0)
+        eng.cache.admit("r")
+        rows = [eng.runner.step([StepEntry("r", prompt[:2100], [0, 1000, 2099])]).cpu()]
+        rows.append(eng.runner.step([StepEntry("r", prompt[2100:2299], [198])]).cpu())
+        rows.append(eng.runner.step([StepEntry("r", prompt[2299:], [0])]).cpu())
+        logits[dtype] = torch.cat(rows)
+        eng.cache.release("r")
+        del eng
+        torch.cuda.empty_cache()
+    ref, got = logits["float32"], logits["bfloat16"]
+    assert torch.isfinite(got).all()
+    err = (got - ref).abs().max().item() / ref.abs().max().item()
+    assert err <= 3e-2, f"bfloat16 differs from float32 by {err:.3e} of max|logit|"
+    print(f"{shape} layer sizes, 2 layers, 2,100-token portion: bfloat16 vs float32 worst {err:.3e} of max|logit|")
+
+
+@pytest.mark.parametrize("shape,page,tokens", [("8b", 16, 257), ("32b", 16, 257), ("14b", 64, 321), ("8b", 64, 2100)])
 def test_a_prompt_portion_gives_the_same_bits_every_time(shape, page, tokens):
     """Kernels that start while the kernel before them is still running (programmatic dependent launch) must give
     what one kernel after the other gives, run after run: with every query tile released at the same moment, copies
@@ -58,7 +86,8 @@ def test_a_prompt_portion_gives_the_same_bits_every_time(shape, page, tokens):
     from inference_bench_b200.kernels import lib as L
     lib = L.load()
     prompt = np.random.default_rng(1).integers(0, 151936, tokens).tolist()
-    eng = Engine(SHAPES[shape], dtype="bfloat16", max_ctx=512, page_size=page, num_pages=64, max_num_seqs=2, random_weights_seed=0)
+    eng = Engine(SHAPES[shape], dtype="bfloat16", max_ctx=max(512, tokens + 64), page_size=page, num_pages=max(64, tokens // page + 4), max_num_seqs=2,
+                 random_weights_seed=0)
 
     def once():
         eng.cache.admit("r")
