@@ -254,6 +254,8 @@ def make_engine(cfg: dict, page: int, big: int):
 
 
 def run_ours(args) -> dict:
+    import gc
+
     import torch
     pk, pk_src = peaks()
     cfg = dict(SHAPES[args.shape])
@@ -283,6 +285,7 @@ def run_ours(args) -> dict:
     extra = {}
     if page != PAGE_ENGINE:   # the same measurements at the engine's default page size
         del engine
+        gc.collect()   # the engine's parts refer to one another: without this its weights outlive the name
         torch.cuda.empty_cache()
         engine = make_engine(cfg, PAGE_ENGINE, big)
         tag = f"_page{PAGE_ENGINE}"
