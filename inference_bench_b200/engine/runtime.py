@@ -97,7 +97,7 @@ class Runtime:
         T, inter = x.shape[0], lw.n // 2
         if self.mode == "bfloat16" and self.gemm != "simt":
             from ..kernels import gemm_tcgen05
-            if gemm_tcgen05.swiglu_supported(T, lw.k):
+            if gemm_tcgen05.swiglu_supported(T, lw.k, inter):
                 act = self.empty((T, inter))
                 gemm_tcgen05.gemm_swiglu(x, lw.weight, act, self.status)
                 return act

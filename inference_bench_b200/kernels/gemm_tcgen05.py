@@ -26,7 +26,7 @@ L.register("ib_gemm_swiglu_tcgen05_2cta", [L._p, L._p, L._p, L._i, L._i, L._i, L
 L.register("ib_gemm_tcgen05_2cta_add", [L._p, L._p, L._p, L._i, L._i, L._i, L._p, L._p])
 L.register("ib_gemm_qkv_tcgen05_2cta", [L._p, L._p, L._i, L._i, L._p, L._p, L._f, L._p, L._p, L._p, L._p, L._p, C.POINTER(L.KvView), L._i, L._i, L._p, L._p])
 
-PAIR_MIN_TOKENS = 129    # the fused gate/up product runs on the persistent CTA-pair kernel (csrc/gemm_tcgen05_2cta.cu) from here on
+PAIR_MIN_TOKENS = 129    # the fused gate/up product runs on the persistent CTA-pair kernel (csrc/gemm_tcgen05_2cta.cu) from here on whatever its size
 PAIR_ALWAYS_TOKENS = 2048   # and every product from here on; between the two, `plan` decides by its cost model
 
 
@@ -186,10 +186,15 @@ def linear(rt, x: torch.Tensor, lw, allow_split: bool = True, add_to: Optional[t
     return out
 
 
-def swiglu_supported(T: int, k: int) -> bool:
-    """The fused gate/up product takes token tiles of 64 and more; fewer tokens go through the
-    split-K product and the SiLU-mul kernel, which fill the GPU better."""
-    return supports(k) and T > 64
+PAIR_SWIGLU_MIN_TILES = 40   # 256-column blocks of the intermediate size from which the CTA-pair kernel takes the fused gate/up product of 33 to 128 tokens
+
+
+def swiglu_supported(T: int, k: int, inter: int = 0) -> bool:
+    """Whether the gate/up product applies the activation in its epilogue: from 65 tokens always; from 33 where the
+    intermediate size gives the CTA-pair kernel 40 tiles or more (measured 8 to 10 % faster there than the split-K
+    product followed by the SiLU-mul kernel, at the 8B, 14B and 32B shapes; slower at the 0.6B shape). Fewer tokens go
+    through the split-K product and the SiLU-mul kernel, which fill the GPU better."""
+    return supports(k) and (T > 64 or (T > 32 and -(-inter // 256) >= PAIR_SWIGLU_MIN_TILES))
 
 
 def gemm_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tensor, status: torch.Tensor, bn: int | None = None) -> None:
@@ -199,7 +204,7 @@ def gemm_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tensor, sta
     ops._check("x", x, torch.bfloat16)
     ops._check("w_gate_up", w_gate_up, torch.bfloat16, (2 * I, K))
     ops._check("act", act, torch.bfloat16, (T, I))
-    if bn is None and T >= PAIR_MIN_TOKENS:
+    if bn is None and (T >= PAIR_MIN_TOKENS or (T > 32 and -(-I // 256) >= PAIR_SWIGLU_MIN_TILES)):
         L.call("ib_gemm_swiglu_tcgen05_2cta", x.data_ptr(), w_gate_up.data_ptr(), act.data_ptr(), T, I, K, status.data_ptr(), ops._stream())
         return
     if bn is None:

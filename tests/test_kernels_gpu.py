@@ -132,9 +132,12 @@ def test_gemm_tcgen05_cta_pairs(status, T, N, K):
     assert status.item() == 0 and torch.equal(acc, base + out)
 
 
-@pytest.mark.parametrize("T,I,K", [(256, 128, 64), (300, 520, 264), (1000, 1000, 1024), (2048, 20000, 128)])
+@pytest.mark.parametrize("T,I,K", [(256, 128, 64), (300, 520, 264), (1000, 1000, 1024), (2048, 20000, 128), (33, 10240, 136), (64, 12288, 200),
+                                   (100, 10300, 72)])
 def test_gemm_swiglu_cta_pairs(status, T, I, K):
+    """The fused gate/up product on CTA pairs: from 129 tokens, and from 33 when the intermediate size gives 40 tiles."""
     from inference_bench_b200.kernels import gemm_tcgen05 as G
+    assert T >= G.PAIR_MIN_TOKENS or (T > 32 and -(-I // 256) >= G.PAIR_SWIGLU_MIN_TILES)
     x = (torch.randn(T, K, generator=_g(5)) * 0.5).to(torch.bfloat16).to(DEV)
     w = (torch.randn(2 * I, K, generator=_g(6)) * 0.2).to(torch.bfloat16).to(DEV)
     act = torch.full((T, I), float("nan"), dtype=torch.bfloat16, device=DEV)
