@@ -114,8 +114,9 @@ def _prompt(seed: int, n: int, vocab: int) -> list[int]:
     return np.random.default_rng(seed).integers(0, vocab, size=n).tolist()
 
 
-def measure_prefill(engine, steps: int, warmup: int) -> float:
-    """Milliseconds for one step that prefills a PROMPT-token prompt and returns its last logits."""
+def measure_prefill(engine, steps: int, warmup: int, after: int = 0) -> float:
+    """Milliseconds for one step that prefills a PROMPT-token prompt portion and returns its last logits; with
+    `after`, the portion follows that many tokens of the same request already in the cache (not timed)."""
     import torch
     from inference_bench_b200.engine.step import StepEntry
     vocab = engine.decoder.plan.vocab_size
@@ -124,6 +125,8 @@ def measure_prefill(engine, steps: int, warmup: int) -> float:
         rid = ("prefill", i)
         toks = _prompt(1000 + i, PROMPT, vocab)
         engine.cache.admit(rid)
+        for a in range(0, after, PROMPT):
+            engine.runner.step([StepEntry(rid, _prompt(2000 + i + a, min(PROMPT, after - a), vocab), [])], check=False)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
         e0.record()
@@ -247,9 +250,9 @@ def measure_decode_e2e(engine, batch: int, steps: int, warmup: int) -> tuple[flo
     return (t1 - t0) * 1e3 / steps, h2d, d2h
 
 
-def make_engine(cfg: dict, page: int, big: int):
+def make_engine(cfg: dict, page: int, big: int, ctx: int = CONTEXT):
     from inference_bench_b200 import Engine
-    return Engine(cfg, dtype="bfloat16", max_ctx=CONTEXT, page_size=page, num_pages=big * (CONTEXT // page) + 64, max_num_seqs=big,
+    return Engine(cfg, dtype="bfloat16", max_ctx=ctx, page_size=page, num_pages=big * (ctx // page) + 64, max_num_seqs=big,
                   max_batched_tokens=8192, prefill_chunk=PROMPT, random_weights_seed=0)
 
 
@@ -263,6 +266,9 @@ def run_ours(args) -> dict:
     cfg["num_hidden_layers"] = layers = args.layers or full_layers
     big = max(args.batch, 64)
     page = args.page_size
+    if args.only == "prefill" and args.prefill_after:   # a portion deep in a long context: a cache for one such request
+        engine = make_engine(cfg, page, 1, args.prefill_after + PROMPT)
+        return {"only": "prefill", "layers": layers, "after": args.prefill_after, "ms": measure_prefill(engine, args.steps, 1, args.prefill_after)}
     engine = make_engine(cfg, page, big)
     steps, warmup = args.steps, max(args.warmup, 3)
     if args.only == "prefill":   # one part alone, for profiling: a short report, not the benchmark line
@@ -327,6 +333,7 @@ def main() -> int:
     ap.add_argument("--page-size", type=int, default=PAGE, help="keys per cache page (the benchmark configuration names 16)")
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (both numbers are reported)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--prefill-after", type=int, default=0, help="with --only prefill: the 2,048-token portion follows this many cached tokens of the same request")
     ap.add_argument("--only", default="", choices=["", "prefill", "decode", "mixed"], help="run one part alone (for profiling); prints a short report")
     args = ap.parse_args()
     if args.impl == "reference":
