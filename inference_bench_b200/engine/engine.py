@@ -41,12 +41,14 @@ class Reply:
 class Engine:
     def __init__(self, model: Union[str, Path, Mapping[str, Any]], dtype: str = "bfloat16", max_ctx: Optional[int] = None,
                  page_size: int = 64, num_pages: Optional[int] = None, kv_gb: Optional[float] = None, max_num_seqs: int = 64,
-                 max_batched_tokens: int = 8192, prefill_chunk: int = 2048, random_weights_seed: Optional[int] = None,
+                 max_batched_tokens: int = 8192, prefill_chunk: Union[int, str] = 2048, random_weights_seed: Optional[int] = None,
                  device: str = "cuda:0", use_graphs: bool = True, pipeline: bool = True):
         """model: a folder with config.json and model.safetensors, or (with random_weights_seed) a raw
         config.json mapping whose weights are then made on the device. num_pages / kv_gb size the
         cache pool; by default it holds max_num_seqs requests of max_ctx tokens, capped by free memory.
-        pipeline: keep decode steps one ahead of the host (see engine/scheduler.py)."""
+        pipeline: keep decode steps one ahead of the host (see engine/scheduler.py). prefill_chunk: the longest
+        portion of one prompt in a step (crates/specrt/src/runtime.rs:801), or "auto" for the size near 2,048 whose
+        matrix-product tiles fill whole rounds of the GPU best at this model's layer sizes."""
         self.rt = Runtime(device, dtype)
         if isinstance(model, Mapping):
             if random_weights_seed is None:
@@ -69,11 +71,28 @@ class Engine:
             num_pages = max(1, min(want, room))
         self.cache = CacheManager(needs, page_size, num_pages, max_num_seqs, self.max_ctx, device=self.rt.device, dtype=self.rt.act_dtype,
                                   sources=self.decoder.cache_sources())
+        if prefill_chunk == "auto":
+            prefill_chunk = self._balanced_portion()
         self.runner = ModelRunner(self.decoder, self.cache, self.rt)
         self.executor = GpuExecutor(self.runner, use_graphs=use_graphs)
         self.scheduler = Scheduler(self.cache, SchedulerConfig(max_num_seqs, max_batched_tokens, prefill_chunk, self.max_ctx, pipeline))
         self._tokenizer = None
         self._next_id = 0
+
+    def _balanced_portion(self) -> int:
+        """The portion size for prefill_chunk="auto": from the matrices of the blocks' parts (bfloat16 mode; 2,048 otherwise)."""
+        from ..kernels import gemm_tcgen05
+        from .runtime import LinearWeights
+        if self.rt.mode != "bfloat16":
+            return 2048
+        seen, matrices = set(), []
+        for block in self.decoder.blocks:
+            for part in block.parts():
+                for v in vars(part).values():
+                    if isinstance(v, LinearWeights) and id(v) not in seen:
+                        seen.add(id(v))
+                        matrices.append((v.n, v.k))
+        return gemm_tcgen05.balanced_portion(matrices) if matrices else 2048
 
     @classmethod
     def load(cls, model, max_ctx: Optional[int] = None, **kw) -> "Engine":

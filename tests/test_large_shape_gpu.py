@@ -147,3 +147,19 @@ def test_mixed_steps_give_the_same_bits_every_time():
         got = replay()
         diff = [j for j, (a, b) in enumerate(zip(ref, got)) if not torch.equal(a, b)]
         assert not diff, f"replay {i}: the logits of steps {diff} of {len(steps)} differ from the run with one kernel after the other"
+
+
+def test_portion_size_chosen_for_the_layer_sizes():
+    """prefill_chunk="auto" at the 14B layer sizes: portions of 1,792 tokens, and a prompt cut that way gives the tokens of
+    the same prompt cut at 2,048 (greedy, a few tokens: the two ways differ by rounding only)."""
+    from inference_bench_b200 import Engine
+    prompt = np.random.default_rng(4).integers(0, 151936, 2500).tolist()
+    got = {}
+    for chunk in ("auto", 2048):
+        eng = Engine(SHAPES["14b"], dtype="bfloat16", max_ctx=3072, page_size=64, max_num_seqs=2, prefill_chunk=chunk, random_weights_seed=0)
+        if chunk == "auto":
+            assert eng.scheduler.cfg.prefill_chunk == 1792
+        got[chunk] = eng.generate(prompt, max_tokens=4).tokens
+        del eng
+        torch.cuda.empty_cache()
+    assert len(got["auto"]) == 4 and got["auto"][0] == got[2048][0]

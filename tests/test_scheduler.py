@@ -389,3 +389,18 @@ def test_random_traffic_gives_every_request_its_own_tokens(executor, seed):
             assert done[rid].tokens == want, f"request {rid}"
             assert done[rid].finish == ("stop" if len(want) < k else "length")
     assert cache.used_pages() == [0] and cache.free_slots() == cache.max_requests
+
+
+def test_balanced_portion_fills_whole_rounds_of_tiles():
+    """The optional portion size (`Engine(prefill_chunk="auto")`): near 2,048, a multiple of 256, and the one whose
+    256 x 256 tiles leave the last round of the 74 CTA pairs fullest (the sizes measured fastest at these shapes)."""
+    from inference_bench_b200.kernels import gemm_tcgen05 as G
+    shapes = {"8b": [(6144, 4096), (4096, 4096), (24576, 4096), (4096, 12288)], "14b": [(7168, 5120), (5120, 5120), (34816, 5120), (5120, 17408)],
+              "32b": [(10240, 5120), (5120, 8192), (51200, 5120), (5120, 25600)]}
+    assert {k: G.balanced_portion(v) for k, v in shapes.items()} == {"8b": 2304, "14b": 1792, "32b": 1792}
+    for m in shapes.values():
+        for nominal in (1024, 2048, 4096):
+            T = G.balanced_portion(m, nominal)
+            assert T % 256 == 0 and nominal * 3 // 4 <= T <= nominal * 5 // 4
+    assert G.balanced_portion([], 2048) == 2048          # nothing to balance: the nominal size
+    assert G.balanced_portion([(256, 64)], 2048) == 2560  # one round whatever the size: the most tokens a round
