@@ -4,7 +4,7 @@
     python -m inference_bench_b200 run        --model DIR [--prompt TEXT | --prompt-file F | --prompt-len N] [--max-tokens 64] [--json] [--max-ctx N]
     python -m inference_bench_b200 batch      --model DIR [--prompt-len 128] [--max-tokens 128] [--sizes 1,4,16] [--json]
     python -m inference_bench_b200 logit-diff --model DIR --reference NAME.ref.json [--quantised]
-    python -m inference_bench_b200 spec       --model DIR
+    python -m inference_bench_b200 spec       --model DIR|SPEC.toml
     python -m inference_bench_b200 random-model --config CONFIG.json --seed N --out DIR
 
 Added here: --temperature, --seed, --top-k, --top-p, --min-p, --dtype bfloat16|float32, and the random-model command.
@@ -43,9 +43,31 @@ def _read_prompt(args, engine) -> list[int]:
     return _synthetic_prompt(args.prompt_len or 128, vocab)
 
 
+def _runtime_overrides(args) -> dict:
+    """--runtime name=value pairs, typed like a TOML value (true/false, integers, numbers, strings)."""
+    out = {}
+    for item in getattr(args, "runtime", None) or []:
+        name, eq, text = item.partition("=")
+        if not eq:
+            raise SystemExit(f"--runtime takes name=value, got {item!r}")
+        low = text.strip().lower()
+        if low in ("true", "false"):
+            value = low == "true"
+        else:
+            try:
+                value = int(text)
+            except ValueError:
+                try:
+                    value = float(text)
+                except ValueError:
+                    value = text.strip().strip('"')
+        out[name.strip()] = value
+    return out
+
+
 def _engine(args, **kw):
     from .engine.engine import Engine
-    return Engine(args.model, dtype=args.dtype, max_ctx=args.max_ctx, **kw)
+    return Engine(args.model, dtype=args.dtype, max_ctx=args.max_ctx, options=_runtime_overrides(args) or None, **kw)
 
 
 def _sampling(args):
@@ -129,12 +151,28 @@ def cmd_logit_diff(args) -> int:
 
 
 def cmd_spec(args) -> int:
-    from .config.qwen3 import read_config_json
+    """The typed configuration the model resolves to, what the plan derives from it and the runtime options it would
+    run with. Works for every registered architecture: derived sizes are whatever integer properties its
+    configuration class offers."""
+    from .config.spec import resolve_model
     from .engine.model import plan_from_config
-    cfg, plan = plan_from_config(read_config_json(args.model))
-    out = cfg.to_dict()
-    out["derived"] = {"q_dim": cfg.q_dim, "kv_dim": cfg.kv_dim, "qkv_rows": cfg.qkv_rows, "layers": len(plan.layers),
-                      "schedule": [e.layer for e in plan.schedule]}
+    from .registry import resolve
+    spec = resolve_model(args.model)
+    cfg, plan = plan_from_config(spec.raw_config)
+    out = resolve(spec.raw_config).config_to_dict(cfg)
+    derived = {}
+    for name in dir(type(cfg)):
+        if isinstance(getattr(type(cfg), name, None), property):
+            value = getattr(cfg, name)
+            if isinstance(value, (int, float, str, bool)):
+                derived[name] = value
+    derived.update(layers=len(plan.layers), schedule=[e.layer for e in plan.schedule],
+                   cache_of=[e.cache_of for e in plan.schedule] if any(e.cache_of is not None for e in plan.schedule) else None)
+    out["derived"] = {k: v for k, v in derived.items() if v is not None}
+    out["name"] = spec.name
+    out["weights"] = str(spec.model_dir) if spec.model_dir else None
+    out["tensors"] = dict(spec.tensors)
+    out["runtime"] = spec.runtime.merged(_runtime_overrides(args), "--runtime").to_dict()
     print(json.dumps(out, indent=2))
     return 0
 
@@ -151,9 +189,10 @@ def main(argv=None) -> int:
     sub = ap.add_subparsers(dest="cmd", required=True)
 
     def common(p, prompt=True):
-        p.add_argument("--model", required=True, help="folder with config.json and model.safetensors")
+        p.add_argument("--model", required=True, help="folder with config.json and model.safetensors, a hub id in the hub cache, or a TOML model spec")
+        p.add_argument("--runtime", action="append", metavar="NAME=VALUE", help="a runtime option laid over the model spec's [runtime] table (may be repeated)")
         p.add_argument("--max-ctx", type=int, default=None, help="context limit (default 2048, capped by max_position_embeddings)")
-        p.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+        p.add_argument("--dtype", default=None, choices=["bfloat16", "float32"], help="default: the model spec's [runtime] dtype, else bfloat16")
         if prompt:
             p.add_argument("--max-tokens", type=int, default=64)
             p.add_argument("--temperature", type=float, default=0.0)
@@ -184,8 +223,9 @@ def main(argv=None) -> int:
     p.add_argument("--quantised", action="store_true")
     p.set_defaults(fn=cmd_logit_diff)
 
-    p = sub.add_parser("spec", help="print the typed configuration of a model folder")
+    p = sub.add_parser("spec", help="print the typed configuration and runtime options of a model folder or model spec")
     p.add_argument("--model", required=True)
+    p.add_argument("--runtime", action="append", metavar="NAME=VALUE")
     p.set_defaults(fn=cmd_spec)
 
     p = sub.add_parser("random-model", help="write a model folder with random weights")

@@ -7,9 +7,7 @@ config.json, and a missing required key is an error that names the key.
 """
 from __future__ import annotations
 
-import json
 from dataclasses import asdict, dataclass, field
-from pathlib import Path
 from typing import Any, Mapping, Optional
 
 from . import ConfigError
@@ -91,6 +89,14 @@ class Qwen3Config:
             raise ConfigError("attention_bias=true is not supported: Qwen3 dense has no attention bias")
         types = c.get("layer_types")
         window = c.get("sliding_window")
+        if types is None and c.get("use_sliding_window") and window:
+            # A config that turns windows on without naming the layers: the layers from max_window_layers on are
+            # windowed. (The reference reads such a config as full attention everywhere, crates/specrt/src/spec.rs:1678;
+            # this engine has windows, so that would be wrong logits without a word.)
+            first = c.get("max_window_layers")
+            if first is None:
+                raise ConfigError("use_sliding_window is true but config.json has neither layer_types nor max_window_layers")
+            types = ["sliding_attention" if i >= int(first) else "full_attention" for i in range(layers)]
         if types is None:
             types = ["full_attention"] * layers
         types = tuple(str(t) for t in types)
@@ -153,13 +159,3 @@ class Qwen3Config:
         d["use_sliding_window"] = self.sliding_window is not None
         d["rope_scaling"] = None
         return d
-
-
-def read_config_json(model_dir) -> dict[str, Any]:
-    path = Path(model_dir) / "config.json"
-    if not path.is_file():
-        raise ConfigError(f"{path} does not exist")
-    try:
-        return json.loads(path.read_text())
-    except json.JSONDecodeError as e:
-        raise ConfigError(f"{path} is not valid JSON: {e}") from e

@@ -45,16 +45,14 @@ __global__ void __launch_bounds__(kWarps * 32)
     decode_split_kernel(const __nv_bfloat16* __restrict__ q, IbKvView kv, const int* __restrict__ dec_tokens,
                         const int* __restrict__ positions, const int* __restrict__ seg_of_token, int window, float scale_log2e,
                         float* __restrict__ part_o, float* __restrict__ part_ml, int heads, int max_slices, int tiles_per_slice,
-                        const __grid_constant__ CUtensorMap kv_map, long long view_row0, int use_tma, unsigned* __restrict__ status) {
+                        unsigned* __restrict__ status) {
   constexpr int CPR = HD / 8;              // 16-byte chunks per row
   constexpr int TILE = kTile * HD * 2;     // bytes of one K (or V) tile
-  // no static shared memory in this kernel: the tiles must start 1024-byte aligned for TMA's swizzle
   extern __shared__ __align__(1024) uint8_t smem[];
   // layout: Q tile [16][HD] | 2 stages x (K tile, V tile) | key offsets [2][kTile]; the merge buffers reuse the tiles
   const uint32_t q_s = mt::smem_u32(smem);
   const uint32_t kv_s = q_s + 16 * HD * 2;
   long long* offs = (long long*)(smem + 16 * HD * 2 + 4 * TILE);
-  uint64_t* full = (uint64_t*)(offs + 2 * kTile);   // [2], one per stage, for tiles that TMA brings
 
   // What the kernel before this one in the stream writes is q and the key and value of each token's
   // own position; the index arrays, the block table and every older key and value were complete
@@ -62,7 +60,6 @@ __global__ void __launch_bounds__(kWarps * 32)
   // wait (it then travels while the kernel before still runs); q and the row of the token's own
   // position are fetched after it.
   ib::pdl_launch_dependents();
-  if (use_tma) ib::pdl_wait();
   const int kvh = blockIdx.x, item = blockIdx.y, slice = blockIdx.z;
   const int t = dec_tokens[item];
   const int pos = positions[t], seg = seg_of_token[t];
@@ -75,64 +72,10 @@ __global__ void __launch_bounds__(kWarps * 32)
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, tq = lane & 3;
   const __nv_bfloat16* base = (const __nv_bfloat16*)kv.base;
-  if (use_tma) {
-    if (tid == 0) {
-      sm100::mbar_init(&full[0], 1);
-      sm100::mbar_init(&full[1], 1);
-      sm100::fence_barrier_init();
-    }
-    __syncthreads();
-  }
 
-  // With TMA (page sizes that divide the tile): one thread sends one box copy per page, plane and
-  // 64-dim block; the cache, seen as a matrix of [all rows, head_dim], is described by kv_map. Pages
-  // that hold no needed key, or that the table does not have, are cleared instead.
-  auto load_tile_tma = [&](int tile, int stage) {
-    const int ps = kv.page_size, pages = kTile / ps;
-    const long long rows_per_page = kv.page_stride / HD, v_rows = kv.v_offset / HD;
-    const uint32_t k_s = kv_s + stage * 2 * TILE, v_s = k_s + TILE;
-    uint32_t bytes = 0;
-    for (int pg = 0; pg < pages; pg++) {
-      const int key0 = tile * kTile + pg * ps;
-      const bool needed = key0 < k_end && key0 + ps > k_begin;
-      const int page = needed ? kv.block_table[(size_t)seg * kv.table_stride + tile * pages + pg] : -1;
-      const bool valid = page >= 0 && page < kv.num_pages;
-      if (needed && !valid && tid == 0) atomicOr(status, IB_ERR_BAD_PAGE);
-      if (valid) {
-        bytes += 2 * ps * HD * 2;
-      } else {
-        for (int idx = tid; idx < ps * CPR; idx += kWarps * 32) {
-          const int row = pg * ps + idx / CPR, c = idx % CPR;
-          mt::st_shared_zero16(k_s + mt::tile_offset<HD, kTile>(row, c));
-          mt::st_shared_zero16(v_s + mt::tile_offset<HD, kTile>(row, c));
-        }
-      }
-    }
-    if (tid == 0) {
-      sm100::mbar_arrive_expect_tx(&full[stage], bytes);
-      for (int pg = 0; pg < pages; pg++) {
-        const int key0 = tile * kTile + pg * ps;
-        if (!(key0 < k_end && key0 + ps > k_begin)) continue;
-        const int page = kv.block_table[(size_t)seg * kv.table_stride + tile * pages + pg];
-        if (page < 0 || page >= kv.num_pages) continue;
-        const long long row = (long long)page * rows_per_page + view_row0 + (long long)kvh * ps;
-#pragma unroll
-        for (int hb = 0; hb < HD / 64; hb++) {
-          uint8_t* dk = smem + 16 * HD * 2 + stage * 2 * TILE + hb * kTile * 128 + pg * ps * 128;
-          sm100::tma_load_2d(dk, &kv_map, hb * 64, (int)row, &full[stage]);
-          sm100::tma_load_2d(dk + TILE, &kv_map, hb * 64, (int)(row + v_rows), &full[stage]);
-        }
-      }
-    }
-  };
-
-  // Without: one thread per key looks its page up; then all threads copy 16-byte chunks.
+  // One thread per key looks its page up; then all threads copy 16-byte chunks.
   // `own_later`: leave out the row of the token's own position (it is not written yet); it is fetched after the wait.
   auto load_tile = [&](int tile, int stage, bool own_later = false) {
-    if (use_tma) {
-      load_tile_tma(tile, stage);
-      return;
-    }
     long long* o = offs + stage * kTile;
     if (tid < kTile) {
       int key = tile * kTile + tid;
@@ -159,8 +102,8 @@ __global__ void __launch_bounds__(kWarps * 32)
 
   // ---- the first tile of older keys, then (after the dependency wait) Q and the token's own row
   load_tile(tile_begin, 0, true);
-  if (!use_tma) ib::pdl_wait();
-  if (!use_tma && pos / kTile == tile_begin && pos >= k_begin && pos < k_end) {
+  ib::pdl_wait();
+  if (pos / kTile == tile_begin && pos >= k_begin && pos < k_end) {
     const long long off = offs[pos % kTile];
     const int row = pos % kTile;
     for (int c = tid; c < CPR; c += kWarps * 32) {
@@ -203,9 +146,6 @@ __global__ void __launch_bounds__(kWarps * 32)
       mt::cp_async_wait<1>();
     } else {
       mt::cp_async_wait<0>();
-    }
-    if (use_tma && !sm100::mbar_wait(&full[stage], ((tile - tile_begin) >> 1) & 1)) {
-      if (lane == 0) atomicOr(status, IB_ERR_WAIT_TIMEOUT);   // the tile never came: its keys count as garbage, the status says so
     }
     __syncthreads();
     // S = Q K^T for this warp's keys of the tile
@@ -329,7 +269,7 @@ template <int HD>
 __global__ void __launch_bounds__(kCombineThreads)
     decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, const int* __restrict__ dec_tokens,
                           const int* __restrict__ positions, int window, __nv_bfloat16* __restrict__ out, int heads, int max_slices,
-                          int tiles_per_slice) {
+                          int tiles_per_slice, unsigned* __restrict__ status) {
   constexpr int DQ = HD / 4;
   constexpr int SG = kCombineThreads / DQ;
   __shared__ float4 o_red[SG][DQ];
@@ -340,7 +280,12 @@ __global__ void __launch_bounds__(kCombineThreads)
   const int pos = positions[t];
   int lo, tile_lo, tps;
   slice_plan(pos, window, max_slices, tiles_per_slice, lo, tile_lo, tps);
-  const int s_begin = (lo / kTile - tile_lo) / tps, s_end = (pos / kTile - tile_lo) / tps + 1;
+  const int s_begin = (lo / kTile - tile_lo) / tps;
+  int s_end = (pos / kTile - tile_lo) / tps + 1;
+  if (s_end > max_slices) {   // the caller's max_slices does not cover this position: nothing beyond the scratch is read, and the status says so
+    if (threadIdx.x == 0) atomicOr(status, IB_ERR_INTERNAL);
+    s_end = max_slices;
+  }
   const size_t slot0 = ((size_t)item * heads + h) * max_slices;
   const int sg = threadIdx.x / DQ, dq = threadIdx.x % DQ;
   ib::pdl_wait();
@@ -871,17 +816,16 @@ int launch_stream(const void* q, const RawQkv* raw, const IbKvView* kv, const in
              *kv_map, view_row0, status);
   IB_CHECK_LAUNCH("attention_decode_stream split");
   ib::launch(decode_combine_kernel<HD>, dim3(heads, n_dec), kCombineThreads, 0, stream, part_o, part_ml, dec_tokens, positions, window, (__nv_bfloat16*)out, heads,
-             max_slices, tiles_per_slice);
+             max_slices, tiles_per_slice, status);
   IB_CHECK_LAUNCH("attention_decode_stream combine");
   return 0;
 }
 
 template <int HD>
 int launch(const void* q, const IbKvView* kv, const int* dec_tokens, int n_dec, const int* positions, const int* seg_of_token, int window,
-           float scale, float* part_o, float* part_ml, void* out, int heads, int max_slices, int tiles_per_slice, const CUtensorMap* kv_map,
-           long long view_row0, unsigned* status, cudaStream_t stream) {
-  constexpr int smem = 16 * HD * 2 + 4 * kTile * HD * 2 + 2 * kTile * 8 + 16;   // Q, two stages of K and V, key offsets, two barriers
-  CUtensorMap none = {};
+           float scale, float* part_o, float* part_ml, void* out, int heads, int max_slices, int tiles_per_slice, unsigned* status,
+           cudaStream_t stream) {
+  constexpr int smem = 16 * HD * 2 + 4 * kTile * HD * 2 + 2 * kTile * 8;   // Q, two stages of K and V, key offsets
   static_assert(kWarps * 16 * HD * 4 <= 4 * kTile * HD * 2, "the merge buffer must fit in the tiles");
   static bool configured = false;
   if (!configured) {
@@ -891,11 +835,10 @@ int launch(const void* q, const IbKvView* kv, const int* dec_tokens, int n_dec, 
   }
   dim3 grid(kv->kv_heads, n_dec, max_slices);
   ib::launch(decode_split_kernel<HD>, grid, kWarps * 32, smem, stream, (const __nv_bfloat16*)q, *kv, dec_tokens, positions, seg_of_token, window,
-             scale * 1.4426950408889634f, part_o, part_ml, heads, max_slices, tiles_per_slice, kv_map ? *kv_map : none, view_row0,
-             kv_map ? 1 : 0, status);
+             scale * 1.4426950408889634f, part_o, part_ml, heads, max_slices, tiles_per_slice, status);
   IB_CHECK_LAUNCH("attention_decode split");
   ib::launch(decode_combine_kernel<HD>, dim3(heads, n_dec), kCombineThreads, 0, stream, part_o, part_ml, dec_tokens, positions, window, (__nv_bfloat16*)out, heads,
-             max_slices, tiles_per_slice);
+             max_slices, tiles_per_slice, status);
   IB_CHECK_LAUNCH("attention_decode combine");
   return 0;
 }
@@ -907,8 +850,7 @@ int launch(const void* q, const IbKvView* kv, const int* dec_tokens, int n_dec, 
 // part_ml float32 [n_dec * heads * max_slices * 2]. A CTA handles a slice of tiles_per_slice tiles of
 // ib_attention_decode_tile() keys; max_slices slices must cover every position in use. Slices are cut at
 // multiples of their size, so for a given tiles_per_slice a token's result does not depend on the batch.
-// kv_map: a tensor map of the view's pool from ib_make_kv_map (then view_row0 = the pool row where this
-// view's keys of page 0, head 0 start), or null to copy keys and values with cp.async.
+// Keys and values are copied with cp.async, so every page size is served.
 extern "C" int ib_attention_decode_tile() { return kTile; }
 
 // Describes a whole cache pool [executions, pages, 2, kv_heads, page_size, head_dim] (bfloat16) to TMA
@@ -934,12 +876,9 @@ extern "C" int ib_make_kv_map(void* map_out, const void* pool_base, long long to
 
 extern "C" int ib_attention_decode(const void* q, const IbKvView* kv, const int* dec_tokens, int n_dec, const int* positions,
                                    const int* seg_of_token, int window, float scale, float* part_o, float* part_ml, void* out, int heads,
-                                   int max_slices, int tiles_per_slice, const void* kv_map, long long view_row0, unsigned* status,
-                                   cudaStream_t stream) {
+                                   int max_slices, int tiles_per_slice, unsigned* status, cudaStream_t stream) {
   if (n_dec == 0) return 0;
   IB_CHECK_ARG(kv && kv->base && kv->block_table, "attention_decode: the cache view has a null pointer");
-  IB_CHECK_ARG(!kv_map || (kv->page_size % 8 == 0 && kTile % kv->page_size == 0),
-               "attention_decode: TMA copies need a page size that divides %d and is a multiple of 8, not %d", kTile, kv->page_size);
   IB_CHECK_ARG(tiles_per_slice >= 1 && tiles_per_slice <= 1024, "attention_decode: %d tiles per slice", tiles_per_slice);
   IB_CHECK_ARG(kv->dtype == IB_BF16, "attention_decode: the cache must be bfloat16");
   IB_CHECK_ARG(kv->kv_heads > 0 && heads % kv->kv_heads == 0 && heads / kv->kv_heads <= 16,
@@ -947,10 +886,10 @@ extern "C" int ib_attention_decode(const void* q, const IbKvView* kv, const int*
   IB_CHECK_ARG(n_dec > 0 && n_dec <= 65535 && max_slices > 0 && max_slices <= 65535, "attention_decode: bad sizes n=%d slices=%d", n_dec, max_slices);
   if (kv->head_dim == 128)
     return launch<128>(q, kv, dec_tokens, n_dec, positions, seg_of_token, window, scale, part_o, part_ml, out, heads, max_slices, tiles_per_slice,
-                       (const CUtensorMap*)kv_map, view_row0, status, stream);
+                       status, stream);
   if (kv->head_dim == 64)
     return launch<64>(q, kv, dec_tokens, n_dec, positions, seg_of_token, window, scale, part_o, part_ml, out, heads, max_slices, tiles_per_slice,
-                      (const CUtensorMap*)kv_map, view_row0, status, stream);
+                      status, stream);
   return ib_set_error("attention_decode: head_dim %d has no tensor-core kernel (64 and 128 have)", kv->head_dim);
 }
 
@@ -1050,8 +989,7 @@ int noalloc_scratch(float** ptr) {
 
 extern "C" int ib_attention_decode_noalloc(const void* q, const IbKvView* kv, const int* dec_tokens, int n_dec, const int* positions,
                                            const int* seg_of_token, int window, float scale, void* out, int heads, int max_slices,
-                                           int tiles_per_slice, const void* kv_map, long long view_row0, unsigned* status,
-                                           cudaStream_t stream) {
+                                           int tiles_per_slice, unsigned* status, cudaStream_t stream) {
   if (n_dec == 0) return 0;
   IB_CHECK_ARG(kv, "attention_decode_noalloc: the cache view is null");
   IB_CHECK_ARG(n_dec > 0 && heads > 0 && max_slices > 0 && kv->head_dim > 0, "attention_decode_noalloc: bad sizes n=%d heads=%d slices=%d", n_dec,
@@ -1067,5 +1005,5 @@ extern "C" int ib_attention_decode_noalloc(const void* q, const IbKvView* kv, co
   float* part_o = scratch;
   float* part_ml = scratch + slots * kv->head_dim;
   return ib_attention_decode(q, kv, dec_tokens, n_dec, positions, seg_of_token, window, scale, part_o, part_ml, out, heads, max_slices, tiles_per_slice,
-                             kv_map, view_row0, status, stream);
+                             status, stream);
 }

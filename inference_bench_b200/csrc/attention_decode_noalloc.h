@@ -34,5 +34,4 @@
 // message that ib_last_error() returns.
 extern "C" int ib_attention_decode_noalloc(const void* q, const IbKvView* kv, const int* dec_tokens, int n_dec, const int* positions,
                                            const int* seg_of_token, int window, float scale, void* out, int heads, int max_slices,
-                                           int tiles_per_slice, const void* kv_map, long long view_row0, unsigned* status,
-                                           cudaStream_t stream);
+                                           int tiles_per_slice, unsigned* status, cudaStream_t stream);

@@ -38,6 +38,11 @@ int ib_set_error(const char* fmt, ...);
 extern "C" int ib_pdl_enabled();
 extern "C" void ib_set_pdl(int on);
 
+// How long a bounded wait inside a kernel (on an mbarrier) may last before the kernel gives up, sets
+// IB_ERR_WAIT_TIMEOUT in the status word and unwinds. Launchers pass it to their kernels as an argument.
+extern "C" unsigned long long ib_wait_limit_ns();
+extern "C" void ib_set_wait_limit_ms(int ms);
+
 namespace ib {
 
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }

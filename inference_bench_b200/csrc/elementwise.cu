@@ -24,6 +24,10 @@ static int g_pdl = 1;
 extern "C" int ib_pdl_enabled() { return g_pdl; }
 extern "C" void ib_set_pdl(int on) { g_pdl = on ? 1 : 0; }
 
+static unsigned long long g_wait_limit_ns = 2000000000ull;  // 2 s
+extern "C" unsigned long long ib_wait_limit_ns() { return g_wait_limit_ns; }
+extern "C" void ib_set_wait_limit_ms(int ms) { g_wait_limit_ns = (unsigned long long)(ms > 0 ? ms : 1) * 1000000ull; }
+
 namespace {
 
 // ---------------------------------------------------------------- embedding

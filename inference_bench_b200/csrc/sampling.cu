@@ -197,7 +197,9 @@ __global__ void __launch_bounds__(kPickThreads) sample_pick_kernel(const float* 
 }
 
 // Stage 3, one warp per row: the best of the chunks.
-__global__ void sample_final_kernel(const float* __restrict__ part_v, const int* __restrict__ part_i, int chunks, int* __restrict__ tokens) {
+// With `status` the step's status word is copied to tokens[gridDim.x], so the host gets it in the transfer that brings the tokens.
+__global__ void sample_final_kernel(const float* __restrict__ part_v, const int* __restrict__ part_i, int chunks, int* __restrict__ tokens,
+                                    const unsigned* __restrict__ status) {
   ib::pdl_launch_dependents();
   ib::pdl_wait();
   const int r = blockIdx.x;
@@ -207,6 +209,7 @@ __global__ void sample_final_kernel(const float* __restrict__ part_v, const int*
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) better(bv, bi, __shfl_xor_sync(0xffffffffu, bv, o), __shfl_xor_sync(0xffffffffu, bi, o));
   if (threadIdx.x == 0) tokens[r] = bi == 0x7fffffff ? 0 : bi;
+  if (status && r == 0 && threadIdx.x == 0) tokens[gridDim.x] = (int)*status;
 }
 
 // After a decode step: feed every row's sampled token back as its next input, move its position on
@@ -251,7 +254,9 @@ extern "C" int ib_sample_chunks(int V) { return V <= 4096 ? 1 : (V + 4095) / 409
 
 // logits float32 [rows, V], params [rows] of six words -> tokens int32 [rows].
 // scratch: float32 [rows * (1 + 2 * ib_sample_chunks(V))] (threshold, then per-chunk best values and indices).
-extern "C" int ib_sample_rows(const float* logits, int rows, int V, const void* params, int* tokens, float* scratch, cudaStream_t stream) {
+// status: null, or the device status word, whose value is then stored in tokens[rows] (tokens has rows + 1 entries).
+extern "C" int ib_sample_rows(const float* logits, int rows, int V, const void* params, int* tokens, float* scratch, const unsigned* status,
+                              cudaStream_t stream) {
   if (rows == 0) return 0;
   IB_CHECK_ARG(rows > 0 && rows <= 65535 && V > 0, "sample_rows: bad sizes rows=%d V=%d", rows, V);
   const int chunks = ib_sample_chunks(V);
@@ -263,7 +268,7 @@ extern "C" int ib_sample_rows(const float* logits, int rows, int V, const void* 
   IB_CHECK_LAUNCH("sample_rows threshold");
   ib::launch(sample_pick_kernel, dim3(chunks, rows), kPickThreads, 0, stream, logits, V, (const RowParams*)params, threshold, part_v, part_i, chunk);
   IB_CHECK_LAUNCH("sample_rows pick");
-  ib::launch(sample_final_kernel, rows, 32, 0, stream, part_v, part_i, chunks, tokens);
+  ib::launch(sample_final_kernel, rows, 32, 0, stream, part_v, part_i, chunks, tokens, status);
   IB_CHECK_LAUNCH("sample_rows final");
   return 0;
 }

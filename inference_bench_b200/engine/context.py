@@ -54,6 +54,9 @@ class StepContext:
     # True when the step is being captured into (or replayed from) a CUDA graph: launch shapes must
     # then depend on the batch's sizes only, never on the host copies of positions or tables
     fixed_shape: bool = False
+    # None, or a list that the decoder fills with the residual stream at the wanted rows: after the embedding, then after
+    # every schedule entry (float32 [wanted, hidden] each). Debugging only.
+    trace: Optional[list] = None
 
     @property
     def n_segments(self) -> int:

@@ -16,6 +16,8 @@ from typing import Any, Hashable, Mapping, Optional, Sequence, Union
 import torch
 
 from ..cache.manager import CacheManager
+from ..config.runtime_options import RuntimeOptions
+from ..config.spec import ModelSpec, resolve_model
 from ..sampling.params import GREEDY, SamplingParams
 from .executor import GpuExecutor
 from .model import load_model, random_model
@@ -39,43 +41,56 @@ class Reply:
 
 
 class Engine:
-    def __init__(self, model: Union[str, Path, Mapping[str, Any]], dtype: str = "bfloat16", max_ctx: Optional[int] = None,
-                 page_size: int = 64, num_pages: Optional[int] = None, kv_gb: Optional[float] = None, max_num_seqs: int = 64,
-                 max_batched_tokens: int = 8192, prefill_chunk: Union[int, str] = 2048, random_weights_seed: Optional[int] = None,
-                 device: str = "cuda:0", use_graphs: bool = True, pipeline: bool = True):
-        """model: a folder with config.json and model.safetensors, or (with random_weights_seed) a raw
-        config.json mapping whose weights are then made on the device. num_pages / kv_gb size the
-        cache pool; by default it holds max_num_seqs requests of max_ctx tokens, capped by free memory.
-        pipeline: keep decode steps one ahead of the host (see engine/scheduler.py). prefill_chunk: the longest
+    def __init__(self, model: Union[str, Path, Mapping[str, Any], ModelSpec], dtype: Optional[str] = None, max_ctx: Optional[int] = None,
+                 page_size: Optional[int] = None, num_pages: Optional[int] = None, kv_gb: Optional[float] = None, max_num_seqs: Optional[int] = None,
+                 max_batched_tokens: Optional[int] = None, prefill_chunk: Union[int, str, None] = None, random_weights_seed: Optional[int] = None,
+                 device: str = "cuda:0", use_graphs: Optional[bool] = None, pipeline: Optional[bool] = None,
+                 options: Union[RuntimeOptions, Mapping[str, Any], None] = None):
+        """model: a folder with config.json and model.safetensors, a hub id whose snapshot lies in the hub cache, a TOML
+        model spec (config/spec.py), or a raw config.json mapping; with random_weights_seed the weights are made on the
+        device instead of read. How the model is run is a `RuntimeOptions`: the defaults, then the `[runtime]` table of
+        a model spec, then `options` (a RuntimeOptions or a mapping of its fields), then the keyword arguments given
+        here (dtype, page_size, num_pages, kv_gb, max_num_seqs, max_batched_tokens, prefill_chunk, use_graphs, pipeline).
+        num_pages / kv_gb size the cache pool; by default it holds max_num_seqs requests of max_ctx tokens, capped by
+        free memory. pipeline: keep decode steps one ahead of the host (engine/scheduler.py). prefill_chunk: the longest
         portion of one prompt in a step (crates/specrt/src/runtime.rs:801), or "auto" for the size near 2,048 whose
         matrix-product tiles fill whole rounds of the GPU best at this model's layer sizes."""
-        self.rt = Runtime(device, dtype)
-        if isinstance(model, Mapping):
-            if random_weights_seed is None:
-                raise ValueError("a raw configuration needs random_weights_seed")
-            self.config, self.decoder = random_model(model, random_weights_seed, self.rt)
+        spec = resolve_model(model)
+        opts = spec.runtime
+        if isinstance(options, RuntimeOptions):
+            opts = opts.merged(options.non_default())
+        elif options is not None:
+            opts = opts.merged(options, "Engine(options=...)")
+        opts = opts.merged(dtype=dtype, page_size=page_size, num_pages=num_pages, kv_gb=kv_gb, max_num_seqs=max_num_seqs,
+                           max_batched_tokens=max_batched_tokens, prefill_chunk=prefill_chunk, graphs=use_graphs, pipeline=pipeline)
+        self.spec, self.options = spec, opts
+        self.rt = Runtime(device, options=opts)
+        if random_weights_seed is not None:
+            self.config, self.decoder = random_model(spec.raw_config, random_weights_seed, self.rt)
             self.model_dir = None
         else:
-            self.model_dir = Path(model)
-            self.config, self.decoder = load_model(self.model_dir, self.rt)
+            if isinstance(model, Mapping):
+                raise ValueError("a raw configuration needs random_weights_seed")
+            self.config, self.decoder = load_model(spec, self.rt)
+            self.model_dir = spec.model_dir
+        page_size, max_num_seqs, num_pages = opts.page_size, opts.max_num_seqs, opts.num_pages
         limit = self.decoder.plan.max_positions
         self.max_ctx = min(max_ctx or DEFAULT_MAX_CTX, limit)   # crates/specrt/src/engine.rs:53-60
         needs = self.decoder.cache_needs()
         if num_pages is None:
             per_page = sum(2 * n.kv_heads * n.head_dim * page_size for n in needs if hasattr(n, "kv_heads")) * torch.empty(0, dtype=self.rt.act_dtype).element_size()
             want = max_num_seqs * -(-self.max_ctx // page_size)
-            if kv_gb is not None:
-                want = int(kv_gb * 2**30 // max(per_page, 1))
+            if opts.kv_gb is not None:
+                want = int(opts.kv_gb * 2**30 // max(per_page, 1))
             free, _ = torch.cuda.mem_get_info(self.rt.device)
             room = int(free * 0.85 // max(per_page, 1))     # keep headroom for activations (crates/specrt/src/runtime.rs:1164-1182)
             num_pages = max(1, min(want, room))
         self.cache = CacheManager(needs, page_size, num_pages, max_num_seqs, self.max_ctx, device=self.rt.device, dtype=self.rt.act_dtype,
                                   sources=self.decoder.cache_sources())
-        if prefill_chunk == "auto":
-            prefill_chunk = self._balanced_portion()
+        prefill_chunk = self._balanced_portion() if opts.prefill_chunk == "auto" else opts.prefill_chunk
         self.runner = ModelRunner(self.decoder, self.cache, self.rt)
-        self.executor = GpuExecutor(self.runner, use_graphs=use_graphs)
-        self.scheduler = Scheduler(self.cache, SchedulerConfig(max_num_seqs, max_batched_tokens, prefill_chunk, self.max_ctx, pipeline))
+        self.executor = GpuExecutor(self.runner, use_graphs=opts.graphs)
+        self.scheduler = Scheduler(self.cache, SchedulerConfig(max_num_seqs, opts.max_batched_tokens, prefill_chunk, self.max_ctx, opts.pipeline))
         self._tokenizer = None
         self._next_id = 0
 
@@ -92,7 +107,7 @@ class Engine:
                     if isinstance(v, LinearWeights) and id(v) not in seen:
                         seen.add(id(v))
                         matrices.append((v.n, v.k))
-        return gemm_tcgen05.balanced_portion(matrices) if matrices else 2048
+        return gemm_tcgen05.balanced_portion(matrices, sm_count=self.rt.sm_count) if matrices else 2048
 
     @classmethod
     def load(cls, model, max_ctx: Optional[int] = None, **kw) -> "Engine":

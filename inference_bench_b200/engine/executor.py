@@ -52,11 +52,12 @@ class _DecodeGraph:
         self.d_count = d[self.n_ints - 1:self.n_ints]
         self.history = torch.zeros((RUN_AHEAD_MAX, B), dtype=torch.int32, device=rt.device)
         self.h_history = torch.zeros((RUN_AHEAD_MAX, B), dtype=torch.int32).pin_memory()
-        self.tokens = torch.zeros(B, dtype=torch.int32, device=rt.device)
-        self.h_out = torch.zeros(B, dtype=torch.int32).pin_memory()
+        self.result = torch.zeros(B + 1, dtype=torch.int32, device=rt.device)   # the step's tokens, then the status word after the step
+        self.tokens = self.result[:B]
+        self.h_out = torch.zeros(B + 1, dtype=torch.int32).pin_memory()
         # for steps launched without waiting (two may be in flight): a staging copy of the inputs, a place for the tokens and an event each
         self.stages = [torch.zeros(self.n_ints, dtype=torch.int32).pin_memory() for _ in range(2)]
-        self.h_outs = [torch.zeros(B, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self.h_outs = [torch.zeros(B + 1, dtype=torch.int32).pin_memory() for _ in range(2)]
         self.events = [torch.cuda.Event() for _ in range(2)]
         self.pending = [False, False]
         self.turn = 0
@@ -78,11 +79,12 @@ class _DecodeGraph:
         from ..kernels import ops
         self.ctx.memo = {}
         self.logits = self.runner.decoder.forward(self.ctx)
-        ops.sample_rows(self.logits, self.d_params, self.tokens)
+        ops.sample_rows(self.logits, self.d_params, self.result, self.runner.rt.status)
         c = self.ctx
         ops.advance_rows(self.tokens, c.token_ids, c.positions, c.seg_pos0, self.d_params, self.history, self.d_count)
 
     def capture(self) -> None:
+        self.runner.rt.activate()
         self.dev.copy_(self.host, non_blocking=True)
         stream = torch.cuda.Stream(device=self.runner.rt.device)
         stream.wait_stream(torch.cuda.current_stream())
@@ -109,7 +111,9 @@ class _DecodeGraph:
         for _ in range(steps):
             self.graph.replay()
         self.h_history.copy_(self.history, non_blocking=True)
+        self.h_out.copy_(self.result, non_blocking=True)
         torch.cuda.current_stream().synchronize()
+        self.runner.rt.raise_for(int(self.h_out[self.rows]))
         return self.h_history[:steps, :len(entries)].tolist()
 
     def run(self, entries: list[StepEntry], sampling: list[tuple[SamplingParams, int]]) -> list[int]:
@@ -117,8 +121,9 @@ class _DecodeGraph:
         self._fill(entries, sampling)
         self.dev.copy_(self.host, non_blocking=True)
         self.graph.replay()
-        self.h_out.copy_(self.tokens, non_blocking=True)
+        self.h_out.copy_(self.result, non_blocking=True)
         torch.cuda.current_stream().synchronize()
+        self.runner.rt.raise_for(int(self.h_out[self.rows]))
         return self.h_out[:n].tolist()
 
     def launch(self, entries: list[StepEntry], sampling: list[tuple[SamplingParams, int]], feed: bool) -> tuple[int, int]:
@@ -136,7 +141,7 @@ class _DecodeGraph:
         else:
             self.dev.copy_(stage, non_blocking=True)
         self.graph.replay()
-        self.h_outs[slot].copy_(self.tokens, non_blocking=True)
+        self.h_outs[slot].copy_(self.result, non_blocking=True)
         self.events[slot].record()
         self.pending[slot] = True
         return slot, len(entries)
@@ -145,6 +150,7 @@ class _DecodeGraph:
         slot, n = handle
         self.events[slot].synchronize()
         self.pending[slot] = False
+        self.runner.rt.raise_for(int(self.h_outs[slot][self.rows]))
         return self.h_outs[slot][:n].tolist()
 
     def _fill(self, entries: list[StepEntry], sampling: list[tuple[SamplingParams, int]], tokens: bool = True) -> None:
@@ -192,7 +198,7 @@ class GpuExecutor:
             cache.commit(e.request, cache.length(e.request) + steps)
         self.steps += steps
         self.h2d_bytes += g.n_ints * 4
-        self.d2h_bytes += steps * g.rows * 4
+        self.d2h_bytes += steps * g.rows * 4 + 4
         return out
 
     def launch_decode(self, entries: list[StepEntry], sampling: list[tuple[SamplingParams, int]], feed: bool = False):
@@ -219,7 +225,7 @@ class GpuExecutor:
             cache.commit(e.request, cache.length(e.request) + 1)
         self.steps += 1
         self.h2d_bytes += (g.n_ints - (g.rows if feed else 0)) * 4
-        self.d2h_bytes += g.rows * 4
+        self.d2h_bytes += g.rows * 4 + 4
         return g, handle
 
     def collect(self, handle) -> list[int]:
@@ -241,13 +247,15 @@ class GpuExecutor:
                 cache.commit(e.request, cache.length(e.request) + 1)
             self.last_logits = g.logits
             self.h2d_bytes += g.n_ints * 4
-            self.d2h_bytes += g.rows * 4
+            self.d2h_bytes += g.rows * 4 + 4
             return out
         logits = self.runner.step(entries, check=False)
-        if logits is None:
+        if logits is None:   # nothing to sample: no transfer comes back, so the status word is read when a later step's tokens are
             return []
-        tokens = self.sampler.sample(logits, [p for p, _ in sampling], [s for _, s in sampling])
+        tokens = self.sampler.sample(logits, [p for p, _ in sampling], [s for _, s in sampling], self.runner.rt.status)
         self.last_logits = logits
         self.h2d_bytes += sum(len(e.tokens) for e in entries) * 12 + len(entries) * (12 + 4 * cache.table_width * len(cache.groups)) + len(sampling) * 28
-        self.d2h_bytes += len(sampling) * 4
-        return tokens.cpu().tolist()
+        self.d2h_bytes += len(sampling) * 4 + 4
+        host = tokens.cpu().tolist()
+        self.runner.rt.raise_for(host[-1])
+        return host[:-1]

@@ -1,16 +1,14 @@
-"""From a model folder (or a raw configuration and a seed) to a decoder bound to a runtime."""
+"""From a model (a folder, a hub id, a TOML model spec, or a raw configuration and a seed) to a
+decoder bound to a runtime."""
 from __future__ import annotations
 
-from pathlib import Path
-from typing import Any, Mapping, Optional
-
-import torch
+from typing import Any, Mapping
 
 from .. import models  # noqa: F401  (fills the architecture registry)
-from ..config.qwen3 import read_config_json
+from ..config.spec import ModelSpec, resolve_model
 from ..parts.decoder import Decoder
 from ..registry import resolve
-from ..weights.loader import load_weights
+from ..weights.loader import stream_into
 from ..weights.random_init import random_tensor
 from .runtime import Runtime
 
@@ -21,17 +19,21 @@ def plan_from_config(raw_config: Mapping[str, Any]):
     return cfg, arch.plan(cfg)
 
 
-def load_model(model_dir, rt: Runtime) -> tuple[Any, Decoder]:
-    """config.json chooses the model class; model.safetensors gives the tensors by name."""
-    cfg, plan = plan_from_config(read_config_json(model_dir))
+def load_model(model, rt: Runtime) -> tuple[Any, Decoder]:
+    """The configuration chooses the model class; the checkpoint gives the tensors by name, one part
+    at a time. `model` is whatever `config.spec.resolve_model` takes."""
+    spec: ModelSpec = resolve_model(model)
+    if spec.model_dir is None:
+        raise FileNotFoundError(f"no weights were found for {spec.name} ({spec.source}): a folder with model.safetensors is needed, or random weights")
+    cfg, plan = plan_from_config(spec.raw_config)
     decoder = Decoder(plan)
-    weights = load_weights(Path(model_dir), decoder.weight_specs(), plan.ignored_tensors, device=rt.device)
-    decoder.bind(weights, rt)
+    decoder.unread_tensors = stream_into(decoder, rt, spec.model_dir, spec.tensors, strict=rt.options.strict_weights)
     return cfg, decoder
 
 
 def random_model(raw_config: Mapping[str, Any], seed: int, rt: Runtime) -> tuple[Any, Decoder]:
-    """The same tensors `write_random_model` would store, made on the device without touching the disk."""
+    """A model with random tensors of the kind `write_random_model` stores (the same distributions, seeded per
+    tensor name; not the same values: the device's generator is not the host's), made on the device part by part."""
     cfg, plan = plan_from_config(raw_config)
     decoder = Decoder(plan)
     specs = {s.name: s for s in decoder.weight_specs()}

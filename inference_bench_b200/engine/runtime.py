@@ -13,6 +13,7 @@ from typing import Optional
 
 import torch
 
+from ..config.runtime_options import RuntimeOptions
 from ..kernels import lib as L
 from ..kernels import ops
 
@@ -33,20 +34,32 @@ class LinearWeights:
 
 
 class Runtime:
-    def __init__(self, device="cuda:0", dtype: str = "bfloat16", gemm: str = "auto"):
-        if dtype not in MODES:
+    def __init__(self, device="cuda:0", dtype: Optional[str] = None, gemm: Optional[str] = None, options: Optional[RuntimeOptions] = None):
+        """`options` holds every choice of kernel and fusion; `dtype` and `gemm` given here replace its fields."""
+        if dtype is not None and dtype not in MODES:
             raise ValueError(f"dtype must be one of {sorted(set(MODES))}, got {dtype!r}")
+        self.options = (options or RuntimeOptions()).merged(dtype=dtype, gemm=gemm)
         self.device = torch.device(device)
         if self.device.type != "cuda":
             raise L.KernelLibraryError("the engine runs on a CUDA device only; there is no CPU path")
         if not torch.cuda.is_available():
             raise L.KernelLibraryError("no CUDA device is visible; the engine has no CPU path")
-        L.load()
-        ops._device_index = self.device.index if self.device.index is not None else torch.cuda.current_device()   # whose current stream the kernels are launched on
-        self.mode = "float32" if MODES[dtype] == torch.float32 else "bfloat16"
-        self.act_dtype = MODES[dtype]
-        self.gemm = gemm  # "auto" | "simt" | "tcgen05"
+        self.lib = L.load()
+        self.device_index = self.device.index if self.device.index is not None else torch.cuda.current_device()
+        self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
+        self.mode = self.options.dtype
+        self.act_dtype = MODES[self.mode]
+        self.gemm = self.options.gemm  # "auto" | "simt" | "tcgen05"
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.activate()
+
+    def activate(self) -> None:
+        """Make this runtime the one whose settings the kernel library uses: the device whose current stream kernels
+        are launched on, programmatic dependent launch on or off, and the limit of bounded waits. The library keeps
+        these per process, so every step (and every graph capture) calls this first; it costs three C calls."""
+        ops._device_index = self.device_index
+        self.lib.ib_set_pdl(1 if self.options.pdl else 0)
+        self.lib.ib_set_wait_limit_ms(int(self.options.wait_limit_ms))
 
     # ---------------------------------------------------------------- memory
     def empty(self, shape, dtype=None) -> torch.Tensor:
@@ -97,9 +110,9 @@ class Runtime:
         T, inter = x.shape[0], lw.n // 2
         if self.mode == "bfloat16" and self.gemm != "simt":
             from ..kernels import gemm_tcgen05
-            if gemm_tcgen05.swiglu_supported(T, lw.k, inter):
+            if self.options.swiglu_epilogue and gemm_tcgen05.swiglu_supported(T, lw.k, inter):
                 act = self.empty((T, inter))
-                gemm_tcgen05.gemm_swiglu(x, lw.weight, act, self.status)
+                gemm_tcgen05.gemm_swiglu(x, lw.weight, act, self.status, pair_min_tokens=self.options.pair_min_tokens)
                 return act
         gu = self.linear(x, lw)
         act = self.empty((T, inter))
@@ -109,7 +122,11 @@ class Runtime:
     # ---------------------------------------------------------------- status word
     def check_status(self) -> None:
         """Read the status word (synchronises) and raise if a kernel reported a fault."""
-        bits = int(self.status.item())
+        self.raise_for(int(self.status.item()))
+
+    def raise_for(self, bits: int) -> None:
+        """Raise DeviceStatusError for a non-zero value of the status word (already on the host, for instance from the
+        transfer that brought a step's tokens) and clear the word on the device."""
         if bits:
             self.status.zero_()
             what = [name for bit, name in ((L.ERR_BAD_PAGE, "a block table entry was missing or out of range"),

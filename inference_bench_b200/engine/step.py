@@ -34,14 +34,16 @@ class ModelRunner:
         self.decoder, self.cache, self.rt = decoder, cache, rt
         self.vocab = decoder.plan.vocab_size
 
-    def step(self, entries: Sequence[StepEntry], check: bool = True) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], check: bool = True, trace: Optional[list] = None) -> Optional[torch.Tensor]:
         """Run one step. Requests must be admitted to the cache manager; every entry continues its
         request where the last step left it. Returns float32 logits [wanted, vocab] on the device in
         the order of the entries and of their `want`, or None when nothing is wanted.
-        Raises OutOfPages (and changes nothing) if a request cannot get its pages."""
+        Raises OutOfPages (and changes nothing) if a request cannot get its pages. `trace`: a list that receives the
+        residual stream at the wanted rows after the embedding and after every schedule entry (debugging)."""
         entries = [e for e in entries if len(e.tokens) > 0]
         if not entries:
             return None
+        self.rt.activate()
         seen = set()
         for e in entries:
             if e.request in seen:
@@ -65,6 +67,7 @@ class ModelRunner:
         tables = self.cache.step_tables([e.request for e in entries])
         dev_tables = [torch.from_numpy(t).pin_memory().to(self.rt.device, non_blocking=True) for t in tables]
         ctx = build_context(self.rt, segments, self.cache.views(dev_tables))
+        ctx.trace = trace
         logits = self.decoder.forward(ctx)
         for e in entries:
             self.cache.commit(e.request, self.cache.length(e.request) + len(e.tokens))

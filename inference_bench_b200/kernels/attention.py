@@ -29,40 +29,30 @@ def decode_tiles_per_slice(n_dec: int, kv_heads: int, max_keys: int) -> int:
         tps *= 2
     return tps
 
-_SM_COUNT: dict = {}
-
-
-def stream_slices(n_dec: int, kv_heads: int, max_keys: int, device) -> int:
+def stream_slices(n_dec: int, kv_heads: int, max_keys: int, sm_count: int) -> int:
     """Into how many slices the streaming decode kernel cuts each token's keys. Its CTAs stay (two per
     SM) and take (slice, token, kv head) units in turn: with few tokens, as many slices as give every
     CTA one unit; with more (token, kv head) pairs than CTAs, enough slices for about six units per
     CTA, so that the last round leaves few CTAs idle. A slice has two tiles at least."""
-    if device not in _SM_COUNT:
-        _SM_COUNT[device] = torch.cuda.get_device_properties(device).multi_processor_count
-    slots = 2 * _SM_COUNT[device]
+    slots = 2 * sm_count
     pairs = n_dec * kv_heads
     want = slots // pairs if pairs <= slots else -(-6 * slots // pairs)
     tiles = -(-max_keys // decode_tile())
     return max(1, min(want, -(-tiles // 2)))
 
 
-QTILE = {"ws": 128, "tcgen05": 128, "mma": 64}   # query rows per CTA of the prefill kernels (csrc/attention_prefill_ws.cu, _tc.cu, attention_prefill.cu)
-PREFILL_KERNEL = "ws"   # which one the engine uses: "ws" (tcgen05, one job per warp, keys and values by TMA; falls back to "tcgen05" for
-                        # page sizes TMA cannot serve), "tcgen05" (every thread does everything, cp.async) or "mma" (mma.sync)
+QTILE = 128   # query rows per CTA of the prefill kernels (csrc/attention_prefill_ws.cu, attention_prefill_tc.cu)
 
-L.register("ib_attention_decode", [L._p, C.POINTER(L.KvView), L._p, L._i, L._p, L._p, L._i, L._f, L._p, L._p, L._p, L._i, L._i, L._i, L._p, L._ll, L._p, L._p])
+# Which kernel runs is a runtime option (config/runtime_options.py): `prefill_attention` "ws" (tcgen05, one job per warp, keys and
+# values by TMA) or "tcgen05" (every thread does everything, cp.async), "auto" = ws where TMA can serve the page size;
+# `decode_attention` "stream" (CTAs that stay and a ring that TMA fills: measured inside whole decode steps at the Qwen3-8B shape and
+# page size 64 the faster one from 1 to 128 requests, by 1 to 7 %) or "split" (one CTA per slice, cp.async), "auto" = stream where TMA
+# can serve the page size; `fuse_decode_qk` with `fuse_decode_max_pairs` (every unit of the fused kernel prepares its queries again,
+# which costs more than the saved kernel from about 16 requests of 8 kv heads on).
+L.register("ib_attention_decode", [L._p, C.POINTER(L.KvView), L._p, L._i, L._p, L._p, L._i, L._f, L._p, L._p, L._p, L._i, L._i, L._i, L._p, L._p])
 L.register("ib_attention_decode_stream", [L._p, C.POINTER(L.KvView), L._p, L._i, L._p, L._p, L._i, L._f, L._p, L._p, L._p, L._i, L._i, L._i, L._p, L._ll, L._p, L._p])
 L.register("ib_attention_decode_fused", [L._p, L._i, L._ll, L._p, L._p, L._f, L._p, L._p, L._i, C.POINTER(L.KvView), L._p, L._i, L._p, L._p, L._i, L._f, L._p, L._p,
                                          L._p, L._i, L._i, L._i, L._p, L._ll, L._p, L._p])
-FUSE_DECODE = True   # steps of decoded tokens only: q/k norm, rotation and the cache write inside the streaming decode kernel
-FUSE_DECODE_MAX_PAIRS = 128   # ... up to this many (token, kv head) pairs: every unit of the kernel prepares its queries again, which costs
-                              # more than the saved kernel from about 16 requests of 8 kv heads on (measured inside whole decode steps)
-DECODE_KERNEL = "stream"   # "stream": CTAs that stay and a ring that TMA fills (needs a page size TMA can serve; measured inside whole decode steps
-                           # at Qwen3-8B shape and page size 64 it is the faster one from 1 to 128 requests, by 1 to 7 %); "split": one CTA per slice
-STREAM_TILES_PER_SLICE = 0   # 0: every token's visible keys in stream_slices() equal parts; n > 0: slices of n tiles at fixed positions
-USE_TMA = False  # decode keys and values by TMA box copies (one thread, one 2 KiB box per page and plane) instead of cp.async by all
-                 # threads: measured slower at page size 16 (3.86 against 3.71 ms per step at batch 8), so off; kept and tested
-L.register("ib_attention_prefill", [L._p, C.POINTER(L.KvView), L._p, L._p, L._i, L._p, L._p, L._i, L._f, L._p, L._i, L._p, L._p])
 L.register("ib_attention_prefill_tc", [L._p, C.POINTER(L.KvView), L._p, L._p, L._i, L._p, L._p, L._i, L._f, L._p, L._i, L._p, L._p])
 L.register("ib_attention_prefill_ws", [L._p, C.POINTER(L.KvView), L._p, L._p, L._i, L._p, L._p, L._i, L._f, L._p, L._i, L._p, L._ll, L._p, L._p])
 
@@ -73,7 +63,7 @@ def has_tensor_core_kernel(dtype: torch.dtype, head_dim: int, heads: int, kv_hea
 
 def _work_lists(ctx):
     """Per step, shared by all layers: flat rows of decoded tokens, and 64-row query tiles of portions."""
-    qtile = QTILE[PREFILL_KERNEL]
+    qtile = QTILE
     key = ("attention_work", qtile)
     if key in ctx.memo:
         return ctx.memo[key]
@@ -112,7 +102,7 @@ def project_qkv(ctx, h: torch.Tensor, lw, q_norm_w, k_norm_w, eps: float, cos, s
         return None
     if cos is not None and 2 * cos.shape[1] != 128:
         return None
-    if not G.qkv_in_epilogue(h.shape[0], lw.n, lw.k):
+    if not G.qkv_in_epilogue(rt, h.shape[0], lw.n, lw.k):
         return None
     q = rt.empty((h.shape[0], heads * 128))
     G.gemm_qkv_pair(h, lw.weight, q, cache, heads, q_norm_w, k_norm_w, eps, cos, sin, ctx.positions, ctx.seg_of_token, write_kv, rt.status)
@@ -132,7 +122,8 @@ def decode_fused(ctx, qkv: torch.Tensor, q_norm_w, k_norm_w, eps: float, cos, si
     hd = view.head_dim
     if not write_kv:
         return None
-    if not (FUSE_DECODE and DECODE_KERNEL == "stream" and rt.act_dtype == torch.bfloat16 and has_tensor_core_kernel(rt.act_dtype, hd, heads, view.kv_heads)):
+    opt = rt.options
+    if not (opt.decode_qk and opt.decode_attention != "split" and rt.act_dtype == torch.bfloat16 and has_tensor_core_kernel(rt.act_dtype, hd, heads, view.kv_heads)):
         return None
     if cos is not None and 2 * cos.shape[1] != hd:
         return None
@@ -140,7 +131,7 @@ def decode_fused(ctx, qkv: torch.Tensor, q_norm_w, k_norm_w, eps: float, cos, si
     if work["n_tiles"] or not work["n_dec"]:
         return None
     kv_map, row0 = cache.tma()
-    if not kv_map or work["n_dec"] * view.kv_heads > FUSE_DECODE_MAX_PAIRS:
+    if not kv_map or work["n_dec"] * view.kv_heads > opt.fuse_decode_max_pairs:
         return None
     P, T, R = qkv.shape
     if R != (heads + 2 * view.kv_heads) * hd or T != ctx.n_tokens:
@@ -155,8 +146,8 @@ def decode_fused(ctx, qkv: torch.Tensor, q_norm_w, k_norm_w, eps: float, cos, si
     out = rt.empty((T, heads * hd), rt.act_dtype)
     limit = view.table_stride * view.page_size
     max_keys = limit if work["max_pos"] is None else work["max_pos"] + 1
-    tps = STREAM_TILES_PER_SLICE
-    max_slices = -(-max_keys // (tps * decode_tile())) if tps else stream_slices(work["n_dec"], view.kv_heads, max_keys, qkv.device)
+    tps = opt.stream_tiles_per_slice
+    max_slices = -(-max_keys // (tps * decode_tile())) if tps else stream_slices(work["n_dec"], view.kv_heads, max_keys, rt.sm_count)
     skey = ("decode_scratch", heads, hd, max_slices)
     if skey not in ctx.memo:
         n = work["n_dec"] * heads * max_slices
@@ -182,29 +173,35 @@ def paged_attention(ctx, q: torch.Tensor, cache: ops.KvLayerView, heads: int, wi
     if work["n_dec"]:
         limit = view.table_stride * view.page_size
         max_keys = limit if work["max_pos"] is None else work["max_pos"] + 1
-        stream_map, stream_row0 = cache.tma() if DECODE_KERNEL == "stream" else (None, 0)
+        opt = rt.options
+        stream_map, stream_row0 = cache.tma() if opt.decode_attention != "split" else (None, 0)
+        if opt.decode_attention == "stream" and not stream_map:
+            raise L.KernelError(f"decode_attention = \"stream\" needs a page size that TMA can serve (a multiple of 8 that divides 64, or a multiple of 64), got {view.page_size}")
         if stream_map:
-            tps = STREAM_TILES_PER_SLICE
-            max_slices = -(-max_keys // (tps * decode_tile())) if tps else stream_slices(work["n_dec"], view.kv_heads, max_keys, q.device)
-            kv_map, row0 = stream_map, stream_row0
+            tps = opt.stream_tiles_per_slice
+            max_slices = -(-max_keys // (tps * decode_tile())) if tps else stream_slices(work["n_dec"], view.kv_heads, max_keys, rt.sm_count)
         else:
-            tps = decode_tiles_per_slice(work["n_dec"], view.kv_heads, max_keys)
+            tps = opt.split_tiles_per_slice or decode_tiles_per_slice(work["n_dec"], view.kv_heads, max_keys)
             max_slices = -(-max_keys // (tps * decode_tile()))
-            kv_map, row0 = cache.tma() if USE_TMA and decode_tile() % view.page_size == 0 else (None, 0)
         skey = ("decode_scratch", heads, view.head_dim, max_slices)
         if skey not in ctx.memo:
             n = work["n_dec"] * heads * max_slices
             ctx.memo[skey] = (rt.empty((n * view.head_dim,), torch.float32), rt.empty((n * 2,), torch.float32))
         part_o, part_ml = ctx.memo[skey]
-        L.call("ib_attention_decode_stream" if stream_map else "ib_attention_decode", q.data_ptr(), C.byref(view), work["dec_tokens"].data_ptr(),
-               work["n_dec"], ctx.positions.data_ptr(), ctx.seg_of_token.data_ptr(), int(window or 0), float(scale), part_o.data_ptr(),
-               part_ml.data_ptr(), out.data_ptr(), heads, max_slices, tps, kv_map, row0, rt.status.data_ptr(), stream)
+        args = (q.data_ptr(), C.byref(view), work["dec_tokens"].data_ptr(), work["n_dec"], ctx.positions.data_ptr(), ctx.seg_of_token.data_ptr(),
+                int(window or 0), float(scale), part_o.data_ptr(), part_ml.data_ptr(), out.data_ptr(), heads, max_slices, tps)
+        if stream_map:
+            L.call("ib_attention_decode_stream", *args, stream_map, stream_row0, rt.status.data_ptr(), stream)
+        else:
+            L.call("ib_attention_decode", *args, rt.status.data_ptr(), stream)
     if work["n_tiles"]:
         args = (q.data_ptr(), C.byref(view), work["tile_seg"].data_ptr(), work["tile_row0"].data_ptr(), work["n_tiles"], ctx.seg_start.data_ptr(),
                 ctx.seg_pos0.data_ptr(), int(window or 0), float(scale), out.data_ptr(), heads)
-        kv_map, row0 = cache.tma() if PREFILL_KERNEL == "ws" else (None, 0)
+        kv_map, row0 = cache.tma() if rt.options.prefill_attention != "tcgen05" else (None, 0)
+        if rt.options.prefill_attention == "ws" and not kv_map:
+            raise L.KernelError(f"prefill_attention = \"ws\" needs a page size that TMA can serve (a multiple of 8 that divides 64, or a multiple of 64), got {view.page_size}")
         if kv_map:
             L.call("ib_attention_prefill_ws", *args, kv_map, row0, rt.status.data_ptr(), stream)
         else:
-            L.call("ib_attention_prefill" if PREFILL_KERNEL == "mma" else "ib_attention_prefill_tc", *args, rt.status.data_ptr(), stream)
+            L.call("ib_attention_prefill_tc", *args, rt.status.data_ptr(), stream)
     return out

@@ -16,7 +16,7 @@ import torch
 from . import lib as L
 from . import ops
 
-SM_COUNT = 148
+FITTED_SM_COUNT = 148   # the part the cost model below was fitted on; every function takes the running device's count as an argument
 TOKEN_TILES = (16, 32, 64, 128, 256)
 
 L.register("ib_gemm_tcgen05", [L._p, L._p, L._p, L._i, L._i, L._i, L._i, L._i, L._i, L._p, L._p])
@@ -26,8 +26,9 @@ L.register("ib_gemm_swiglu_tcgen05_2cta", [L._p, L._p, L._p, L._i, L._i, L._i, L
 L.register("ib_gemm_tcgen05_2cta_add", [L._p, L._p, L._p, L._i, L._i, L._i, L._p, L._p])
 L.register("ib_gemm_qkv_tcgen05_2cta", [L._p, L._p, L._i, L._i, L._p, L._p, L._f, L._p, L._p, L._p, L._p, L._p, C.POINTER(L.KvView), L._i, L._i, L._p, L._p])
 
-PAIR_MIN_TOKENS = 129    # the fused gate/up product runs on the persistent CTA-pair kernel (csrc/gemm_tcgen05_2cta.cu) from here on whatever its size
-PAIR_ALWAYS_TOKENS = 2048   # and every product from here on; between the two, `plan` decides by its cost model
+# Runtime options that steer the choice (config/runtime_options.py): `pair_min_tokens` (129: the fused gate/up product runs on the
+# persistent CTA-pair kernel, csrc/gemm_tcgen05_2cta.cu, from here on whatever its size), `pair_always_tokens` (2,048: every
+# product from here on; between the two, `plan` decides by its cost model) and `fuse_qkv_epilogue`.
 
 
 def supports(k: int) -> bool:
@@ -35,7 +36,7 @@ def supports(k: int) -> bool:
 
 
 @functools.lru_cache(maxsize=4096)
-def choose(T: int, N: int, K: int, allow_split: bool = True) -> tuple[int, int, bool]:
+def choose(T: int, N: int, K: int, allow_split: bool = True, sm_count: int = FITTED_SM_COUNT) -> tuple[int, int, bool]:
     """(tokens per CTA, k-splits, wide) for up to 128 tokens: the smallest token tile that holds them, and the
     k-range split over CTAs until the GPU is full."""
     if T > 128:
@@ -43,7 +44,7 @@ def choose(T: int, N: int, K: int, allow_split: bool = True) -> tuple[int, int, 
     ktiles = -(-K // 64)
     bn = next(b for b in TOKEN_TILES if T <= b)
     tiles = -(-N // 128)
-    slots = SM_COUNT * (2 if bn <= 64 else 1)      # CTAs resident at once (two per SM for the small token tiles)
+    slots = sm_count * (2 if bn <= 64 else 1)      # CTAs resident at once (two per SM for the small token tiles)
     splits = 1
     if allow_split and tiles < slots:
         splits = max(1, min(slots // tiles, ktiles // 4, 16))
@@ -60,7 +61,7 @@ _MID = dict(rate=4.015e6, cap=250e3, t0=4.36, partial_bw=3.455e6, pair_rate=5.44
             speed={(256, True): 1.0, (256, False): 0.982, (128, True): 0.895, (128, False): 0.956})
 
 
-def single_variants(T: int, N: int, K: int):
+def single_variants(T: int, N: int, K: int, sm_count: int = FITTED_SM_COUNT):
     """The forms of the single-CTA kernel that `plan` weighs for more than 128 tokens: (tokens per CTA, k-splits, wide)."""
     ktiles = -(-K // 64)
     for bn in (128, 256):
@@ -70,61 +71,58 @@ def single_variants(T: int, N: int, K: int):
                 if sp > max(1, ktiles // 4) or -(-ktiles // per) != sp:   # at least four k-tiles a split, and none empty
                     continue
                 ctas = -(-N // (256 if wide else 128)) * -(-T // bn) * sp
-                if sp > 1 and ctas > 4 * SM_COUNT:
+                if sp > 1 and ctas > 4 * sm_count:
                     continue
                 yield bn, sp, wide
 
 
 @functools.lru_cache(maxsize=4096)
-def plan_costs(T: int, N: int, K: int) -> tuple:
+def plan_costs(T: int, N: int, K: int, sm_count: int = FITTED_SM_COUNT) -> tuple:
     """(expected us of the CTA-pair kernel, expected us of the best single-CTA form, that form) for 129 <= T < 2048."""
     m = _MID
     tiles = -(-N // 256) * -(-T // 256)
-    active = min(tiles, SM_COUNT // 2) * 2
-    pair = -(-tiles // (SM_COUNT // 2)) * max(256 * 256 * K * 2 / (2 * m["pair_rate"]), 256 * K * 2 / min(m["pair_cap"], m["hbm"] / active)) + m["t0"]
+    active = min(tiles, sm_count // 2) * 2
+    pair = -(-tiles // (sm_count // 2)) * max(256 * 256 * K * 2 / (2 * m["pair_rate"]), 256 * K * 2 / min(m["pair_cap"], m["hbm"] / active)) + m["t0"]
     best = (float("inf"), None)
     ktiles = -(-K // 64)
-    for bn, sp, wide in single_variants(T, N, K):
+    for bn, sp, wide in single_variants(T, N, K, sm_count):
         rows = 256 if wide else 128
         ctas = -(-N // rows) * -(-T // bn) * sp
         kc = -(-ktiles // sp) * 64
         mma = rows * bn * kc * 2 / (m["rate"] * m["speed"][(bn, wide)])
-        copy = (rows + min(bn, T)) * kc * 2 / min(m["cap"], m["hbm"] / min(ctas, SM_COUNT))
-        t = -(-ctas // SM_COUNT) * max(mma, copy) + m["t0"] + (sp * T * N * 4 / m["partial_bw"] if sp > 1 else 0.0)
+        copy = (rows + min(bn, T)) * kc * 2 / min(m["cap"], m["hbm"] / min(ctas, sm_count))
+        t = -(-ctas // sm_count) * max(mma, copy) + m["t0"] + (sp * T * N * 4 / m["partial_bw"] if sp > 1 else 0.0)
         if t < best[0]:
             best = (t, (bn, sp, wide))
     return pair, best[0], best[1]
 
 
-def plan(T: int, N: int, K: int) -> tuple:
+def plan(T: int, N: int, K: int, sm_count: int = FITTED_SM_COUNT) -> tuple:
     """For 129 <= T < 2048: ("pair",) or ("single", tokens per CTA, k-splits, wide), whichever the cost model
-    expects to be faster. Depends on the sizes only."""
-    pair, single, form = plan_costs(T, N, K)
+    expects to be faster. Depends on the sizes (and the device's SM count) only."""
+    pair, single, form = plan_costs(T, N, K, sm_count)
     return ("pair",) if pair <= single else ("single",) + form
 
 
-QKV_EPILOGUE = True   # the q/k/v projection may finish norm, rotation and cache write in its epilogue (CTA-pair kernel, head size 128)
-
-
-def qkv_in_epilogue(T: int, N: int, K: int) -> bool:
+def qkv_in_epilogue(rt, T: int, N: int, K: int) -> bool:
     """Whether the q/k/v projection of T tokens runs as the CTA-pair kernel with the q/k norm, the rotation and the
     cache write in its epilogue: from 2,048 tokens always; from 129 when that is expected to take no longer than the
     best plain product followed by the kernel it saves (about 3 us + 20 ns a token inside a step)."""
-    if not QKV_EPILOGUE or T <= 128:
+    if not rt.options.qkv_epilogue or T <= 128:
         return False
-    if T >= PAIR_ALWAYS_TOKENS:
+    if T >= rt.options.pair_always_tokens:
         return True
-    pair, single, _ = plan_costs(T, N, K)
+    pair, single, _ = plan_costs(T, N, K, rt.sm_count)
     return pair <= single + 3.0 + 0.02 * T
 
 
-def balanced_portion(matrices, nominal: int = 2048) -> int:
+def balanced_portion(matrices, nominal: int = 2048, sm_count: int = FITTED_SM_COUNT) -> int:
     """A prompt-portion size near `nominal` (a multiple of 256 between 3/4 and 5/4 of it) whose 256 x 256 tiles fill
     whole rounds of the CTA pairs best, for the [N, K] matrices of a layer: the time a token costs is taken as the sum
     over the matrices of K x rounds x 74 tiles / tokens. The CTA-pair products work in rounds of 74 tiles, and a portion
     that ends in a nearly empty round pays for it (measured: 14B shape 45.2 k tok/s at 1,792 tokens against 41.3 k at
     2,048; 32B 19.0 against 18.1 k; 8B 80.8 k at 2,304 against 79.9 k). Ties go to the size nearest to `nominal`."""
-    pairs = SM_COUNT // 2
+    pairs = sm_count // 2
     best = None
     for T in range(max(256, nominal * 3 // 4 // 256 * 256), nominal * 5 // 4 + 1, 256):
         cost = sum(k * -(-(-(-n // 256) * -(-T // 256)) // pairs) for n, k in matrices) / T
@@ -183,7 +181,7 @@ def gemm_qkv_pair(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, kv: "op
 
 def linear(rt, x: torch.Tensor, lw, allow_split: bool = True, add_to: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
     T = x.shape[0]
-    how = ("pair",) if T >= PAIR_ALWAYS_TOKENS else (plan(T, lw.n, lw.k) if T > 128 else None)
+    how = ("pair",) if T >= rt.options.pair_always_tokens else (plan(T, lw.n, lw.k, rt.sm_count) if T > 128 else None)
     if how is not None and how[0] == "single":
         _, bn, splits, wide = how
         out = rt.empty((splits, T, lw.n), torch.float32)
@@ -196,7 +194,7 @@ def linear(rt, x: torch.Tensor, lw, allow_split: bool = True, add_to: Optional[t
         out = rt.empty((1, T, lw.n), torch.float32)
         gemm_pair(x, lw.weight, out[0], rt.status)
         return out
-    bn, splits, wide = choose(T, lw.n, lw.k, allow_split)
+    bn, splits, wide = choose(T, lw.n, lw.k, allow_split, rt.sm_count)
     out = rt.empty((splits, T, lw.n), torch.float32)
     gemm(x, lw.weight, out, bn, splits, rt.status, wide)
     return out
@@ -213,14 +211,14 @@ def swiglu_supported(T: int, k: int, inter: int = 0) -> bool:
     return supports(k) and (T > 64 or (T > 32 and -(-inter // 256) >= PAIR_SWIGLU_MIN_TILES))
 
 
-def gemm_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tensor, status: torch.Tensor, bn: int | None = None) -> None:
+def gemm_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tensor, status: torch.Tensor, bn: int | None = None, pair_min_tokens: int = 129) -> None:
     """act [T, I] bfloat16 = silu(x gate^T) * (x up^T) with w_gate_up [2I, K] = gate rows then up rows."""
     T, K = x.shape
     I = w_gate_up.shape[0] // 2
     ops._check("x", x, torch.bfloat16)
     ops._check("w_gate_up", w_gate_up, torch.bfloat16, (2 * I, K))
     ops._check("act", act, torch.bfloat16, (T, I))
-    if bn is None and (T >= PAIR_MIN_TOKENS or (T > 32 and -(-I // 256) >= PAIR_SWIGLU_MIN_TILES)):
+    if bn is None and (T >= pair_min_tokens or (T > 32 and -(-I // 256) >= PAIR_SWIGLU_MIN_TILES)):
         L.call("ib_gemm_swiglu_tcgen05_2cta", x.data_ptr(), w_gate_up.data_ptr(), act.data_ptr(), T, I, K, status.data_ptr(), ops._stream())
         return
     if bn is None:

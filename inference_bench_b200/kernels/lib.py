@@ -51,7 +51,7 @@ _SIGNATURES = {
     "ib_qk_norm_rope_kv": [_p, _i, _ll, _p, _p, _f, _p, _p, _i, _p, _p, _p, _i, C.POINTER(KvView), _i, _i, _i, _p, _p],
     "ib_attention_generic": [_p, _i, C.POINTER(KvView), _p, _p, _i, _f, _p, _i, _i, _p, _p],
     "ib_gemm_simt": [_p, _i, _p, _i, _p, _i, _i, _i, _p],
-    "ib_sample_rows": [_p, _i, _i, _p, _p, _p, _p],
+    "ib_sample_rows": [_p, _i, _i, _p, _p, _p, _p, _p],
     "ib_advance_rows": [_p, _p, _p, _p, _p, _p, _p, _i, _i, _p],
 }
 

@@ -214,14 +214,16 @@ def sample_chunks(vocab: int) -> int:
     return int(L.load().ib_sample_chunks(int(vocab)))
 
 
-def sample_rows(logits: torch.Tensor, params: torch.Tensor, tokens: torch.Tensor) -> None:
-    """params int32 [rows, 6] = (inv_temp bits, seed, step, top_k, top_p bits, min_p bits)."""
+def sample_rows(logits: torch.Tensor, params: torch.Tensor, tokens: torch.Tensor, status: Optional[torch.Tensor] = None) -> None:
+    """params int32 [rows, 6] = (inv_temp bits, seed, step, top_k, top_p bits, min_p bits). With `status` (the
+    device status word) tokens has rows + 1 entries and the last one receives the word's value, so one
+    transfer brings the host both the tokens and whether a kernel of the step reported a fault."""
     rows, V = logits.shape
     _check("logits", logits, torch.float32)
     _check("params", params, torch.int32, (rows, 6))
-    _check("tokens", tokens, torch.int32, (rows,))
+    _check("tokens", tokens, torch.int32, (rows + (1 if status is not None else 0),))
     scratch = torch.empty(rows * (1 + 2 * sample_chunks(V)), dtype=torch.float32, device=logits.device)
-    L.call("ib_sample_rows", logits.data_ptr(), rows, V, params.data_ptr(), tokens.data_ptr(), scratch.data_ptr(), _stream())
+    L.call("ib_sample_rows", logits.data_ptr(), rows, V, params.data_ptr(), tokens.data_ptr(), scratch.data_ptr(), _ptr(status), _stream())
 
 
 def advance_rows(sampled: torch.Tensor, token_in: torch.Tensor, positions: torch.Tensor, pos0: torch.Tensor, params: torch.Tensor,

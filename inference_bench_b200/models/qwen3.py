@@ -42,4 +42,5 @@ def qwen3_plan(c: Qwen3Config) -> ModelPlan:
 
 
 # `Qwen3MoeForCausalLM` / `qwen3_moe` are deliberately not registered: this engine has the dense decoder only.
-register_architecture(["Qwen3ForCausalLM", "qwen3"], Qwen3Config.from_dict, qwen3_plan)
+register_architecture(["Qwen3ForCausalLM", "qwen3"], Qwen3Config.from_dict, qwen3_plan,
+                      traits={"attention": "gqa", "qk_norm": True, "norm": "rmsnorm", "norm_unit_offset": False, "rope_style": "neox", "activation": "swiglu"})

@@ -67,13 +67,30 @@ class Decoder:
             p.bind(weights, rt)
 
     # ------------------------------------------------------------ one step
+    @staticmethod
+    def _residual_rows(ctx, x: torch.Tensor, pending: Optional[torch.Tensor]) -> torch.Tensor:
+        """The residual stream at the wanted rows as it stands after a block: x plus the contribution the block left
+        for the next norm to add. Debugging only (a step with `ctx.trace` set): it copies with torch, off the serving path,
+        like the reference's per-layer trace buffer (crates/specrt/src/runtime.rs:1406-1412, 2480-2504)."""
+        rows = ctx.logit_rows.long()
+        out = x.index_select(0, rows)
+        if pending is not None:
+            for p in range(pending.shape[0]):
+                out = out + pending[p].index_select(0, rows)
+        return out
+
     def forward(self, ctx) -> Optional[torch.Tensor]:
         """Runs the step's tokens through the schedule; returns float32 logits [K, V] at the wanted
         rows, or None when no row is wanted (the caches are still filled)."""
         x = self.embedding.forward(ctx)
         pending = None
+        trace = ctx.trace
+        if trace is not None:
+            trace.append(self._residual_rows(ctx, x, None))
         for i, e in enumerate(self.plan.schedule):
             pending = self.blocks[e.layer].forward(ctx, x, pending, ctx.caches[i] if ctx.caches else None)
+            if trace is not None:
+                trace.append(self._residual_rows(ctx, x, pending))
         if ctx.logit_rows.shape[0] == 0:
             return None
         h = self.final_norm.forward(ctx, x, pending, rows=ctx.logit_rows)

@@ -49,6 +49,7 @@ class ModelPlan:
     final_norm: PartSpec
     head: PartSpec
     ignored_tensors: tuple[str, ...] = ()   # names a checkpoint may carry that the model does not read
+    root: str = "model"                     # the prefix the decoder's tensors are named under; the loader probes a checkpoint for its other usual places
 
     def validate(self) -> None:
         for i, e in enumerate(self.schedule):

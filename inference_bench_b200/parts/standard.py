@@ -207,7 +207,7 @@ class LinearHead(base.Head):
         self.w = None
 
     def weight_specs(self):
-        return [] if self.tied_to else [WeightSpec(self.name, (self.vocab, self.hidden))]
+        return [WeightSpec(self.tied_to or self.name, (self.vocab, self.hidden))]   # tied: the embedding's table, read by both
 
     def bind(self, weights, rt):
         self.w = rt.matrix(weights[self.tied_to or self.name])

@@ -20,15 +20,18 @@ class Architecture:
     config_from_dict: Callable[[Mapping[str, Any]], Any]
     plan: Callable[[Any], ModelPlan]
     config_to_dict: Callable[[Any], dict]
+    traits: Mapping[str, Any]     # what the architecture does where config.json has no key for it (checked against a model spec's claims)
 
 
 _ARCHITECTURES: dict[str, Architecture] = {}
 
 
-def register_architecture(names, config_from_dict, plan, config_to_dict=None) -> Architecture:
-    """Register one model under every name it goes by (`architectures` entries and `model_type`)."""
+def register_architecture(names, config_from_dict, plan, config_to_dict=None, traits=None) -> Architecture:
+    """Register one model under every name it goes by (`architectures` entries and `model_type`).
+    `traits` says what the architecture does where config.json has no key (for instance
+    {"qk_norm": True, "rope_style": "neox"}); a TOML model spec that claims otherwise is refused."""
     names = [names] if isinstance(names, str) else list(names)
-    arch = Architecture(names[0], config_from_dict, plan, config_to_dict or (lambda c: c.to_dict()))
+    arch = Architecture(names[0], config_from_dict, plan, config_to_dict or (lambda c: c.to_dict()), dict(traits or {}))
     for n in names:
         _ARCHITECTURES[n] = arch
     return arch

@@ -5,7 +5,8 @@ import pytest
 
 from inference_bench_b200 import models  # noqa: F401
 from inference_bench_b200.config import ConfigError
-from inference_bench_b200.config.qwen3 import Qwen3Config, read_config_json
+from inference_bench_b200.config.qwen3 import Qwen3Config
+from inference_bench_b200.config.spec import read_config_json
 from inference_bench_b200.engine.model import plan_from_config
 from inference_bench_b200.registry import known_architectures, resolve
 from tiny_configs import CONFIGS

@@ -137,7 +137,7 @@ def test_gemm_tcgen05_cta_pairs(status, T, N, K):
 def test_gemm_swiglu_cta_pairs(status, T, I, K):
     """The fused gate/up product on CTA pairs: from 129 tokens, and from 33 when the intermediate size gives 40 tiles."""
     from inference_bench_b200.kernels import gemm_tcgen05 as G
-    assert T >= G.PAIR_MIN_TOKENS or (T > 32 and -(-I // 256) >= G.PAIR_SWIGLU_MIN_TILES)
+    assert T >= 129 or (T > 32 and -(-I // 256) >= G.PAIR_SWIGLU_MIN_TILES)
     x = (torch.randn(T, K, generator=_g(5)) * 0.5).to(torch.bfloat16).to(DEV)
     w = (torch.randn(2 * I, K, generator=_g(6)) * 0.2).to(torch.bfloat16).to(DEV)
     act = torch.full((T, I), float("nan"), dtype=torch.bfloat16, device=DEV)
@@ -284,16 +284,16 @@ def test_attention_generic(status, dtype, window):
 
 @pytest.mark.parametrize("hd,heads,kvh,page", [(128, 8, 2, 16), (64, 5, 1, 32), (128, 16, 1, 16), (64, 4, 4, 8)])
 @pytest.mark.parametrize("window", [None, 100])
-@pytest.mark.parametrize("prefill", ["ws", "tcgen05", "mma"])
-def test_attention_tensor_core_kernels(status, monkeypatch, hd, heads, kvh, page, window, prefill):
+@pytest.mark.parametrize("prefill", ["ws", "tcgen05"])
+def test_attention_tensor_core_kernels(status, hd, heads, kvh, page, window, prefill):
     """Decode slices and prefill tiles (either prefill kernel) through the engine's dispatch, against the plain reference."""
+    from inference_bench_b200.config.runtime_options import RuntimeOptions
     from inference_bench_b200.engine.context import Segment, build_context
     from inference_bench_b200.engine.runtime import Runtime
     from inference_bench_b200.kernels import attention
-    monkeypatch.setattr(attention, "PREFILL_KERNEL", prefill)
     shapes = [(300, 300), (500, 70), (1000, 1), (129, 1), (128, 1), (5, 2), (260, 1), (64, 64), (65, 65)]
     q, view, pos, seg, ref, _ = _attention_case(torch.bfloat16, heads, kvh, hd, page, window, shapes, 12, needle=True)
-    rt = Runtime(DEV, "bfloat16")
+    rt = Runtime(DEV, options=RuntimeOptions(prefill_attention=prefill))
     segs = [Segment(i, i, L - n, [0] * n) for i, (L, n) in enumerate(shapes)]
     ctx = build_context(rt, segs)
     assert torch.equal(ctx.positions, pos) and torch.equal(ctx.seg_of_token, seg)
@@ -310,21 +310,18 @@ def test_attention_tensor_core_kernels(status, monkeypatch, hd, heads, kvh, page
 
 
 @pytest.mark.parametrize("tiles_per_slice", [1, 2, 8])
-@pytest.mark.parametrize("kernel,tma,page,hd", [("stream", False, 16, 128), ("stream", False, 64, 64), ("stream", False, 8, 128), ("stream", False, 128, 128),
-                                                ("stream", False, 32, 64), ("stream", False, 24, 64), ("split", True, 16, 128), ("split", True, 64, 64),
-                                                ("split", True, 8, 128), ("split", False, 16, 128), ("split", False, 24, 64), ("split", False, 128, 64)])
-def test_attention_decode_slices_of_several_tiles(status, monkeypatch, tiles_per_slice, kernel, tma, page, hd):
-    """Both decode kernels (CTAs that stay and a ring filled by TMA; one CTA per slice, filled by TMA
-    or by cp.async) walking 1, 2 or 8 tiles per slice, windows starting inside a slice included. A page
-    size of 24 can only be copied by cp.async, so it takes the kernel with one CTA per slice either way."""
+@pytest.mark.parametrize("kernel,page,hd", [("stream", 16, 128), ("stream", 64, 64), ("stream", 8, 128), ("stream", 128, 128), ("stream", 32, 64),
+                                            ("auto", 24, 64), ("split", 16, 128), ("split", 64, 64), ("split", 8, 128), ("split", 24, 64), ("split", 128, 64)])
+def test_attention_decode_slices_of_several_tiles(status, monkeypatch, tiles_per_slice, kernel, page, hd):
+    """Both decode kernels (CTAs that stay and a ring filled by TMA; one CTA per slice, filled by cp.async)
+    walking 1, 2 or 8 tiles per slice, windows starting inside a slice included. A page size of 24 can only
+    be copied by cp.async, so "auto" takes the kernel with one CTA per slice there (and "stream" refuses it)."""
+    from inference_bench_b200.config.runtime_options import RuntimeOptions
     from inference_bench_b200.engine.context import Segment, build_context
     from inference_bench_b200.engine.runtime import Runtime
     from inference_bench_b200.kernels import attention
     from inference_bench_b200.kernels import lib as L
-    monkeypatch.setattr(attention, "decode_tiles_per_slice", lambda *a: tiles_per_slice)
-    monkeypatch.setattr(attention, "STREAM_TILES_PER_SLICE", tiles_per_slice)
-    monkeypatch.setattr(attention, "DECODE_KERNEL", kernel)
-    monkeypatch.setattr(attention, "USE_TMA", tma)
+    options = RuntimeOptions(decode_attention=kernel, stream_tiles_per_slice=tiles_per_slice, split_tiles_per_slice=tiles_per_slice)
     called = []
     real_call = L.call
     monkeypatch.setattr(L, "call", lambda name, *a: (called.append(name), real_call(name, *a))[1])
@@ -333,26 +330,30 @@ def test_attention_decode_slices_of_several_tiles(status, monkeypatch, tiles_per
     for window in (None, 300):
         q, view, pos, seg, ref, _ = _attention_case(torch.bfloat16, heads, kvh, hd, page, window, shapes, 21, needle=True)
         assert (view.tma()[0] is not None) == (page != 24)
-        rt = Runtime(DEV, "bfloat16")
+        rt = Runtime(DEV, options=options)
         ctx = build_context(rt, [Segment(i, i, L_ - n, [0] * n) for i, (L_, n) in enumerate(shapes)])
         out = attention.paged_attention(ctx, q, view, heads, window, 1 / math.sqrt(hd))
         rt.check_status()
         err = (out.cpu().double() - ref).abs()
         assert err.max() <= 1.5e-2 * ref.abs().max(), f"row {int(err.max(dim=1).values.argmax())} is off by {err.max():.3e}"
-    assert called[-1] == ("ib_attention_decode_stream" if kernel == "stream" and page != 24 else "ib_attention_decode")
+    assert called[-1] == ("ib_attention_decode_stream" if kernel == "stream" else "ib_attention_decode")
+    if page == 24:
+        with pytest.raises(L.KernelError, match="page size"):
+            attention.paged_attention(build_context(Runtime(DEV, options=RuntimeOptions(decode_attention="stream")), [Segment(0, 0, 999, [0])]),
+                                      q[:1], view, heads, None, 1 / math.sqrt(hd))
 
 
-def test_attention_decode_stream_many_units_per_cta(status, monkeypatch):
+def test_attention_decode_stream_many_units_per_cta(status):
     """More units than CTAs that fit the device, with contexts of very different lengths: every CTA
     of the streaming kernel walks several units, and its ring runs across their ends."""
+    from inference_bench_b200.config.runtime_options import RuntimeOptions
     from inference_bench_b200.engine.context import Segment, build_context
     from inference_bench_b200.engine.runtime import Runtime
     from inference_bench_b200.kernels import attention
     heads, kvh, hd, page = 8, 8, 128, 16
     shapes = [(L_, 1) for L_ in (1500, 3, 700, 64, 1100, 129, 1, 900, 1300, 450, 31, 640)]
-    rt = Runtime(DEV, "bfloat16")
     for fixed, window in ((1, None), (0, None), (0, 500), (0, 70)):   # slices of one tile at fixed places; each token's keys in equal parts
-        monkeypatch.setattr(attention, "STREAM_TILES_PER_SLICE", fixed)
+        rt = Runtime(DEV, options=RuntimeOptions(stream_tiles_per_slice=fixed))
         q, view, pos, seg, ref, _ = _attention_case(torch.bfloat16, heads, kvh, hd, page, window, shapes, 22, needle=True)
         ctx = build_context(rt, [Segment(i, i, L_ - n, [0] * n) for i, (L_, n) in enumerate(shapes)])
         out = attention.paged_attention(ctx, q, view, heads, window, 1 / math.sqrt(hd))
@@ -365,13 +366,12 @@ def test_attention_decode_stream_many_units_per_cta(status, monkeypatch):
 def test_stream_slices(n_dec, kv_heads, max_keys, want):
     from inference_bench_b200.kernels import attention
     if torch.cuda.get_device_properties(DEV).multi_processor_count == 148:
-        assert attention.stream_slices(n_dec, kv_heads, max_keys, torch.device(DEV)) == want
+        assert attention.stream_slices(n_dec, kv_heads, max_keys, 148) == want
 
 
 @pytest.mark.parametrize("hd,page,heads,kvh,parts,norms,rope,window", [(128, 16, 8, 2, 3, True, True, None), (64, 64, 6, 2, 1, True, True, 300),
                                                                        (128, 64, 16, 1, 2, False, True, None), (64, 8, 4, 4, 2, True, False, 100)])
-def test_attention_decode_fused_equals_the_two_steps(status, monkeypatch, hd, page, heads, kvh, parts, norms, rope, window):
-    monkeypatch.setattr("inference_bench_b200.kernels.attention.FUSE_DECODE_MAX_PAIRS", 1 << 30)
+def test_attention_decode_fused_equals_the_two_steps(status, hd, page, heads, kvh, parts, norms, rope, window):
     """Decoded tokens through the fused kernel (norm, rotation, cache write and attention in one) against
     the q/k kernel followed by the decode kernel, and the cache rows both leave behind."""
     from inference_bench_b200.engine.context import Segment, build_context
@@ -384,7 +384,8 @@ def test_attention_decode_fused_equals_the_two_steps(status, monkeypatch, hd, pa
     qkv = (torch.randn(parts, T, R, generator=_g(32)) * 0.7).to(DEV)
     qw = (1 + 0.1 * torch.randn(hd, generator=_g(33))).to(DEV) if norms else None
     kw = (1 + 0.1 * torch.randn(hd, generator=_g(34))).to(DEV) if norms else None
-    rt = Runtime(DEV, "bfloat16")
+    from inference_bench_b200.config.runtime_options import RuntimeOptions
+    rt = Runtime(DEV, options=RuntimeOptions(fuse_decode_max_pairs=1 << 30))
     ctx = build_context(rt, [Segment(i, i, L_ - 1, [0]) for i, L_ in enumerate(lengths)])
     cos = sin = None
     if rope:

@@ -95,12 +95,14 @@ def test_a_prompt_portion_gives_the_same_bits_every_time(shape, page, tokens):
         eng.cache.release("r")
         return out
 
-    assert lib.ib_pdl_enabled() == 1
-    lib.ib_set_pdl(0)
+    early = eng.rt.options
+    assert early.pdl
+    eng.rt.options = early.merged(pdl=False)   # a step applies its runtime's options to the library when it starts
     try:
         ref = once()
+        assert lib.ib_pdl_enabled() == 0
     finally:
-        lib.ib_set_pdl(1)
+        eng.rt.options = early
     different = sum(not torch.equal(once(), ref) for _ in range(60))
     assert different == 0, f"{different} of 60 runs differ from the run with one kernel after the other"
 
@@ -138,11 +140,13 @@ def test_mixed_steps_give_the_same_bits_every_time():
             eng.cache.release(k)
         return outs
 
-    lib.ib_set_pdl(0)
+    early = eng.rt.options
+    eng.rt.options = early.merged(pdl=False)
     try:
         ref = replay()
+        assert lib.ib_pdl_enabled() == 0
     finally:
-        lib.ib_set_pdl(1)
+        eng.rt.options = early
     for i in range(8):
         got = replay()
         diff = [j for j, (a, b) in enumerate(zip(ref, got)) if not torch.equal(a, b)]

@@ -121,3 +121,127 @@ def test_random_weights_mode(tmp_path):
     norm = ta["model.layers.0.input_layernorm.weight"].float()
     assert 0.89 <= norm.min() and norm.max() <= 1.11 and norm.std() > 0.03              # 1 + U(-0.1, 0.1)
     assert all(t.dtype == torch.bfloat16 for t in ta.values())
+
+
+# ------------------------------------------------------------------------------------------ names, roots, strictness, streaming
+class _HostRuntime:
+    """Stands for the device-side runtime where a test only needs what `bind` asks of it."""
+
+    def __init__(self):
+        from inference_bench_b200.config.runtime_options import RuntimeOptions
+        self.device, self.options, self.act_dtype = torch.device("cpu"), RuntimeOptions(), torch.bfloat16
+        self.live = self.peak = 0
+
+    def upload(self, t, dtype=None):
+        return t if dtype is None or t.dtype == dtype else t.to(dtype)
+
+    def matrix(self, w):
+        from inference_bench_b200.engine.runtime import LinearWeights
+        return LinearWeights(self.upload(w, self.act_dtype), w.shape[0], w.shape[1])
+
+    def vector(self, w):
+        return self.upload(w, torch.float32)
+
+
+def test_rename_rules_and_the_decoders_other_roots(model_dirs, tmp_path):
+    from inference_bench_b200.weights.loader import public_names
+    dec = _decoder("B")
+    tensors = _all(model_dirs["B"])
+    want = load_weights(model_dirs["B"], dec.weight_specs())
+    # the decoder saved inside a larger model: both usual places of its root (crates/specrt/src/weights.rs:365-375)
+    for alt in ("model.language_model", "language_model.model"):
+        moved = {(alt + n[len("model"):] if n.startswith("model.") else n): t for n, t in tensors.items()}
+        moved["model.visual.patch_embed.weight"] = torch.zeros(4, 4, dtype=torch.bfloat16)      # something the text model does not read
+        write_safetensors(tmp_path / "model.safetensors", moved)
+        with pytest.raises(WeightError) as e:
+            load_weights(tmp_path, dec.weight_specs())
+        assert e.value.unexpected == ["model.visual.patch_embed.weight"] and not e.value.missing      # strict: the extra tensor is an error
+        got = load_weights(tmp_path, dec.weight_specs(), strict=False)
+        assert set(got) == set(want) and all(torch.equal(got[n], want[n]) for n in want)
+    # rename rules: parts of names replaced (crates/specrt/src/weights.rs:226-240)
+    odd = {n.replace("model.layers.", "transformer.h.").replace("self_attn", "attn"): t for n, t in tensors.items()}
+    write_safetensors(tmp_path / "model.safetensors", odd)
+    with pytest.raises(WeightError, match="missing tensors"):
+        load_weights(tmp_path, dec.weight_specs())
+    got = load_weights(tmp_path, dec.weight_specs(), rules={"transformer.h.": "model.layers.", ".attn.": ".self_attn."})
+    assert all(torch.equal(got[n], want[n]) for n in want)
+    with pytest.raises(CheckpointError, match="both renamed to"):
+        public_names(["a.x", "b.x"], ["c.x"], {"a.": "c.", "b.": "c."})
+
+
+def test_unexpected_tensors_are_a_note_unless_strict(model_dirs, tmp_path):
+    from inference_bench_b200.weights.loader import stream_into
+    dec = _decoder("A")
+    tensors = _all(model_dirs["A"])
+    tensors["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(8)
+    write_safetensors(tmp_path / "model.safetensors", tensors)
+    said = []
+    assert stream_into(dec, _HostRuntime(), tmp_path, say=said.append) == ["model.layers.0.self_attn.rotary_emb.inv_freq"]
+    assert len(said) == 1 and "1 tensor(s) of the checkpoint are not read" in said[0]
+    with pytest.raises(WeightError, match="unexpected tensors"):
+        stream_into(_decoder("A"), _HostRuntime(), tmp_path, strict=True)
+    # and a missing tensor still lists the unexpected one beside it: one error says everything
+    del tensors["model.norm.weight"]
+    write_safetensors(tmp_path / "model.safetensors", tensors)
+    with pytest.raises(WeightError) as e:
+        stream_into(_decoder("A"), _HostRuntime(), tmp_path)
+    assert e.value.missing == ["model.norm.weight"] and e.value.unexpected == ["model.layers.0.self_attn.rotary_emb.inv_freq"]
+
+
+def test_weights_are_streamed_part_by_part(model_dirs, monkeypatch):
+    """While the model is bound, at most one part's source tensors are alive beside what is already bound; a tied
+    embedding is read once and shared by the embedding and the head."""
+    from inference_bench_b200.weights import loader
+    dec = _decoder("A")   # tied
+    reads, alive, most = [], [], [0]
+    real = loader.WeightStore.read
+
+    def counting(self, name, device=None):
+        t = real(self, name, device)
+        reads.append(name)
+        alive.append(__import__("weakref").ref(t))
+        most[0] = max(most[0], sum(r() is not None for r in alive))
+        return t
+
+    monkeypatch.setattr(loader.WeightStore, "read", counting)
+    loader.stream_into(dec, _HostRuntime(), model_dirs["A"], say=False)
+    assert sorted(reads) == sorted(s.name for s in dec.weight_specs())            # every tensor once, the tied table too
+    assert dec.head.w.weight.data_ptr() == dec.embedding.table.weight.data_ptr()
+    # bound tensors stay alive where binding keeps the stored tensor itself (bfloat16 matrices that need no fusing): what must
+    # not happen is that the q, k, v, gate and up sources of every layer are alive at once
+    per_layer_sources = 5
+    layers = len(dec.blocks)
+    kept = sum(r() is not None for r in alive)
+    assert kept <= len(reads) - per_layer_sources * layers
+    assert most[0] <= kept + 3
+
+
+def test_the_reference_checkpoints_header_is_what_the_model_asks_for():
+    """The names, stored dtypes and shapes of the published Qwen3-0.6B checkpoint, as the reference recorded them
+    (crates/specrt/tests/fixtures/headers/qwen3-0.6b.json; it checks its own plan against them in
+    crates/specrt/src/plan.rs:569-633), against what this engine's decoder asks of a loader for that model's config.json."""
+    from pathlib import Path
+    data = Path(__file__).parent / "data" / "reference"
+    header = {name: (dtype, tuple(shape)) for name, dtype, shape in json.loads((data / "qwen3-0.6b.header.json").read_text())}
+    _, plan = plan_from_config(json.loads((data / "qwen3-0.6b.config.json").read_text()))
+    specs = {s.name: s for s in Decoder(plan).weight_specs()}
+    assert plan.ignored_tensors == ("lm_head.weight",)                 # tied: the stored head is not read (crates/specrt/src/weights.rs:1396-1405)
+    assert set(header) - set(plan.ignored_tensors) == set(specs)
+    for name, s in specs.items():
+        assert header[name][1] == tuple(s.shape), name
+        assert header[name][0] == "BF16"
+    assert sum(s.role == "norm" for s in specs.values()) == 28 * 4 + 1 and len(specs) == 28 * 11 + 2
+
+
+def test_a_checkpoint_written_by_the_official_writer_loads(tmp_path):
+    """crates/specrt/tests/fixtures/tiny-qwen3-sliding: config.json with rope_parameters, layer_types and a window; tensors in
+    the official writer's order and header layout. The repo's own reader and the test-side reader agree on every value."""
+    from pathlib import Path
+    folder = Path(__file__).parent / "data" / "reference" / "tiny-qwen3-sliding"
+    cfg, plan = plan_from_config(json.loads((folder / "config.json").read_text()))
+    assert cfg.rope_theta == 10000.0 and cfg.head_dim == 64 and cfg.sliding_window == 16
+    assert cfg.layer_types == ("sliding_attention", "full_attention", "sliding_attention", "full_attention")
+    dec = Decoder(plan)
+    w = load_weights(folder, dec.weight_specs(), plan.ignored_tensors)       # strict: nothing missing, unexpected or misshapen
+    plain = read_safetensors(folder / "model.safetensors")
+    assert set(plain) == set(w) and all(torch.equal(w[n].float(), plain[n]) for n in w)
