@@ -67,8 +67,21 @@ class _Request:
 
 @dataclass
 class StateView:
-    """Fixed-size state of one execution: `tensor[slot]` belongs to the request in that slot."""
+    """Fixed-size state of one execution: `tensor[slot]` belongs to the request in that slot.
+
+    A mixer reads and writes the state of the step's segments through `gather` and `scatter`, which index with the
+    device copy of the segments' slots (`ctx.seg_slot`). That is the only form that is right inside a captured decode
+    step: there the host-side segments are placeholders and only the device arrays are filled in before each replay.
+    Padded rows of such a step carry the scratch slot (the tensor's last row), which no request ever owns."""
     tensor: Any
+
+    def gather(self, ctx) -> Any:
+        """The state of every segment of the step, [segments, *shape] (a copy)."""
+        return self.tensor.index_select(0, ctx.seg_slot.long())
+
+    def scatter(self, ctx, values) -> None:
+        """Store `values` [segments, *shape] as the new state of the step's segments."""
+        self.tensor.index_copy_(0, ctx.seg_slot.long(), values.to(self.tensor.dtype))
 
 
 class CacheManager:

@@ -247,6 +247,28 @@ def _paged(contexts, page_size, dtype, seed, entries=2, entry=1):
     return KvLayerView(pool.to(DEV), entry, torch.from_numpy(table).to(DEV)), table
 
 
+def _plant_window_edges(q, k, v, L, n, window, dtype, tile=128):
+    """Make an off-by-one at a window's edge show. For the last query of the segment, and for the first and last query
+    row of its last 128-row tile, at position p: the key at p - window (just outside) gets a direction aligned with that
+    query and a loud value, so it must stay invisible; the key at p - window + 1 (the oldest visible one) gets the same
+    direction and another loud value, so it must dominate that query's head 0. Letting the first in or dropping the
+    second moves the output by several units."""
+    used = set()
+    rows = sorted({n - 1, (n - 1) // tile * tile, max(0, (n - 1) // tile * tile - 1)})
+    for r in rows:
+        p = L - n + r
+        out_j, edge_j = p - window, p - window + 1
+        if out_j < 0 or edge_j in used or out_j in used or edge_j >= p:
+            continue
+        u = q[r, 0] / q[r, 0].norm()
+        k[out_j, 0] = (14.0 * u).to(dtype).float()
+        v[out_j, 0] = -9.0
+        k[edge_j, 0] = (12.0 * u).to(dtype).float()
+        v[edge_j, 0] = 7.0
+        used |= {out_j, edge_j}
+    return len(used) // 2
+
+
 def _attention_case(dtype, heads, kvh, hd, page_size, window, shapes, seed, needle=False):
     """shapes: (context length L, query tokens n) per segment; queries sit at the last n positions."""
     g = _g(seed)
@@ -259,6 +281,8 @@ def _attention_case(dtype, heads, kvh, hd, page_size, window, shapes, seed, need
             k[3, 0] = 6.0 * q[-1, 0] / q[-1, 0].norm() * math.sqrt(hd) / math.sqrt(hd) * 1.0
             k[3, 0] = k[3, 0].to(dtype).float()
             v[3, 0] = 5.0
+        if needle and window:
+            _plant_window_edges(q, k, v, L, n, window, dtype)
         q_full = torch.zeros(L, heads, hd)
         q_full[L - n:] = q
         ref = P.attention_scores(q_full.double(), k.double(), v.double(), window)[L - n:]
@@ -367,6 +391,73 @@ def test_stream_slices(n_dec, kv_heads, max_keys, want):
     from inference_bench_b200.kernels import attention
     if torch.cuda.get_device_properties(DEV).multi_processor_count == 148:
         assert attention.stream_slices(n_dec, kv_heads, max_keys, 148) == want
+
+
+@pytest.mark.parametrize("kernels", [("stream", "ws"), ("split", "tcgen05")])
+@pytest.mark.parametrize("hd,page", [(128, 16), (64, 64)])
+def test_window_edges_on_tile_slice_and_page_boundaries(status, kernels, hd, page):
+    """Windows chosen so that the oldest visible key of the decoded token (and of a prompt portion's last row) is the
+    first or the last key of a 64-key tile, of a slice and of a page, with the keys on both sides of the edge made loud
+    (see _plant_window_edges): the plain float64 attention on one side, the tensor-core kernels on the other."""
+    from inference_bench_b200.config.runtime_options import RuntimeOptions
+    from inference_bench_b200.engine.context import Segment, build_context
+    from inference_bench_b200.engine.runtime import Runtime
+    from inference_bench_b200.kernels import attention
+    decode, prefill = kernels
+    heads, kvh = 8, 2
+    L_ = 1000
+    for edge in (64, 63, 128, 127, 512, 511, 16, 15, 1, 936):       # position of the oldest visible key of the last query
+        window = L_ - edge
+        for tps in (0, 1, 2):
+            rt = Runtime(DEV, options=RuntimeOptions(decode_attention=decode, prefill_attention=prefill, stream_tiles_per_slice=tps,
+                                                     split_tiles_per_slice=max(tps, 1)))
+            shapes = [(L_, 1), (L_, 200), (L_, 129)]
+            q, view, pos, seg, ref, _ = _attention_case(torch.bfloat16, heads, kvh, hd, page, window, shapes, 50 + edge, needle=True)
+            ctx = build_context(rt, [Segment(i, i, L - n, [0] * n) for i, (L, n) in enumerate(shapes)])
+            out = attention.paged_attention(ctx, q, view, heads, window, 1 / math.sqrt(hd))
+            rt.check_status()
+            err = (out.cpu().double() - ref).abs()
+            assert ref.abs().max() > 5.0        # the planted edge key dominates somewhere
+            assert err.max() <= 1.5e-2 * ref.abs().max(), f"edge {edge}, {tps} tiles a slice: row {int(err.max(dim=1).values.argmax())} is off by {err.max():.3e}"
+
+
+@pytest.mark.parametrize("hd,page,window", [(128, 16, 300), (64, 64, 937), (128, 64, 64), (64, 8, 129)])
+def test_attention_decode_fused_window_edges(status, hd, page, window):
+    """The fused decode kernel (no norms, no rotation, so the queries are the projection's own values) with the keys on both
+    sides of each token's window edge made loud, against the plain float64 attention."""
+    from inference_bench_b200.config.runtime_options import RuntimeOptions
+    from inference_bench_b200.engine.context import Segment, build_context
+    from inference_bench_b200.engine.runtime import Runtime
+    from inference_bench_b200.kernels import attention
+    heads, kvh = 8, 2
+    lengths = [1000, 513, 2047, 700, window + 1, window + 2]
+    g = _g(61)
+    contexts, qs, refs = [], [], []
+    R = (heads + 2 * kvh) * hd
+    qkv = torch.zeros(1, len(lengths), R)
+    for s, L_ in enumerate(lengths):
+        k = torch.randn(L_, kvh, hd, generator=g).to(torch.bfloat16).float()
+        v = torch.randn(L_, kvh, hd, generator=g).to(torch.bfloat16).float()
+        q = torch.randn(1, heads, hd, generator=g).to(torch.bfloat16).float()
+        planted = _plant_window_edges(q, k, v, L_, 1, window, torch.bfloat16)
+        assert planted == (1 if L_ - 1 - window >= 0 else 0)
+        qkv[0, s] = torch.cat([q.reshape(-1), k[-1].reshape(-1), v[-1].reshape(-1)])      # the token's own key and value come from the projection
+        q_full = torch.zeros(L_, heads, hd, dtype=torch.float64)
+        q_full[-1] = q[0].double()
+        refs.append(P.attention_scores(q_full, k.double(), v.double(), window)[-1])
+        k2, v2 = k.clone(), v.clone()
+        k2[-1], v2[-1] = 31.0, 31.0                                                        # what the cache holds there before the step: must be overwritten
+        contexts.append((k2, v2))
+    view, _ = _paged(contexts, page, torch.bfloat16, 62)
+    rt = Runtime(DEV, options=RuntimeOptions(fuse_decode_max_pairs=1 << 30))
+    ctx = build_context(rt, [Segment(i, i, L_ - 1, [0]) for i, L_ in enumerate(lengths)])
+    out = attention.decode_fused(ctx, qkv.to(DEV), None, None, 1e-5, None, None, view, heads, window, 1 / math.sqrt(hd), True)
+    rt.check_status()
+    assert out is not None
+    ref = torch.stack(refs)
+    err = (out.cpu().double() - ref).abs()
+    assert ref.abs().max() > 5.0
+    assert err.max() <= 1.5e-2 * ref.abs().max(), f"row {int(err.max(dim=1).values.argmax())} is off by {err.max():.3e}"
 
 
 @pytest.mark.parametrize("hd,page,heads,kvh,parts,norms,rope,window", [(128, 16, 8, 2, 3, True, True, None), (64, 64, 6, 2, 1, True, True, 300),

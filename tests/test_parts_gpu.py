@@ -151,16 +151,19 @@ def _register_toy():
             self.w = weights[f"{self.prefix}.mix.weight"].to(rt.device).float()
 
         def forward(self, ctx, h, cache):
+            # The requests' state comes and goes through the view's gather and scatter (indexed by the device copy of
+            # the slots), and the segments' extents from h_seg_start: both are right inside a captured decode step too.
             H = self.hidden
+            state = cache.gather(ctx)                                   # [segments, H + 1]
             out = torch.empty(ctx.n_tokens, H, dtype=torch.float32, device=h.device)
-            for i, seg in enumerate(ctx.segments):
+            new = []
+            for i in range(ctx.n_segments):
                 a, b = int(ctx.h_seg_start[i]), int(ctx.h_seg_start[i + 1])
-                state = cache.tensor[seg.slot]
-                sums = state[:H] + torch.cumsum(h[a:b].float(), dim=0)
-                counts = state[H] + torch.arange(1, b - a + 1, device=h.device, dtype=torch.float32)
+                sums = state[i, :H] + torch.cumsum(h[a:b].float(), dim=0)
+                counts = state[i, H] + torch.arange(1, b - a + 1, device=h.device, dtype=torch.float32)
                 out[a:b] = (sums / counts[:, None]) @ self.w.T
-                state[:H] = sums[-1]
-                state[H] = counts[-1]
+                new.append(torch.cat([sums[-1], counts[-1:]]))
+            cache.scatter(ctx, torch.stack(new))
             return out.unsqueeze(0)
 
     @dataclass(frozen=True)

@@ -65,3 +65,29 @@ def test_cut_matches_plain(model_dirs, plain_logits, name, dtype, cut):
     runner.cache.check()
     assert runner.cache.used_pages() == [0] * len(runner.cache.groups)
     print(f"{name}/{dtype}/{cut}: worst {worst:.3e} of max|logit|, pool {max_tokens} tokens")
+
+
+# ------------------------------------------------------------------------------------------ a checkpoint this repository did not write
+REFERENCE_FIXTURE = __import__("pathlib").Path(__file__).parent / "data" / "reference" / "tiny-qwen3-sliding"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("cut", ["whole", "tail", "portions", "mixed"])
+def test_reference_fixture_matches_plain(dtype, cut):
+    """The reference's own tiny checkpoint (crates/specrt/tests/fixtures/tiny-qwen3-sliding: four layers, alternating
+    windowed and full attention with a window of 16, head size 64, `rope_parameters` in config.json, written by the official
+    safetensors writer) under the four cuts against the plain model. The prompt lengths of the reference's script are
+    kept (96 tokens and 32 decoded: crates/specrt/scripts/tiny_sliding.py:9-11); token ids are this test's own."""
+    from inference_bench_b200.trace import build_runner
+    reqs = {r: traces.prompt(40 + i, n, 512) for i, (r, n) in enumerate({"a": 128, "b": 17, "c": 96, "d": 3, "e": 60}.items())}
+    plain = PlainModel(REFERENCE_FIXTURE)
+    want = {r: plain.logits(t).numpy() for r, t in reqs.items()}
+    steps = {"whole": traces.whole, "tail": traces.tail_one_by_one, "portions": traces.portions, "mixed": traces.mixed}[cut](reqs)
+    max_tokens = traces.max_live_tokens(steps)
+    runner = build_runner(REFERENCE_FIXTURE, dtype, max_tokens, page_size=16)
+    assert [g.window for g in runner.cache.groups] == [16, None]
+    got = traces.run_steps(runner, steps)
+    worst = _compare(got, want, dtype, f"reference fixture/{dtype}/{cut}")
+    runner.cache.check()
+    assert runner.cache.used_pages() == [0, 0]
+    print(f"reference fixture/{dtype}/{cut}: worst {worst:.3e} of max|logit|")

@@ -46,7 +46,7 @@ def portions(reqs: dict[str, list[int]], sizes=(7, 5, 3, 2)) -> list[dict]:
     return steps
 
 
-def mixed(reqs: dict[str, list[int]], max_live: int = 4, seed: int = 0, decode_tail: int = 12) -> list[dict]:
+def mixed(reqs: dict[str, list[int]], max_live: int = 4, seed: int = 0, decode_tail: int = 12, sizes=(2, 3, 5, 9, 17)) -> list[dict]:
     """Up to `max_live` requests at a time: portions of some beside single tokens of others, a
     request sometimes left out of a step, new requests admitted as old ones end."""
     rng = np.random.default_rng(seed)
@@ -63,7 +63,7 @@ def mixed(reqs: dict[str, list[int]], max_live: int = 4, seed: int = 0, decode_t
             if len(live) > 1 and rng.random() < 0.2:
                 continue  # left out of this step
             left = len(t) - at
-            size = 1 if left <= decode_tail else int(min(left - decode_tail, rng.choice([2, 3, 5, 9, 17])))
+            size = 1 if left <= decode_tail else int(min(left - decode_tail, rng.choice(list(sizes))))
             part = t[at:at + size]
             entries.append({"id": r, "tokens": part, "want": list(range(len(part)))})
             live[r] = at + len(part)
