@@ -367,7 +367,7 @@ __global__ void __launch_bounds__((kWarps + 1) * 32, 2)
     decode_stream_kernel(const __nv_bfloat16* __restrict__ q, RawQkv raw, IbKvView kv, const int* __restrict__ dec_tokens, const int* __restrict__ positions,
                          const int* __restrict__ seg_of_token, int window, float scale_log2e, float* __restrict__ part_o,
                          float* __restrict__ part_ml, int heads, int n_dec, int max_slices, int tiles_per_slice, int merge_cols,
-                         const __grid_constant__ CUtensorMap kv_map, long long view_row0, unsigned* __restrict__ status) {
+                         const __grid_constant__ CUtensorMap kv_map, long long view_row0, unsigned long long wait_ns, unsigned* __restrict__ status) {
   constexpr int CPR = HD / 8;
   constexpr int TILE = kTile * HD * 2;
   constexpr int HB = HD / 64;
@@ -474,7 +474,7 @@ __global__ void __launch_bounds__((kWarps + 1) * 32, 2)
           waited = true;
         }
         const int stage = n % kRing;
-        if (lane == 0) ok = sm100::mbar_wait(&empty[stage], ((n / kRing) & 1) ^ 1);
+        if (lane == 0) ok = sm100::mbar_wait(&empty[stage], ((n / kRing) & 1) ^ 1, wait_ns);
         ok = __shfl_sync(0xffffffffu, ok, 0) && !*gave_up;
         if (!ok) break;
         uint8_t* k_t = ring + stage * 2 * TILE;
@@ -509,7 +509,7 @@ __global__ void __launch_bounds__((kWarps + 1) * 32, 2)
       if (lane == 0) {
         *gave_up = 1;
         atomicOr(status, IB_ERR_WAIT_TIMEOUT);
-        for (uint32_t j = n > kRing ? n - kRing : 0; j < n; j++) sm100::mbar_wait(&full[j % kRing], (j / kRing) & 1);
+        for (uint32_t j = n > kRing ? n - kRing : 0; j < n; j++) sm100::mbar_wait(&full[j % kRing], (j / kRing) & 1, wait_ns);
       }
     }
     return;
@@ -653,7 +653,7 @@ __global__ void __launch_bounds__((kWarps + 1) * 32, 2)
       // After a wait that ran out nothing is waited for any more; the loops still run to their ends,
       // so that every warp meets the others at the barriers (the results are then void, and the status says so).
       if (!dead) {
-        if (!sm100::mbar_wait(&full[stage], (n / kRing) & 1)) {
+        if (!sm100::mbar_wait(&full[stage], (n / kRing) & 1, wait_ns)) {
           *gave_up = 1;
           if (lane == 0) atomicOr(status, IB_ERR_WAIT_TIMEOUT);
         }
@@ -813,7 +813,7 @@ int launch_stream(const void* q, const RawQkv* raw, const IbKvView* kv, const in
   const RawQkv none = {};
   ib::launch(decode_stream_kernel<HD, FUSED>, grid, (kWarps + 1) * 32, smem, stream, (const __nv_bfloat16*)q, raw ? *raw : none, *kv, dec_tokens,
              positions, seg_of_token, window, scale * 1.4426950408889634f, part_o, part_ml, heads, n_dec, max_slices, tiles_per_slice, merge_cols,
-             *kv_map, view_row0, status);
+             *kv_map, view_row0, ib_wait_limit_ns(), status);
   IB_CHECK_LAUNCH("attention_decode_stream split");
   ib::launch(decode_combine_kernel<HD>, dim3(heads, n_dec), kCombineThreads, 0, stream, part_o, part_ml, dec_tokens, positions, window, (__nv_bfloat16*)out, heads,
              max_slices, tiles_per_slice, status);

@@ -71,7 +71,7 @@ template <int HD>
 __global__ void __launch_bounds__(kThreads, 2)
     prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, IbKvView kv, const int* __restrict__ tile_seg, const int* __restrict__ tile_row0,
                       const int* __restrict__ seg_start, const int* __restrict__ seg_pos0, int window, float scale_log2e,
-                      __nv_bfloat16* __restrict__ out, int heads, int n_tiles, unsigned* __restrict__ status) {
+                      __nv_bfloat16* __restrict__ out, int heads, int n_tiles, unsigned long long wait_ns, unsigned* __restrict__ status) {
   using SM = Smem<HD>;
   constexpr int CPR = HD / 8;               // 16-byte chunks per row of a Q/K/V tile
   constexpr int kTmemCols = 256;            // S0 [0,64) | S1 [64,128) | O [128, 128+HD)
@@ -213,7 +213,7 @@ __global__ void __launch_bounds__(kThreads, 2)
   bool ok = true;
   for (int j = 0; j < n_kt && ok; j++) {
     const int kt = kt_begin + j;
-    ok = sm100::mbar_wait(&bar_s[j & 1], (j >> 1) & 1);   // S_j is done: its K buffer is free
+    ok = sm100::mbar_wait(&bar_s[j & 1], (j >> 1) & 1, wait_ns);   // S_j is done: its K buffer is free
     if (!ok) {
       atomicOr(status, IB_ERR_WAIT_TIMEOUT);
       break;
@@ -252,7 +252,7 @@ __global__ void __launch_bounds__(kThreads, 2)
     for (int c = 0; c < HC; c++) tile_max = fmaxf(tile_max, __uint_as_float(sr[c]));
     // ---- P V of tile j-1 must be finished before O, the P tile or its V buffer are touched
     if (j > 0) {
-      ok = sm100::mbar_wait(bar_o, (j - 1) & 1);
+      ok = sm100::mbar_wait(bar_o, (j - 1) & 1, wait_ns);
       if (!ok) {
         atomicOr(status, IB_ERR_WAIT_TIMEOUT);
         break;
@@ -316,7 +316,7 @@ __global__ void __launch_bounds__(kThreads, 2)
   }
   // ---- O / l -> out
   if (ok) {
-    ok = sm100::mbar_wait(bar_o, (n_kt - 1) & 1);
+    ok = sm100::mbar_wait(bar_o, (n_kt - 1) & 1, wait_ns);
     if (!ok) atomicOr(status, IB_ERR_WAIT_TIMEOUT);
   }
   sm100::tc_fence_after();
@@ -366,7 +366,7 @@ int launch(const void* q, const IbKvView* kv, const int* tile_seg, const int* ti
     configured = true;
   }
   ib::launch(prefill_tc_kernel<HD>, dim3(heads, n_tiles), kThreads, Smem<HD>::kBytes, stream, (const __nv_bfloat16*)q, *kv, tile_seg, tile_row0,
-             seg_start, seg_pos0, window, scale * 1.4426950408889634f, (__nv_bfloat16*)out, heads, n_tiles, status);
+             seg_start, seg_pos0, window, scale * 1.4426950408889634f, (__nv_bfloat16*)out, heads, n_tiles, ib_wait_limit_ns(), status);
   IB_CHECK_LAUNCH("attention_prefill_tc");
   return 0;
 }

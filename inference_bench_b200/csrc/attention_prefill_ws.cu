@@ -80,7 +80,7 @@ __global__ void __launch_bounds__(kThreads, 2)
     prefill_ws_kernel(const __nv_bfloat16* __restrict__ q, IbKvView kv, const int* __restrict__ tile_seg, const int* __restrict__ tile_row0,
                       const int* __restrict__ seg_start, const int* __restrict__ seg_pos0, int window, float scale_log2e,
                       __nv_bfloat16* __restrict__ out, int heads, const __grid_constant__ CUtensorMap kv_map, long long view_row0,
-                      unsigned* __restrict__ status) {
+                      unsigned long long wait_ns, unsigned* __restrict__ status) {
   using SM = Smem<HD>;
   constexpr int CPR = HD / 8, HB = HD / 64;
   constexpr int kTmemCols = 256;            // S0 [0,64) | S1 [64,128) | O [128, 128+HD); P_j lies over the first 32 columns of S_j
@@ -139,7 +139,7 @@ __global__ void __launch_bounds__(kThreads, 2)
   // a wait that ran out: say so once, and from then on nobody waits (the results are void, the status says so)
   auto wait = [&](uint64_t* bar, uint32_t parity) {
     if (*gave_up) return;
-    if (!sm100::mbar_wait(bar, parity)) {
+    if (!sm100::mbar_wait(bar, parity, wait_ns)) {
       *gave_up = 1;
       atomicOr(status, IB_ERR_WAIT_TIMEOUT);
     }
@@ -381,7 +381,7 @@ int launch(const void* q, const IbKvView* kv, const int* tile_seg, const int* ti
     configured = true;
   }
   ib::launch(prefill_ws_kernel<HD>, dim3(heads, n_tiles), kThreads, Smem<HD>::kBytes, stream, (const __nv_bfloat16*)q, *kv, tile_seg, tile_row0,
-             seg_start, seg_pos0, window, scale * 1.4426950408889634f, (__nv_bfloat16*)out, heads, *kv_map, view_row0, status);
+             seg_start, seg_pos0, window, scale * 1.4426950408889634f, (__nv_bfloat16*)out, heads, *kv_map, view_row0, ib_wait_limit_ns(), status);
   IB_CHECK_LAUNCH("attention_prefill_ws");
   return 0;
 }

@@ -44,7 +44,9 @@ struct Tile {
 template <int BN, int MT, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
     gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, void* __restrict__ out_, int T,
-                        int N, int K, int ktiles_per_split, int second_off, unsigned* __restrict__ status) {
+                        int N, int K, int ktiles_per_split, int second_off, unsigned long long wait_ns, int starve, unsigned* __restrict__ status) {
+  // wait_ns: the limit of every wait below. starve != 0 (the wait-limit test only): the copying warp sends nothing, so that
+  // the waits run out the way they would if a copy never landed, and the kernel has to unwind through its ordinary path.
   using TL = Tile<BN, MT>;
   constexpr int STAGES = TL::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -85,7 +87,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   const uint32_t tmem = *tmem_slot;
 
   if (warp == 0) {
-    if (sm100::elect_one()) {
+    if (!starve && sm100::elect_one()) {
       sm100::prefetch_tensormap(&tmap_w);
       sm100::prefetch_tensormap(&tmap_x);
       // The weights do not depend on earlier kernels: fill the pipeline with them before waiting
@@ -102,7 +104,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         sm100::tma_load_2d(tiles + i * TL::kStageBytes + MT * TL::kABytes, &tmap_x, (kt_begin + i) * BK, t0, &full[i]);
       for (int i = first; i < nkt; i++) {
         const int s = i % STAGES;
-        if (!sm100::mbar_wait(&empty[s], ((i / STAGES) & 1) ^ 1)) {
+        if (!sm100::mbar_wait(&empty[s], ((i / STAGES) & 1) ^ 1, wait_ns)) {
           atomicOr(status, IB_ERR_WAIT_TIMEOUT);
           break;
         }
@@ -119,7 +121,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       bool ok = true;
       for (int i = 0; i < nkt && ok; i++) {
         const int s = i % STAGES;
-        if (!sm100::mbar_wait(&full[s], (i / STAGES) & 1)) {
+        if (!sm100::mbar_wait(&full[s], (i / STAGES) & 1, wait_ns)) {
           atomicOr(status, IB_ERR_WAIT_TIMEOUT);
           ok = false;
           break;
@@ -146,7 +148,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     ib::pdl_wait();   // the output buffer may still be in use by an earlier kernel
     bool ok = true;
     if (nkt > 0) {
-      ok = sm100::mbar_wait(acc_full, 0);
+      ok = sm100::mbar_wait(acc_full, 0, wait_ns);
       if (!ok && lane == 0) atomicOr(status, IB_ERR_WAIT_TIMEOUT);
       sm100::tc_fence_after();
     }
@@ -232,7 +234,7 @@ int make_tmap(CUtensorMap* m, const void* ptr, int rows, int K, int box_rows) {
 
 template <int BN, int MT, int EPI>
 int launch(const CUtensorMap& tw, const CUtensorMap& tx, void* out, int T, int N, int K, int splits, int kt_per_split, int second_off,
-           unsigned* status, cudaStream_t stream) {
+           unsigned* status, cudaStream_t stream, int starve = 0) {
   using TL = Tile<BN, MT>;
   static bool configured = false;
   if (!configured) {
@@ -243,7 +245,7 @@ int launch(const CUtensorMap& tw, const CUtensorMap& tx, void* out, int T, int N
   const int cols_per_cta = EPI == EPI_SWIGLU ? BM : BM * MT;
   dim3 grid((T + BN - 1) / BN, (N + cols_per_cta - 1) / cols_per_cta, splits);
   IB_CHECK_ARG(grid.y <= 65535, "gemm_tcgen05: N=%d gives more than 65535 row blocks", N);
-  ib::launch(gemm_tcgen05_kernel<BN, MT, EPI>, grid, kThreads, TL::kSmemBytes, stream, tw, tx, out, T, N, K, kt_per_split, second_off, status);
+  ib::launch(gemm_tcgen05_kernel<BN, MT, EPI>, grid, kThreads, TL::kSmemBytes, stream, tw, tx, out, T, N, K, kt_per_split, second_off, ib_wait_limit_ns(), starve, status);
   IB_CHECK_LAUNCH("gemm_tcgen05");
   return 0;
 }
@@ -287,6 +289,20 @@ extern "C" int ib_gemm_tcgen05(const void* x, const void* w, float* out, int T, 
     case 256: return launch<256, 1, EPI_STORE>(tw, tx, out, T, N, K, splits, kt_per_split, 0, status, stream);
     default: return ib_set_error("gemm_tcgen05: token tile %d is not one of 16, 32, 64, 128, 256", bn);
   }
+}
+
+// The wait-limit test's entry: ib_gemm_tcgen05 for up to 16 tokens whose copying warp sends nothing. Every wait in the
+// kernel then runs out after the limit set with ib_set_wait_limit_ms: the status word gets IB_ERR_WAIT_TIMEOUT, nothing
+// is stored, tensor memory is given back and the kernel returns. No copy is in flight at any time.
+extern "C" int ib_test_gemm_tcgen05_starved(const void* x, const void* w, float* out, int T, int N, int K, unsigned* status, cudaStream_t stream) {
+  if (check_common("test_gemm_tcgen05_starved", x, w, T, N, K, 16)) return 1;
+  IB_CHECK_ARG(T <= 16, "test_gemm_tcgen05_starved: up to 16 tokens, got %d", T);
+  IB_CHECK_ARG(ib_wait_limit_ns() <= 100000000ull, "test_gemm_tcgen05_starved: set a wait limit of 100 ms or less first (it is %llu ns)", ib_wait_limit_ns());
+  const int total_kt = (K + BK - 1) / BK;
+  CUtensorMap tw, tx;
+  if (make_tmap(&tw, w, N, K, BM)) return 1;
+  if (make_tmap(&tx, x, T, K, 16)) return 1;
+  return launch<16, 1, EPI_STORE>(tw, tx, out, T, N, K, 1, total_kt, 0, status, stream, 1);
 }
 
 // SwiGLU front half in one kernel: w [2*I, K] = gate rows then up rows; act [T, I] bfloat16 =

@@ -117,7 +117,7 @@ struct QkvEpi {
 template <int MT, int EPI, int BN>
 __global__ void __launch_bounds__(kThreads, 1)
     gemm_2cta_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, void* __restrict__ out_, int T, int N,
-                     int K, int token_tiles, int total_tiles, int second_off, unsigned* __restrict__ status, const QkvEpi qe) {
+                     int K, int token_tiles, int total_tiles, int second_off, unsigned long long wait_ns, unsigned* __restrict__ status, const QkvEpi qe) {
   using TL = Tile<MT, BN>;
   constexpr int STAGES = TL::kStages;
   constexpr int BNH = BN / 2;
@@ -183,7 +183,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         const int t0 = (tile % token_tiles) * BN, rb = tile / token_tiles;
         for (int i = 0; i < nkt; i++, it++) {
           const int s = it % STAGES;
-          if (!sm100::mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1)) {
+          if (!sm100::mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, wait_ns)) {
             atomicOr(status, IB_ERR_WAIT_TIMEOUT);
             ok = false;
             break;
@@ -211,7 +211,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       int it = 0, tl = 0;
       for (int tile = pair; tile < total_tiles && ok; tile += n_pairs, tl++) {
         const int b = tl % NBUF;
-        if (tl >= NBUF && !sm100::mbar_wait(&acc_empty[b], ((tl / NBUF) - 1) & 1)) {   // the accumulator's last contents have been stored
+        if (tl >= NBUF && !sm100::mbar_wait(&acc_empty[b], ((tl / NBUF) - 1) & 1, wait_ns)) {   // the accumulator's last contents have been stored
           atomicOr(status, IB_ERR_WAIT_TIMEOUT);
           ok = false;
           break;
@@ -219,7 +219,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         sm100::tc_fence_after();
         for (int i = 0; i < nkt; i++, it++) {
           const int s = it % STAGES;
-          if (!sm100::mbar_wait(&full[s], (it / STAGES) & 1)) {
+          if (!sm100::mbar_wait(&full[s], (it / STAGES) & 1, wait_ns)) {
             atomicOr(status, IB_ERR_WAIT_TIMEOUT);
             ok = false;
             break;
@@ -246,7 +246,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     for (int tile = pair; tile < total_tiles; tile += n_pairs, tl++) {
       const int b = tl % NBUF;
       const int t0 = (tile % token_tiles) * BN, n_pair = (tile / token_tiles) * kColsPerPair;
-      bool ok = sm100::mbar_wait(&acc_full[b], (tl / NBUF) & 1);
+      bool ok = sm100::mbar_wait(&acc_full[b], (tl / NBUF) & 1, wait_ns);
       if (!ok && lane == 0) atomicOr(status, IB_ERR_WAIT_TIMEOUT);
       sm100::tc_fence_after();
       ok = __all_sync(0xffffffffu, ok);
@@ -452,7 +452,7 @@ int launch(const void* x, const void* w, void* out, int T, int N, int K, int w_r
   attr[1].val.programmaticStreamSerializationAllowed = ib_pdl_enabled();
   cfg.attrs = attr;
   cfg.numAttrs = 2;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_2cta_kernel<MT, EPI, BN>, tw, tx, out, T, N, K, token_tiles, total_tiles, second_off, status, qe);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_2cta_kernel<MT, EPI, BN>, tw, tx, out, T, N, K, token_tiles, total_tiles, second_off, ib_wait_limit_ns(), status, qe);
   IB_CHECK_ARG(e == cudaSuccess, "gemm_tcgen05_2cta: launch failed: %s", cudaGetErrorString(e));
   return 0;
 }

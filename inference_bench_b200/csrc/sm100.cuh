@@ -1,15 +1,14 @@
 // Thin wrappers over the sm_100a instructions the tensor-core kernels use: mbarrier, TMA tile
 // loads, tensor memory (TMEM) allocation, tcgen05.mma / commit / ld, and the descriptors they take.
-// Every wait is bounded: it gives up after kWaitLimitNs and reports it, so a fault in a pipeline
-// shows up as a status bit instead of a hung GPU.
+// Every wait is bounded: it gives up after a limit that the launcher passes to the kernel (ib_wait_limit_ns(),
+// 2 s unless the host set another) and reports it, so a fault in a pipeline shows up as a status bit
+// instead of a hung GPU.
 #pragma once
 #include <cuda.h>
 
 #include "common.cuh"
 
 namespace sm100 {
-
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -53,15 +52,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait. Returns false after kWaitLimitNs (the caller sets the status bit and unwinds).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+// Bounded wait. Returns false after limit_ns (the caller sets the status bit and unwinds).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned long long limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   unsigned long long t0 = global_timer_ns();
   for (;;) {
 #pragma unroll 1
     for (int i = 0; i < 1024; i++)
       if (mbar_try_wait(bar, parity)) return true;
-    if (global_timer_ns() - t0 > kWaitLimitNs) return false;
+    if (global_timer_ns() - t0 > limit_ns) return false;
   }
 }
 

@@ -61,12 +61,12 @@ _MID = dict(rate=4.015e6, cap=250e3, t0=4.36, partial_bw=3.455e6, pair_rate=5.44
             speed={(256, True): 1.0, (256, False): 0.982, (128, True): 0.895, (128, False): 0.956})
 
 
-def single_variants(T: int, N: int, K: int, sm_count: int = FITTED_SM_COUNT):
+def single_variants(T: int, N: int, K: int, sm_count: int = FITTED_SM_COUNT, allow_split: bool = True):
     """The forms of the single-CTA kernel that `plan` weighs for more than 128 tokens: (tokens per CTA, k-splits, wide)."""
     ktiles = -(-K // 64)
     for bn in (128, 256):
         for wide in (False, True):
-            for sp in (1, 2, 3, 4, 6):
+            for sp in ((1, 2, 3, 4, 6) if allow_split else (1,)):
                 per = -(-ktiles // sp)
                 if sp > max(1, ktiles // 4) or -(-ktiles // per) != sp:   # at least four k-tiles a split, and none empty
                     continue
@@ -77,15 +77,16 @@ def single_variants(T: int, N: int, K: int, sm_count: int = FITTED_SM_COUNT):
 
 
 @functools.lru_cache(maxsize=4096)
-def plan_costs(T: int, N: int, K: int, sm_count: int = FITTED_SM_COUNT) -> tuple:
-    """(expected us of the CTA-pair kernel, expected us of the best single-CTA form, that form) for 129 <= T < 2048."""
+def plan_costs(T: int, N: int, K: int, sm_count: int = FITTED_SM_COUNT, allow_split: bool = True) -> tuple:
+    """(expected us of the CTA-pair kernel, expected us of the best single-CTA form, that form) for 129 <= T < 2048.
+    allow_split=False leaves out the forms that cut the k-range (for a caller that wants one finished product)."""
     m = _MID
     tiles = -(-N // 256) * -(-T // 256)
     active = min(tiles, sm_count // 2) * 2
     pair = -(-tiles // (sm_count // 2)) * max(256 * 256 * K * 2 / (2 * m["pair_rate"]), 256 * K * 2 / min(m["pair_cap"], m["hbm"] / active)) + m["t0"]
     best = (float("inf"), None)
     ktiles = -(-K // 64)
-    for bn, sp, wide in single_variants(T, N, K, sm_count):
+    for bn, sp, wide in single_variants(T, N, K, sm_count, allow_split):
         rows = 256 if wide else 128
         ctas = -(-N // rows) * -(-T // bn) * sp
         kc = -(-ktiles // sp) * 64
@@ -97,10 +98,10 @@ def plan_costs(T: int, N: int, K: int, sm_count: int = FITTED_SM_COUNT) -> tuple
     return pair, best[0], best[1]
 
 
-def plan(T: int, N: int, K: int, sm_count: int = FITTED_SM_COUNT) -> tuple:
+def plan(T: int, N: int, K: int, sm_count: int = FITTED_SM_COUNT, allow_split: bool = True) -> tuple:
     """For 129 <= T < 2048: ("pair",) or ("single", tokens per CTA, k-splits, wide), whichever the cost model
     expects to be faster. Depends on the sizes (and the device's SM count) only."""
-    pair, single, form = plan_costs(T, N, K, sm_count)
+    pair, single, form = plan_costs(T, N, K, sm_count, allow_split)
     return ("pair",) if pair <= single else ("single",) + form
 
 
@@ -181,7 +182,7 @@ def gemm_qkv_pair(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, kv: "op
 
 def linear(rt, x: torch.Tensor, lw, allow_split: bool = True, add_to: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
     T = x.shape[0]
-    how = ("pair",) if T >= rt.options.pair_always_tokens else (plan(T, lw.n, lw.k, rt.sm_count) if T > 128 else None)
+    how = ("pair",) if T >= rt.options.pair_always_tokens else (plan(T, lw.n, lw.k, rt.sm_count, allow_split) if T > 128 else None)
     if how is not None and how[0] == "single":
         _, bn, splits, wide = how
         out = rt.empty((splits, T, lw.n), torch.float32)

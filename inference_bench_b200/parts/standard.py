@@ -213,7 +213,10 @@ class LinearHead(base.Head):
         self.w = rt.matrix(weights[self.tied_to or self.name])
 
     def forward(self, ctx, h):
-        return ctx.rt.linear(h, self.w, allow_split=False)[0]
+        out = ctx.rt.linear(h, self.w, allow_split=False)
+        if out.shape[0] != 1:
+            raise RuntimeError(f"the head's product came back in {out.shape[0]} partial sums although it asked for one")
+        return out[0]
 
 
 # ------------------------------------------------------------------------------------------ block

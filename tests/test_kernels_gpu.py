@@ -224,6 +224,47 @@ def test_rope_table():
     assert (sin.cpu() - torch.sin(ang.double()).float()).abs().max() <= 2e-6
 
 
+def test_a_wait_that_runs_out_is_reported_and_the_kernel_returns(status):
+    """Every wait inside the tensor-core kernels has a limit. Here the limit is set to a millisecond and the matrix
+    product is launched through the entry point whose copying warp sends nothing, so no barrier is ever completed: the
+    kernel must set the wait-timeout bit, store nothing, give its tensor memory back and return; and the next ordinary
+    product on the same device must be right (tensor memory that was not given back would make it wait for ever)."""
+    import ctypes as C
+    from inference_bench_b200.kernels import gemm_tcgen05 as G
+    from inference_bench_b200.kernels import lib as L
+    lib = L.load()
+    fn = lib.ib_test_gemm_tcgen05_starved
+    fn.restype = C.c_int
+    fn.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
+    lib.ib_set_wait_limit_ms.argtypes = [C.c_int]
+    T, N, K = 8, 256, 512
+    x = (torch.randn(T, K, generator=_g(71)) * 0.5).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, K, generator=_g(72)) * 0.5).to(torch.bfloat16).to(DEV)
+    out = torch.full((1, T, N), float("nan"), device=DEV)
+    stream = torch.cuda.current_stream().cuda_stream
+    assert fn(x.data_ptr(), w.data_ptr(), out.data_ptr(), T, N, K, status.data_ptr(), stream) != 0      # refused while the limit is the ordinary two seconds
+    assert b"wait limit" in lib.ib_last_error()
+    lib.ib_set_wait_limit_ms(1)
+    try:
+        t0 = torch.cuda.Event(enable_timing=True)
+        t1 = torch.cuda.Event(enable_timing=True)
+        t0.record()
+        assert fn(x.data_ptr(), w.data_ptr(), out.data_ptr(), T, N, K, status.data_ptr(), stream) == 0, lib.ib_last_error()
+        t1.record()
+        torch.cuda.synchronize()
+    finally:
+        lib.ib_set_wait_limit_ms(2000)
+    assert status.item() == L.ERR_WAIT_TIMEOUT
+    assert 0.9 <= t0.elapsed_time(t1) < 50.0, f"the starved kernel took {t0.elapsed_time(t1):.2f} ms with a limit of 1 ms"
+    assert torch.isnan(out).all()                      # nothing was stored
+    status.zero_()
+    for _ in range(3):                                 # the ordinary kernel, three times: it allocates tensor memory again
+        G.gemm(x, w, out, 16, 1, status)
+    ref = x.double() @ w.double().T
+    assert status.item() == 0
+    assert (out[0].double() - ref).abs().max() <= 2e-5 * ref.abs().max() + 1e-6
+
+
 # ------------------------------------------------------------------------------------------ paged attention
 def _paged(contexts, page_size, dtype, seed, entries=2, entry=1):
     """Scatter dense K, V ([L, kv_heads, hd] per request) into a pool with shuffled pages."""

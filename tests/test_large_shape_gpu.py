@@ -55,7 +55,8 @@ def test_a_long_portion_in_bfloat16_against_float32(shape, page):
     from inference_bench_b200.engine.step import StepEntry
     from inference_bench_b200.kernels import gemm_tcgen05 as G
     cfg = SHAPES[shape]
-    assert G.qkv_in_epilogue(2100, (cfg["num_attention_heads"] + 2 * cfg["num_key_value_heads"]) * 128, cfg["hidden_size"])
+    from inference_bench_b200.engine.runtime import Runtime
+    assert G.qkv_in_epilogue(Runtime("cuda:0"), 2100, (cfg["num_attention_heads"] + 2 * cfg["num_key_value_heads"]) * 128, cfg["hidden_size"])
     prompt = np.random.default_rng(2).integers(0, 151936, 2300).tolist()
     logits = {}
     for dtype in ("float32", "bfloat16"):

@@ -60,7 +60,7 @@ def test_norm_embedding_and_head_alone(dtype):
     assert logits.dtype == torch.float32 and (logits.cpu() - ref).abs().max() <= 1e-4 * ref.abs().max()
     # tied head reads the embedding table
     tied = LinearHead("unused", 301, 72, tied_to="e.weight")
-    assert tied.weight_specs() == []
+    assert [(w_.name, w_.shape) for w_ in tied.weight_specs()] == [("e.weight", (301, 72))]     # the table it shares with the embedding, so a loader knows it has two readers
     tied.bind({k: v.to(DEV) for k, v in w.items()}, rt)
     ref = h.float().cpu() @ wf["e.weight"].T
     assert (tied.forward(ctx, h).cpu() - ref).abs().max() <= 1e-4 * ref.abs().max()

@@ -404,3 +404,15 @@ def test_balanced_portion_fills_whole_rounds_of_tiles():
             assert T % 256 == 0 and nominal * 3 // 4 <= T <= nominal * 5 // 4
     assert G.balanced_portion([], 2048) == 2048          # nothing to balance: the nominal size
     assert G.balanced_portion([(256, 64)], 2048) == 2560  # one round whatever the size: the most tokens a round
+
+
+def test_a_product_that_wants_one_sum_is_never_planned_with_a_cut_k_range():
+    """The head asks for one finished product (it hands logits on, nobody adds partial sums after it). For a small vocabulary
+    and a few hundred tokens the cost model's favourite cuts the k-range; with allow_split=False it must not."""
+    from inference_bench_b200.kernels import gemm_tcgen05 as G
+    cut = [(T, N, K) for T in (130, 150, 300, 513, 1000) for N, K in ((1500, 1024), (500, 128), (4096, 4096), (151936, 1024))
+           if G.plan(T, N, K)[0] == "single" and G.plan(T, N, K)[2] > 1]
+    assert (150, 1500, 1024) in cut                       # the case that showed it: 150 tokens, a vocabulary of 1,500
+    for T, N, K in cut:
+        how = G.plan(T, N, K, allow_split=False)
+        assert how[0] == "pair" or how[2] == 1, (T, N, K, how)

@@ -100,7 +100,7 @@ def test_engine_logits_cuts_a_long_prompt_itself(model_dirs, name, dtype):
 # ------------------------------------------------------------------------------------------ the status word on the serving path
 @pytest.mark.parametrize("graphs,pipeline", [(True, True), (True, False), (False, False)])
 def test_engine_step_raises_when_a_kernel_reports_a_fault(model_dirs, graphs, pipeline):
-    """A block table entry that vanishes under a running request (made from the host here): the kernels skip the page
+    """A block table entry that goes bad under a running request (made from the host here): the kernels skip the page
     and set the status word, and the caller of Engine.step gets an error with the step's tokens, not garbage tokens."""
     from inference_bench_b200.engine.runtime import DeviceStatusError
     name = "D"
@@ -110,11 +110,16 @@ def test_engine_step_raises_when_a_kernel_reports_a_fault(model_dirs, graphs, pi
     for _ in range(4):
         eng.step()
     slot = eng.cache.slot(rid)
+    saved = [int(t[slot, 0]) for t in eng.cache._tables]
     for t in eng.cache._tables:
-        t[slot, 0] = -1
-    with pytest.raises(DeviceStatusError, match="block table"):
-        for _ in range(4):
-            eng.step()
+        t[slot, 0] = 10 ** 6       # (an entry of -1 would be filled with a fresh page by the cache manager's next extend)
+    try:
+        with pytest.raises(DeviceStatusError, match="block table"):
+            for _ in range(4):
+                eng.step()
+    finally:
+        for t, page in zip(eng.cache._tables, saved):
+            t[slot, 0] = page
     assert int(eng.rt.status.item()) == 0      # the word is cleared when it is reported
 
 
@@ -172,8 +177,9 @@ SERVING = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_siz
                num_hidden_layers=2, num_attention_heads=8, num_key_value_heads=2, head_dim=128, rms_norm_eps=1e-6, rope_theta=1000000.0,
                tie_word_embeddings=False, max_position_embeddings=4096, hidden_act="silu", attention_bias=False, torch_dtype="bfloat16")
 SERVING_LENGTHS = {"a": 150, "b": 300, "c": 2100, "d": 513, "e": 40}
-# Largest |engine - plain| / max|logit| allowed in bfloat16 at these sizes, per cut: about twice the worst value seen on a B200.
-SERVING_BF16 = {"whole": 3e-2, "tail": 3e-2, "portions": 3e-2, "mixed": 3e-2}
+# Largest |engine - plain| / max|logit| allowed in bfloat16 at these sizes, per cut: about twice the worst value seen on a B200
+# (whole 9.1e-3, tail 8.7e-3, portions 9.1e-3, mixed 8.5e-3; float32: 1.2e-5 in every cut).
+SERVING_BF16 = {"whole": 2e-2, "tail": 2e-2, "portions": 2e-2, "mixed": 2e-2}
 
 
 @pytest.fixture(scope="module")
