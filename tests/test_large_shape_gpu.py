@@ -43,7 +43,7 @@ def test_bfloat16_against_float32_at_large_layer_sizes(shape, page):
     ref, got = logits["float32"], logits["bfloat16"]
     assert torch.isfinite(got).all()
     err = (got - ref).abs().max().item() / ref.abs().max().item()
-    assert err <= 3e-2, f"bfloat16 differs from float32 by {err:.3e} of max|logit|"
+    assert err <= 2e-2, f"bfloat16 differs from float32 by {err:.3e} of max|logit| (worst seen on a B200: 9.4e-3)"
     print(f"{shape} layer sizes, 2 layers: bfloat16 vs float32 worst {err:.3e} of max|logit|")
 
 
@@ -72,7 +72,7 @@ def test_a_long_portion_in_bfloat16_against_float32(shape, page):
     ref, got = logits["float32"], logits["bfloat16"]
     assert torch.isfinite(got).all()
     err = (got - ref).abs().max().item() / ref.abs().max().item()
-    assert err <= 3e-2, f"bfloat16 differs from float32 by {err:.3e} of max|logit|"
+    assert err <= 2e-2, f"bfloat16 differs from float32 by {err:.3e} of max|logit| (worst seen on a B200: 9.4e-3)"
     print(f"{shape} layer sizes, 2 layers, 2,100-token portion: bfloat16 vs float32 worst {err:.3e} of max|logit|")
 
 

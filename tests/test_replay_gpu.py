@@ -16,6 +16,9 @@ pytestmark = pytest.mark.gpu
 # float32: the two differ only in summation order. bfloat16: activations and the cache are rounded
 # to 8 bits of mantissa (2^-9 relative per rounding) between float32 accumulations.
 TOLERANCE = {"float32": 1e-4, "bfloat16": 3e-2}
+# The bfloat16 bound per configuration: about twice the worst value seen on a B200 over the four cuts
+# (A 5.9e-3, B 6.9e-3, C 1.10e-2, D 1.01e-2, E 6.1e-3, the reference's fixture 6.7e-3; float32: below 1e-6 everywhere).
+BF16_ENVELOPE = {"A": 1.2e-2, "B": 1.4e-2, "C": 2.2e-2, "D": 2.0e-2, "E": 1.2e-2, "reference fixture": 1.4e-2}
 LENGTHS = {"a": 7, "b": 19, "c": 33, "d": 70, "e": 45, "f": 100, "g": 2, "h": 64}
 
 
@@ -39,13 +42,14 @@ def _runner(model_dirs, name, dtype, max_tokens):
 
 
 def _compare(got, want_by_req, dtype, what):
+    bound = TOLERANCE[dtype] if dtype == "float32" else BF16_ENVELOPE.get(what.split("/")[0], TOLERANCE[dtype])
     worst = 0.0
     for (r, pos), row in got.items():
         want = want_by_req[r][pos]
         scale = np.abs(want_by_req[r]).max()
         err = np.abs(row - want).max() / scale
-        if err > TOLERANCE[dtype]:
-            raise AssertionError(f"{what}: request {r} position {pos}: |diff| = {err:.3e} of max|logit| (allowed {TOLERANCE[dtype]:.0e})")
+        if err > bound:
+            raise AssertionError(f"{what}: request {r} position {pos}: |diff| = {err:.3e} of max|logit| (allowed {bound:.1e})")
         worst = max(worst, err)
     n_expected = sum(len(v) for v in want_by_req.values())
     assert len(got) == n_expected, f"{what}: {len(got)} logits rows, expected {n_expected}"
