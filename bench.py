@@ -182,10 +182,37 @@ def measure_decode_device(engine, batch: int, steps: int, warmup: int) -> tuple[
     return ms, launches
 
 
-def measure_mixed_step(engine, steps: int) -> tuple[float, int]:
+LEAVE_OUT = {   # kinds of kernel by the library entry points that launch them
+    "attention": ["ib_attention_decode", "ib_attention_decode_stream", "ib_attention_decode_fused"],
+    "norm": ["ib_add_rmsnorm"], "silu_mul": ["ib_silu_mul"], "qk": ["ib_qk_norm_rope_kv"], "sampling": ["ib_sample_rows"],
+    "gemm": ["ib_gemm_tcgen05", "ib_gemm_swiglu_tcgen05", "ib_gemm_swiglu_tcgen05_2cta", "ib_gemm_tcgen05_2cta", "ib_gemm_tcgen05_2cta_add"],
+    "small": ["ib_add_rmsnorm", "ib_silu_mul", "ib_qk_norm_rope_kv", "ib_rope_table", "ib_sample_rows", "ib_embed"],
+}
+
+
+def leave_out_costs(engine, batch: int, steps: int, warmup: int, kinds: str) -> dict:
+    """Milliseconds per decode step with one kind of kernel left out of the captured step at a time (the results of such a
+    step are void; only its time means something). The difference from the whole step is what that kind costs inside
+    the graph, where kernels overlap their neighbours' tails: the figure a launch list cannot give."""
+    from inference_bench_b200.kernels import lib as L
+    real, out = L.call, {}
+    try:
+        for kind in kinds.split(","):
+            names = set(sum((LEAVE_OUT[k] for k in kind.split("+")), []))
+            L.call = lambda name, *a, _n=names: None if name in _n else real(name, *a)
+            engine.executor._graphs.clear()
+            out[kind] = measure_decode_device(engine, batch, steps, warmup)[0]
+    finally:
+        L.call = real
+        engine.executor._graphs.clear()
+    return out
+
+
+def measure_mixed_step(engine, steps: int, cfg: dict, layers: int) -> tuple[float, int, float, float]:
     """Milliseconds for one step that holds 8 prompt portions of 512 tokens (starting 0, 512, ... 3,584 tokens into
     their prompts) beside 56 decoded tokens of requests at contexts drawn uniformly from 1,024 to 4,096: the
-    mixed batch the baseline names for the 14B shape. Returns (median ms, rows in the step)."""
+    mixed batch the baseline names for the 14B shape. Returns (median ms, rows in the step, the step's FLOPs, the
+    bytes it has to read: every weight once and the cache of the live requests)."""
     import numpy as np
     import torch
     from inference_bench_b200.engine.step import StepEntry
@@ -219,7 +246,14 @@ def measure_mixed_step(engine, steps: int) -> tuple[float, int]:
     for e in entries:
         engine.cache.release(e.request)
     engine.rt.check_status()
-    return statistics.median(times[2:]), sum(len(e.tokens) for e in entries)
+    rows = sum(len(e.tokens) for e in entries)
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    q = cfg["num_attention_heads"] * cfg["head_dim"]
+    kv = cfg["num_key_value_heads"] * cfg["head_dim"]
+    keys_seen = sum(contexts) + sum(512 * (512 * i) + 512 * 513 // 2 for i in range(8))       # (query, key) pairs of the step
+    flops = 2.0 * rows * layers * ((q + 2 * kv) * H + H * q + 3 * I * H) + layers * 4.0 * keys_seen * q + 2.0 * 64 * V * H
+    cached = sum(contexts) + sum(512 * (i + 1) for i in range(8))
+    return statistics.median(times[2:]), rows, flops, weight_bytes(cfg, layers) + cached * kv_bytes_per_token(cfg, layers)
 
 
 def measure_decode_e2e(engine, batch: int, steps: int, warmup: int) -> tuple[float, float, float]:
@@ -274,11 +308,19 @@ def run_ours(args) -> dict:
     if args.only == "prefill":   # one part alone, for profiling: a short report, not the benchmark line
         return {"only": "prefill", "layers": layers, "ms": measure_prefill(engine, args.steps, 1)}
     if args.only == "mixed":
-        ms, rows = measure_mixed_step(engine, max(args.steps, 3) if args.steps < 16 else 5)
-        return {"only": "mixed", "layers": layers, "rows": rows, "ms": ms, "tok_s": rows * 1e3 / ms}
+        clocks = ClockSampler()
+        clocks.start()
+        ms, rows, flops, step_bytes = measure_mixed_step(engine, max(args.steps, 3) if args.steps < 16 else 5, cfg, layers)
+        return {"only": "mixed", "shape": args.shape, "layers": layers, "layers_full": full_layers, "page_size": page, "rows": rows, "ms": ms,
+                "tok_s": rows * 1e3 / ms, "prefill": {"tokens": 8 * 512, "frac": flops / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), "peak_tflops": pk["bf16_tflops"]},
+                "roofline": {"bound": "hbm", "achieved": step_bytes / (ms * 1e-3) / 1e9, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                             "frac": step_bytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"]}, "peaks": pk_src, "clocks": clocks.stop()}
     if args.only == "decode":
         ms, launches = measure_decode_device(engine, args.batch, steps, warmup)
-        return {"only": "decode", "layers": layers, "batch": args.batch, "ms_per_step": ms, "launches_per_step": launches}
+        report = {"only": "decode", "layers": layers, "batch": args.batch, "ms_per_step": ms, "launches_per_step": launches}
+        if args.leave_out:
+            report["without"] = leave_out_costs(engine, args.batch, steps, warmup, args.leave_out)
+        return report
 
     prefill_ms = measure_prefill(engine, 5, 3)
     b1_ms, _ = measure_decode_device(engine, 1, steps, warmup)
@@ -334,6 +376,8 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (both numbers are reported)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--prefill-after", type=int, default=0, help="with --only prefill: the 2,048-token portion follows this many cached tokens of the same request")
+    ap.add_argument("--leave-out", default="", help="with --only decode: also time the step without each of these kinds of kernel (comma separated; "
+                    "a+b leaves both out): " + ", ".join(sorted(LEAVE_OUT)))
     ap.add_argument("--only", default="", choices=["", "prefill", "decode", "mixed"], help="run one part alone (for profiling); prints a short report")
     args = ap.parse_args()
     if args.impl == "reference":
