@@ -28,6 +28,9 @@ constexpr int UMMA_K = 16;  // k per tcgen05.mma of kind::f16
 constexpr int kThreads = 192;
 constexpr int EPI_STORE = 0;   // float32 partial products
 constexpr int EPI_SWIGLU = 1;  // accumulator 0 = gate, accumulator 1 = up -> bfloat16 silu(gate) * up
+constexpr int EPI_SWIGLU_HALF = 2;  // one accumulator: rows 0-63 = 64 gate rows, rows 64-127 = the matching 64 up rows -> bfloat16 silu(gate) * up
+// (for a handful of tokens: as many CTAs as the plain product has, I / 64, so the weights stream as fast, and neither the
+// float32 [T, 2I] intermediate nor the SiLU-mul kernel exists)
 
 template <int BN, int MT>
 struct Tile {
@@ -61,7 +64,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   // first output column of this CTA, and the W row where each accumulator's block starts
   // (token tiles vary fastest in the grid: the CTAs that share a block of W run together, so W comes
   // from memory once and the much smaller x stays in L2)
-  const int n0 = blockIdx.y * (EPI == EPI_SWIGLU ? BM : BM * MT);
+  const int n0 = blockIdx.y * (EPI == EPI_SWIGLU_HALF ? BM / 2 : EPI == EPI_SWIGLU ? BM : BM * MT);
   const int t0 = blockIdx.x * BN, split = blockIdx.z;
   const int total_kt = (K + BK - 1) / BK;
   const int kt_begin = split * ktiles_per_split;
@@ -92,12 +95,19 @@ __global__ void __launch_bounds__(kThreads, 1)
       sm100::prefetch_tensormap(&tmap_x);
       // The weights do not depend on earlier kernels: fill the pipeline with them before waiting
       // for the kernel that produces x, then send the x tiles after.
+      auto load_w = [&](uint8_t* a, int kt, uint64_t* bar) {   // this CTA's rows of W for k-tile kt
+        if constexpr (EPI == EPI_SWIGLU_HALF) {   // tmap_w's box has 64 rows here: gate rows, then the up rows second_off further on
+          sm100::tma_load_2d(a, &tmap_w, kt * BK, n0, bar);
+          sm100::tma_load_2d(a + TL::kABytes / 2, &tmap_w, kt * BK, n0 + second_off, bar);
+        } else {
+#pragma unroll
+          for (int m = 0; m < MT; m++) sm100::tma_load_2d(a + m * TL::kABytes, &tmap_w, kt * BK, n0 + m * second_off, bar);
+        }
+      };
       const int first = min(nkt, STAGES);
       for (int i = 0; i < first; i++) {
         sm100::mbar_arrive_expect_tx(&full[i], TL::kStageBytes);
-#pragma unroll
-        for (int m = 0; m < MT; m++)
-          sm100::tma_load_2d(tiles + i * TL::kStageBytes + m * TL::kABytes, &tmap_w, (kt_begin + i) * BK, n0 + m * second_off, &full[i]);
+        load_w(tiles + i * TL::kStageBytes, kt_begin + i, &full[i]);
       }
       ib::pdl_wait();
       for (int i = 0; i < first; i++)
@@ -110,8 +120,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         uint8_t* a = tiles + s * TL::kStageBytes;
         sm100::mbar_arrive_expect_tx(&full[s], TL::kStageBytes);
-#pragma unroll
-        for (int m = 0; m < MT; m++) sm100::tma_load_2d(a + m * TL::kABytes, &tmap_w, (kt_begin + i) * BK, n0 + m * second_off, &full[s]);
+        load_w(a, kt_begin + i, &full[s]);
         sm100::tma_load_2d(a + MT * TL::kABytes, &tmap_x, (kt_begin + i) * BK, t0, &full[s]);
       }
     }
@@ -207,6 +216,42 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
       }
     }
+    if constexpr (EPI == EPI_SWIGLU_HALF) {
+      // Lanes 0-63 of the accumulator (warps with q = 0, 1) hold gate rows, lanes 64-127 (q = 2, 3) the matching up rows. The up
+      // half goes through shared memory (the pipeline's stages are free once the accumulator is complete) to the warps that
+      // hold the gate half, which apply the activation and store. All four warps meet at a barrier of their own, whatever ok says.
+      float* up_s = (float*)tiles;   // [64][BN]
+      uint32_t r[CH];
+      static_assert(BN <= 64, "the half-and-half form is for few tokens");
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += CH) {
+        if (ok) {
+          if constexpr (CH == 32)
+            sm100::tmem_ld_32x32b_x32(lane_addr + c0, r);
+          else
+            sm100::tmem_ld_32x32b_x16(lane_addr + c0, r);
+          sm100::tmem_ld_wait();
+        }
+        if (ok && q >= 2) {
+#pragma unroll
+          for (int c = 0; c < CH; c++) up_s[(c0 + c) * 64 + (q - 2) * 32 + lane] = __uint_as_float(r[c]);   // [token][row]: no bank conflicts
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (ok && q < 2) {
+          __nv_bfloat16* dst = (__nv_bfloat16*)out_;
+          const int n = n0 + q * 32 + lane;
+          if (n < N) {
+#pragma unroll
+            for (int c = 0; c < CH; c++) {
+              const int t = t0 + c0 + c;
+              const float gv = __uint_as_float(r[c]), uv = up_s[(c0 + c) * 64 + q * 32 + lane];
+              if (t < T) dst[(size_t)t * N + n] = __float2bfloat16_rn(__fdividef(gv, 1.f + __expf(-gv)) * uv);
+            }
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");   // the buffer is read before the next chunk overwrites it
+      }
+    }
   }
   sm100::tc_fence_before();
   __syncthreads();
@@ -242,7 +287,7 @@ int launch(const CUtensorMap& tw, const CUtensorMap& tx, void* out, int T, int N
     IB_CHECK_ARG(e == cudaSuccess, "gemm_tcgen05: cannot reserve %d bytes of shared memory: %s", TL::kSmemBytes, cudaGetErrorString(e));
     configured = true;
   }
-  const int cols_per_cta = EPI == EPI_SWIGLU ? BM : BM * MT;
+  const int cols_per_cta = EPI == EPI_SWIGLU_HALF ? BM / 2 : EPI == EPI_SWIGLU ? BM : BM * MT;
   dim3 grid((T + BN - 1) / BN, (N + cols_per_cta - 1) / cols_per_cta, splits);
   IB_CHECK_ARG(grid.y <= 65535, "gemm_tcgen05: N=%d gives more than 65535 row blocks", N);
   ib::launch(gemm_tcgen05_kernel<BN, MT, EPI>, grid, kThreads, TL::kSmemBytes, stream, tw, tx, out, T, N, K, kt_per_split, second_off, ib_wait_limit_ns(), starve, status);
@@ -306,19 +351,27 @@ extern "C" int ib_test_gemm_tcgen05_starved(const void* x, const void* w, float*
 }
 
 // SwiGLU front half in one kernel: w [2*I, K] = gate rows then up rows; act [T, I] bfloat16 =
-// silu(x gate^T) * (x up^T). bn: 64, 128 or 256 tokens per CTA.
+// silu(x gate^T) * (x up^T). bn: 16 or 32 tokens per CTA (64 gate rows and their 64 up rows in one accumulator: I must be a
+// multiple of 64), or 64, 128 or 256 (128 gate rows and 128 up rows in two accumulators).
 extern "C" int ib_gemm_swiglu_tcgen05(const void* x, const void* w, void* act, int T, int I, int K, int bn, unsigned* status,
                                       cudaStream_t stream) {
   if (T == 0 || I == 0) return 0;
   if (check_common("gemm_swiglu_tcgen05", x, w, T, I, K, bn)) return 1;
   const int total_kt = (K + BK - 1) / BK;
   CUtensorMap tw, tx;
+  if (bn == 16 || bn == 32) {
+    IB_CHECK_ARG(I % 64 == 0, "gemm_swiglu_tcgen05: with %d tokens per CTA the intermediate size must be a multiple of 64, not %d", bn, I);
+    if (make_tmap(&tw, w, 2 * I, K, BM / 2)) return 1;
+    if (make_tmap(&tx, x, T, K, bn)) return 1;
+    if (bn == 16) return launch<16, 1, EPI_SWIGLU_HALF>(tw, tx, act, T, I, K, 1, total_kt, I, status, stream);
+    return launch<32, 1, EPI_SWIGLU_HALF>(tw, tx, act, T, I, K, 1, total_kt, I, status, stream);
+  }
   if (make_tmap(&tw, w, 2 * I, K, BM)) return 1;
   if (make_tmap(&tx, x, T, K, bn)) return 1;
   switch (bn) {
     case 64: return launch<64, 2, EPI_SWIGLU>(tw, tx, act, T, I, K, 1, total_kt, I, status, stream);
     case 128: return launch<128, 2, EPI_SWIGLU>(tw, tx, act, T, I, K, 1, total_kt, I, status, stream);
     case 256: return launch<256, 2, EPI_SWIGLU>(tw, tx, act, T, I, K, 1, total_kt, I, status, stream);
-    default: return ib_set_error("gemm_swiglu_tcgen05: token tile %d is not one of 64, 128, 256", bn);
+    default: return ib_set_error("gemm_swiglu_tcgen05: token tile %d is not one of 16, 32, 64, 128, 256", bn);
   }
 }

@@ -115,6 +115,33 @@ def test_gemm_swiglu_tcgen05(status, T, I, K, bn):
     assert ((act.double() - ref).abs() <= 2.0 ** -8 * ref.abs() + 1e-5 * ref.abs().max()).all()
 
 
+@pytest.mark.parametrize("T,I,K", [(1, 64, 64), (8, 12288, 4096), (5, 192, 72), (16, 640, 136), (17, 1344, 264), (32, 9536, 520), (3, 17408, 5120)])
+def test_gemm_swiglu_few_tokens(status, T, I, K):
+    """Up to 32 tokens: 64 gate rows and their 64 up rows in one accumulator, the halves meeting in the epilogue. Intermediate
+    sizes that are no multiple of 128 (but of 64), k-ranges that end inside a k-tile, one token."""
+    from inference_bench_b200.kernels import gemm_tcgen05 as G
+    from inference_bench_b200.kernels import lib as L
+    x = (torch.randn(T, K, generator=_g(5)) * 0.5).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(2 * I, K, generator=_g(6)) * (3.0 / math.sqrt(K))).to(torch.bfloat16).to(DEV)
+    act = torch.full((T, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    called = []
+    real = L.call
+    L.call = lambda name, *a: (called.append((name, a[6] if name == "ib_gemm_swiglu_tcgen05" else None)), real(name, *a))[1]
+    try:
+        G.gemm_swiglu(x, w, act, status)
+    finally:
+        L.call = real
+    assert called == [("ib_gemm_swiglu_tcgen05", 16 if T <= 16 else 32)]
+    gu = x.double() @ w.double().T
+    g, u = gu[:, :I], gu[:, I:]
+    ref = g / (1 + torch.exp(-g)) * u
+    assert status.item() == 0
+    assert ((act.double() - ref).abs() <= 2.0 ** -8 * ref.abs() + 1e-5 * ref.abs().max()).all()
+    with pytest.raises(L.KernelError, match="multiple of 64"):
+        G.gemm_swiglu(x, torch.zeros(2 * 100, K, dtype=torch.bfloat16, device=DEV), torch.empty(T, 100, dtype=torch.bfloat16, device=DEV), status, bn=16)
+    assert G.swiglu_supported(8, 4096, 12288) and not G.swiglu_supported(8, 4096, 3072) and not G.swiglu_supported(8, 4096, 12300)
+
+
 @pytest.mark.parametrize("T,N,K", [(256, 256, 64), (257, 130, 72), (300, 520, 264), (1000, 1000, 1024), (2048, 1536, 512), (4152, 640, 256)])
 def test_gemm_tcgen05_cta_pairs(status, T, N, K):
     """The persistent CTA-pair kernel (cta_group::2), more tiles than pairs included."""
