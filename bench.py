@@ -40,6 +40,8 @@ CONTEXT = 4096          # benchmark context length
 PROMPT = 2048           # prefill length, and the context each decode request starts from
 PAGE = 16           # keys per cache page of the benchmark configuration
 PAGE_ENGINE = 64    # the engine's own default (one TMA box of 64 rows per page, plane and half head): measured too, as extra points
+SETTLE_MS = 250     # idle time between building the requests' contexts (prefill at full power) and a decode measurement's warm-up steps:
+                    # the power limiter's clock reduction after the prefill would otherwise be charged to the decode steps
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -58,12 +60,19 @@ class ClockSampler:
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self):
-        self.rows: list[list[str]] = []
+        self.rows: list[list[str]] = []      # each with the time it arrived at
         self.proc = None
+        self.begin = self.end = None         # the timed region, by time.perf_counter()
+
+    def mark_begin(self):
+        self.begin = time.perf_counter()
+
+    def mark_end(self):
+        self.end = time.perf_counter()
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -71,14 +80,17 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append([c.strip() for c in line.split(",")] + [time.perf_counter()])
 
     def stop(self) -> dict:
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         time.sleep(0.15)
         self.proc.terminate()
-        rows = [r for r in self.rows if len(r) >= 7]
+        rows = [r for r in self.rows if len(r) >= 8]
+        if self.begin is not None:   # the samples of the timed region; if it was too short to catch one, the first ones after its start
+            inside = [r for r in rows if self.begin <= r[-1] <= (self.end or float("inf")) + 0.03]
+            rows = inside or [r for r in rows if r[-1] >= self.begin][:3]
         if not rows:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
@@ -140,7 +152,7 @@ def measure_prefill(engine, steps: int, warmup: int, after: int = 0) -> float:
     return statistics.median(times)
 
 
-def measure_decode_device(engine, batch: int, steps: int, warmup: int) -> tuple[float, int]:
+def measure_decode_device(engine, batch: int, steps: int, warmup: int, clocks=None) -> tuple[float, int]:
     """Milliseconds per decode step of `batch` requests whose contexts start at PROMPT tokens, steps
     enqueued back to back with tokens fed back on the device; and kernel launches per step."""
     import torch
@@ -155,6 +167,8 @@ def measure_decode_device(engine, batch: int, steps: int, warmup: int) -> tuple[
         logits = engine.runner.step([StepEntry(rid, _prompt(2000 + i, PROMPT, vocab), [PROMPT - 1])], check=False)
         last.append(int(engine.executor.sampler.sample(logits, [GREEDY], [0]).item()))
     generated = 1
+    torch.cuda.synchronize()
+    time.sleep(SETTLE_MS / 1e3)
 
     def run(n):
         nonlocal last, generated
@@ -170,10 +184,14 @@ def measure_decode_device(engine, batch: int, steps: int, warmup: int) -> tuple[
     run(max(warmup, 1))
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
+    if clocks is not None:
+        clocks.mark_begin()
     e0.record()
     run(steps)
     e1.record()
     torch.cuda.synchronize()
+    if clocks is not None:
+        clocks.mark_end()
     ms = e0.elapsed_time(e1) / steps
     launches = engine.executor.graph_for(batch).launches
     for rid in ids:
@@ -265,6 +283,8 @@ def measure_decode_e2e(engine, batch: int, steps: int, warmup: int) -> tuple[flo
         engine.submit(_prompt(3000 + i, PROMPT, vocab), max_tokens=warmup + steps + 8)
     while engine.scheduler.waiting or any(not s.decoding for s in engine.scheduler.running):
         engine.step()
+    torch.cuda.synchronize()
+    time.sleep(SETTLE_MS / 1e3)
     for _ in range(max(warmup, 1)):
         engine.step()
     ex = engine.executor
@@ -322,14 +342,15 @@ def run_ours(args) -> dict:
             report["without"] = leave_out_costs(engine, args.batch, steps, warmup, args.leave_out)
         return report
 
-    prefill_ms = measure_prefill(engine, 5, 3)
-    b1_ms, _ = measure_decode_device(engine, 1, steps, warmup)
-    b64_ms, _ = measure_decode_device(engine, 64, min(steps, 64), warmup)
+    # the headline first (device-timed, then through the entry point), then the other points
     clocks = ClockSampler()
-    clocks.start()
-    ms, launches = measure_decode_device(engine, args.batch, steps, warmup)
+    clocks.start()      # nvidia-smi takes a while to start reporting: it runs from here on, and the samples of the timed region are kept
+    ms, launches = measure_decode_device(engine, args.batch, steps, warmup, clocks)
     clock_report = clocks.stop()
     e2e_ms, h2d, d2h = measure_decode_e2e(engine, args.batch, steps, warmup)
+    b1_ms, _ = measure_decode_device(engine, 1, steps, warmup)
+    b64_ms, _ = measure_decode_device(engine, 64, min(steps, 64), warmup)
+    prefill_ms = measure_prefill(engine, 5, 3)
     extra = {}
     if page != PAGE_ENGINE:   # the same measurements at the engine's default page size
         del engine
@@ -355,7 +376,7 @@ def run_ours(args) -> dict:
                    "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"],
                    "vocab": cfg["vocab_size"], "global_batch": B, "seq_len": CONTEXT, "decode_context_start": PROMPT, "prefill_tokens": PROMPT,
                    "page_size": page, "weights": "random N(0,0.02) bf16 seed 0", "parallelism": "single_gpu",
-                   "l2": "inputs larger than L2 (weights read every step)", "peaks": pk_src},
+                   "l2": "inputs larger than L2 (weights read every step)", "peaks": pk_src, "settle_ms": SETTLE_MS},
         "e2e": {"value": B * 1e3 / e2e_ms, "unit": "tok/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": launches * steps,
         "prefill": {"value": PROMPT * 1e3 / prefill_ms, "tokens": PROMPT, "ms": prefill_ms, "frac": flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12)},
