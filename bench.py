@@ -152,7 +152,7 @@ def measure_prefill(engine, steps: int, warmup: int, after: int = 0) -> float:
     return statistics.median(times)
 
 
-def measure_decode_device(engine, batch: int, steps: int, warmup: int, clocks=None) -> tuple[float, int]:
+def measure_decode_device(engine, batch: int, steps: int, warmup: int, clocks=None, start: int = PROMPT) -> tuple[float, int]:
     """Milliseconds per decode step of `batch` requests whose contexts start at PROMPT tokens, steps
     enqueued back to back with tokens fed back on the device; and kernel launches per step."""
     import torch
@@ -164,7 +164,10 @@ def measure_decode_device(engine, batch: int, steps: int, warmup: int, clocks=No
     last = []
     for i, rid in enumerate(ids):
         engine.cache.admit(rid)
-        logits = engine.runner.step([StepEntry(rid, _prompt(2000 + i, PROMPT, vocab), [PROMPT - 1])], check=False)
+        toks = _prompt(2000 + i, start, vocab)
+        for a in range(0, start, PROMPT):   # the context, in portions of the benchmark's prefill length
+            part = toks[a:a + PROMPT]
+            logits = engine.runner.step([StepEntry(rid, part, [len(part) - 1] if a + PROMPT >= start else [])], check=False)
         last.append(int(engine.executor.sampler.sample(logits, [GREEDY], [0]).item()))
     generated = 1
     torch.cuda.synchronize()
@@ -201,7 +204,8 @@ def measure_decode_device(engine, batch: int, steps: int, warmup: int, clocks=No
 
 
 LEAVE_OUT = {   # kinds of kernel by the library entry points that launch them
-    "attention": ["ib_attention_decode", "ib_attention_decode_stream", "ib_attention_decode_fused"],
+    "attention": ["ib_attention_decode", "ib_attention_decode_stream", "ib_attention_decode_fused", "ib_attention_prefill_ws", "ib_attention_prefill_tc"],
+    "head": ["ib_embed", "ib_sample_rows"],
     "norm": ["ib_add_rmsnorm"], "silu_mul": ["ib_silu_mul"], "qk": ["ib_qk_norm_rope_kv"], "sampling": ["ib_sample_rows"],
     "gemm": ["ib_gemm_tcgen05", "ib_gemm_swiglu_tcgen05", "ib_gemm_swiglu_tcgen05_2cta", "ib_gemm_tcgen05_2cta", "ib_gemm_tcgen05_2cta_add"],
     "small": ["ib_add_rmsnorm", "ib_silu_mul", "ib_qk_norm_rope_kv", "ib_rope_table", "ib_sample_rows", "ib_embed"],
@@ -323,10 +327,25 @@ def run_ours(args) -> dict:
     if args.only == "prefill" and args.prefill_after:   # a portion deep in a long context: a cache for one such request
         engine = make_engine(cfg, page, 1, args.prefill_after + PROMPT)
         return {"only": "prefill", "layers": layers, "after": args.prefill_after, "ms": measure_prefill(engine, args.steps, 1, args.prefill_after)}
-    engine = make_engine(cfg, page, big)
+    start = args.context_start
+    if args.only == "decode" and start != PROMPT:   # another context length: a cache for just these requests
+        engine = make_engine(cfg, page, max(args.batch, 8), start + CONTEXT - PROMPT)
+    else:
+        engine = make_engine(cfg, page, big)
     steps, warmup = args.steps, max(args.warmup, 3)
     if args.only == "prefill":   # one part alone, for profiling: a short report, not the benchmark line
-        return {"only": "prefill", "layers": layers, "ms": measure_prefill(engine, args.steps, 1)}
+        report = {"only": "prefill", "layers": layers, "ms": measure_prefill(engine, args.steps, 2)}
+        if args.leave_out:
+            from inference_bench_b200.kernels import lib as L
+            real, report["without"] = L.call, {}
+            try:
+                for kind in args.leave_out.split(","):
+                    names = set(sum((LEAVE_OUT[k] for k in kind.split("+")), []))
+                    L.call = lambda name, *a, _n=names: None if name in _n else real(name, *a)
+                    report["without"][kind] = measure_prefill(engine, args.steps, 2)
+            finally:
+                L.call = real
+        return report
     if args.only == "mixed":
         clocks = ClockSampler()
         clocks.start()
@@ -336,8 +355,10 @@ def run_ours(args) -> dict:
                 "roofline": {"bound": "hbm", "achieved": step_bytes / (ms * 1e-3) / 1e9, "peak": pk["hbm_gbs"], "unit": "GB/s",
                              "frac": step_bytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"]}, "peaks": pk_src, "clocks": clocks.stop()}
     if args.only == "decode":
-        ms, launches = measure_decode_device(engine, args.batch, steps, warmup)
-        report = {"only": "decode", "layers": layers, "batch": args.batch, "ms_per_step": ms, "launches_per_step": launches}
+        ms, launches = measure_decode_device(engine, args.batch, steps, warmup, start=start)
+        step_bytes = weight_bytes(cfg, layers) + args.batch * (start + 1 + warmup + steps / 2) * kv_bytes_per_token(cfg, layers)
+        report = {"only": "decode", "shape": args.shape, "layers": layers, "batch": args.batch, "context_start": start, "page_size": page, "ms_per_step": ms,
+                  "tok_s": args.batch * 1e3 / ms, "launches_per_step": launches, "hbm_frac": step_bytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"]}
         if args.leave_out:
             report["without"] = leave_out_costs(engine, args.batch, steps, warmup, args.leave_out)
         return report
@@ -397,7 +418,8 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (both numbers are reported)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--prefill-after", type=int, default=0, help="with --only prefill: the 2,048-token portion follows this many cached tokens of the same request")
-    ap.add_argument("--leave-out", default="", help="with --only decode: also time the step without each of these kinds of kernel (comma separated; "
+    ap.add_argument("--context-start", type=int, default=PROMPT, help="with --only decode: the context each request starts from (default: the benchmark's 2,048)")
+    ap.add_argument("--leave-out", default="", help="with --only decode or prefill: also time the step without each of these kinds of kernel (comma separated; "
                     "a+b leaves both out): " + ", ".join(sorted(LEAVE_OUT)))
     ap.add_argument("--only", default="", choices=["", "prefill", "decode", "mixed"], help="run one part alone (for profiling); prints a short report")
     args = ap.parse_args()
