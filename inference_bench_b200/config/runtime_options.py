@@ -56,6 +56,7 @@ class RuntimeOptions:
     strict_weights: bool = False       # an unexpected tensor in the checkpoint is an error instead of a note
     # ---- failure reporting
     wait_limit_ms: int = 2000          # how long a bounded wait inside a kernel may last before it gives up and sets the status word
+    nvtx: bool = False                 # NVTX ranges around every step and every schedule entry (for ncu --nvtx-include and timelines); off: no cost
 
     def __post_init__(self):
         for name, allowed in _CHOICES.items():

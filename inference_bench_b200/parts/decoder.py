@@ -82,16 +82,33 @@ class Decoder:
     def forward(self, ctx) -> Optional[torch.Tensor]:
         """Runs the step's tokens through the schedule; returns float32 logits [K, V] at the wanted
         rows, or None when no row is wanted (the caches are still filled)."""
+        nvtx = torch.cuda.nvtx if ctx.rt.options.nvtx else None
+        if nvtx:
+            nvtx.range_push(f"step {ctx.n_tokens} tokens in {ctx.n_segments} segments")
+            nvtx.range_push("embedding")
         x = self.embedding.forward(ctx)
+        if nvtx:
+            nvtx.range_pop()
         pending = None
         trace = ctx.trace
         if trace is not None:
             trace.append(self._residual_rows(ctx, x, None))
         for i, e in enumerate(self.plan.schedule):
+            if nvtx:
+                nvtx.range_push(f"entry {i} layer {e.layer}")
             pending = self.blocks[e.layer].forward(ctx, x, pending, ctx.caches[i] if ctx.caches else None)
+            if nvtx:
+                nvtx.range_pop()
             if trace is not None:
                 trace.append(self._residual_rows(ctx, x, pending))
-        if ctx.logit_rows.shape[0] == 0:
-            return None
-        h = self.final_norm.forward(ctx, x, pending, rows=ctx.logit_rows)
-        return self.head.forward(ctx, h)
+        logits = None
+        if ctx.logit_rows.shape[0] != 0:
+            if nvtx:
+                nvtx.range_push("head")
+            h = self.final_norm.forward(ctx, x, pending, rows=ctx.logit_rows)
+            logits = self.head.forward(ctx, h)
+            if nvtx:
+                nvtx.range_pop()
+        if nvtx:
+            nvtx.range_pop()
+        return logits

@@ -234,3 +234,22 @@ def test_serving_sizes_reach_the_serving_kernels(serving, monkeypatch):
     for name in ("ib_gemm_qkv_tcgen05_2cta", "ib_gemm_tcgen05_2cta_add", "ib_gemm_swiglu_tcgen05_2cta", "ib_gemm_tcgen05", "ib_attention_prefill_ws",
                  "ib_attention_decode_fused", "ib_add_rmsnorm"):
         assert called.get(name, 0) > 0, f"{name} never ran: {sorted(called)}"
+
+
+def test_runtime_options_reach_the_engine(model_dirs):
+    """Options given to the entry point are the ones the runtime carries, and an engine with everything optional switched off
+    (no graphs, no pipeline, no early launches, no fused forms, NVTX ranges on) generates the plain model's tokens."""
+    from inference_bench_b200.config.runtime_options import RuntimeOptions
+    name = "D"
+    vocab = CONFIGS[name]["config"]["vocab_size"]
+    p = traces.prompt(12, 70, vocab)
+    want = PlainModel(model_dirs[name]).greedy(p, 6)
+    off = RuntimeOptions(graphs=False, pipeline=False, pdl=False, fuse=False, nvtx=True, decode_attention="split", prefill_attention="tcgen05")
+    eng = _engine(model_dirs, name, "float32", options=off)
+    assert eng.rt.options.pdl is False and eng.rt.options.dtype == "float32" and eng.rt.options.page_size == CONFIGS[name]["page_size"]
+    assert eng.executor.use_graphs is False and eng.scheduler.cfg.pipeline is False
+    assert eng.generate(p, max_tokens=6).tokens == want
+    eng16 = _engine(model_dirs, name, "bfloat16", options={"fuse": False, "decode_attention": "split", "prefill_attention": "tcgen05", "nvtx": True})
+    on16 = _engine(model_dirs, name, "bfloat16")
+    a, b = eng16.logits(p), on16.logits(p)
+    assert (a - b).abs().max() <= 2e-2 * b.abs().max() and not torch.equal(a, b)      # other kernels, the same model
