@@ -7,7 +7,8 @@
     python -m inference_bench_b200 spec       --model DIR|SPEC.toml
     python -m inference_bench_b200 random-model --config CONFIG.json --seed N --out DIR
 
-Added here: --temperature, --seed, --top-k, --top-p, --min-p, --dtype bfloat16|float32, and the random-model command.
+Added here: --temperature, --seed, --top-k, --top-p, --min-p, --dtype bfloat16|float32, --runtime NAME=VALUE, --random-weights SEED
+(weights made on the device: --model is then a config.json), and the random-model command.
 Prompts are token ids unless the model folder has a tokenizer.json; --prompt-len makes a synthetic
 prompt of that many token ids, 1000 + (i*7) % 5000 clipped to the vocabulary, like the reference's
 bench tool (crates/specrt/src/bin/bench.rs:320-343).
@@ -67,7 +68,12 @@ def _runtime_overrides(args) -> dict:
 
 def _engine(args, **kw):
     from .engine.engine import Engine
-    return Engine(args.model, dtype=args.dtype, max_ctx=args.max_ctx, options=_runtime_overrides(args) or None, **kw)
+    model = args.model
+    seed = getattr(args, "random_weights", None)
+    if seed is not None:   # weights made on the device from a seed: --model is then a config.json (or a folder that has one)
+        path = Path(model)
+        model = json.loads((path / "config.json" if path.is_dir() else path).read_text())
+    return Engine(model, dtype=args.dtype, max_ctx=args.max_ctx, options=_runtime_overrides(args) or None, random_weights_seed=seed, **kw)
 
 
 def _sampling(args):
@@ -109,6 +115,7 @@ def cmd_batch(args) -> int:
     results = []
     for n in sizes:
         prompts = [_synthetic_prompt(args.prompt_len, vocab, seed=i) for i in range(n)]
+        engine.generate(prompts, max_tokens=3)    # untimed: captures this batch size's decode graph and warms the kernels' one-time set-up
         t0 = time.perf_counter()
         replies = engine.generate(prompts, max_tokens=args.max_tokens, sampling=_sampling(args))
         wall = time.perf_counter() - t0
@@ -191,6 +198,7 @@ def main(argv=None) -> int:
     def common(p, prompt=True):
         p.add_argument("--model", required=True, help="folder with config.json and model.safetensors, a hub id in the hub cache, or a TOML model spec")
         p.add_argument("--runtime", action="append", metavar="NAME=VALUE", help="a runtime option laid over the model spec's [runtime] table (may be repeated)")
+        p.add_argument("--random-weights", type=int, default=None, metavar="SEED", help="make random weights on the device from this seed; --model is then a config.json")
         p.add_argument("--max-ctx", type=int, default=None, help="context limit (default 2048, capped by max_position_embeddings)")
         p.add_argument("--dtype", default=None, choices=["bfloat16", "float32"], help="default: the model spec's [runtime] dtype, else bfloat16")
         if prompt:
