@@ -351,20 +351,21 @@ extern "C" int ib_test_gemm_tcgen05_starved(const void* x, const void* w, float*
 }
 
 // SwiGLU front half in one kernel: w [2*I, K] = gate rows then up rows; act [T, I] bfloat16 =
-// silu(x gate^T) * (x up^T). bn: 16 or 32 tokens per CTA (64 gate rows and their 64 up rows in one accumulator: I must be a
-// multiple of 64), or 64, 128 or 256 (128 gate rows and 128 up rows in two accumulators).
-extern "C" int ib_gemm_swiglu_tcgen05(const void* x, const void* w, void* act, int T, int I, int K, int bn, unsigned* status,
+// silu(x gate^T) * (x up^T). bn: 16 or 32 tokens per CTA, or 64 with half != 0 (64 gate rows and their 64 up rows in one
+// accumulator: I must be a multiple of 64), or 64, 128 or 256 (128 gate rows and 128 up rows in two accumulators).
+extern "C" int ib_gemm_swiglu_tcgen05(const void* x, const void* w, void* act, int T, int I, int K, int bn, int half, unsigned* status,
                                       cudaStream_t stream) {
   if (T == 0 || I == 0) return 0;
   if (check_common("gemm_swiglu_tcgen05", x, w, T, I, K, bn)) return 1;
   const int total_kt = (K + BK - 1) / BK;
   CUtensorMap tw, tx;
-  if (bn == 16 || bn == 32) {
+  if (bn == 16 || bn == 32 || (bn == 64 && half)) {
     IB_CHECK_ARG(I % 64 == 0, "gemm_swiglu_tcgen05: with %d tokens per CTA the intermediate size must be a multiple of 64, not %d", bn, I);
     if (make_tmap(&tw, w, 2 * I, K, BM / 2)) return 1;
     if (make_tmap(&tx, x, T, K, bn)) return 1;
     if (bn == 16) return launch<16, 1, EPI_SWIGLU_HALF>(tw, tx, act, T, I, K, 1, total_kt, I, status, stream);
-    return launch<32, 1, EPI_SWIGLU_HALF>(tw, tx, act, T, I, K, 1, total_kt, I, status, stream);
+    if (bn == 32) return launch<32, 1, EPI_SWIGLU_HALF>(tw, tx, act, T, I, K, 1, total_kt, I, status, stream);
+    return launch<64, 1, EPI_SWIGLU_HALF>(tw, tx, act, T, I, K, 1, total_kt, I, status, stream);
   }
   if (make_tmap(&tw, w, 2 * I, K, BM)) return 1;
   if (make_tmap(&tx, x, T, K, bn)) return 1;

@@ -20,7 +20,7 @@ FITTED_SM_COUNT = 148   # the part the cost model below was fitted on; every fun
 TOKEN_TILES = (16, 32, 64, 128, 256)
 
 L.register("ib_gemm_tcgen05", [L._p, L._p, L._p, L._i, L._i, L._i, L._i, L._i, L._i, L._p, L._p])
-L.register("ib_gemm_swiglu_tcgen05", [L._p, L._p, L._p, L._i, L._i, L._i, L._i, L._p, L._p])
+L.register("ib_gemm_swiglu_tcgen05", [L._p, L._p, L._p, L._i, L._i, L._i, L._i, L._i, L._p, L._p])
 L.register("ib_gemm_tcgen05_2cta", [L._p, L._p, L._p, L._i, L._i, L._i, L._p, L._p])
 L.register("ib_gemm_swiglu_tcgen05_2cta", [L._p, L._p, L._p, L._i, L._i, L._i, L._p, L._p])
 L.register("ib_gemm_tcgen05_2cta_add", [L._p, L._p, L._p, L._i, L._i, L._i, L._p, L._p])
@@ -204,35 +204,44 @@ def linear(rt, x: torch.Tensor, lw, allow_split: bool = True, add_to: Optional[t
 PAIR_SWIGLU_MIN_TILES = 40   # 256-column blocks of the intermediate size from which the CTA-pair kernel takes the fused gate/up product of 33 to 128 tokens
 
 
-HALF_SWIGLU_MIN_CTAS = 148   # CTAs (intermediate size / 64) from which the form for up to 32 tokens is used
+HALF_SWIGLU_MIN_CTAS = 148   # CTAs (intermediate size / 64) from which the form with gate and up rows in one accumulator is used
+HALF_SWIGLU_MAX_TOKENS = 64   # ... and up to how many tokens (at 64 tokens 0.7 % of a batch-64 decode step faster than the CTA-pair form, Qwen3-8B shape)
 
 
 def swiglu_supported(T: int, k: int, inter: int = 0) -> bool:
     """Whether the gate/up product applies the activation in its epilogue: from 65 tokens always; from 33 where the
     intermediate size gives the CTA-pair kernel 40 tiles or more (measured 8 to 10 % faster there than the split-K
-    product followed by the SiLU-mul kernel, at the 8B, 14B and 32B shapes; slower at the 0.6B shape); up to 32 tokens
+    product followed by the SiLU-mul kernel, at the 8B, 14B and 32B shapes; slower at the 0.6B shape); up to 64 tokens
     in the form that puts 64 gate rows and their 64 up rows into one accumulator, where the intermediate size is a
     multiple of 64 and gives every SM a CTA (a smaller one goes through the split-K product and the SiLU-mul kernel,
     which then fill the GPU better)."""
     if not supports(k):
         return False
-    if T <= 32:
-        return inter % 64 == 0 and inter // 64 >= HALF_SWIGLU_MIN_CTAS
-    return T > 64 or -(-inter // 256) >= PAIR_SWIGLU_MIN_TILES
+    if half_swiglu(T, inter):
+        return True
+    return T > 64 or (T > 32 and -(-inter // 256) >= PAIR_SWIGLU_MIN_TILES)
 
 
-def gemm_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tensor, status: torch.Tensor, bn: int | None = None, pair_min_tokens: int = 129) -> None:
+def half_swiglu(T: int, inter: int) -> bool:
+    """Whether the fused gate/up product of T tokens takes the form with 64 gate rows and 64 up rows in one accumulator."""
+    return T <= HALF_SWIGLU_MAX_TOKENS and inter % 64 == 0 and inter // 64 >= HALF_SWIGLU_MIN_CTAS
+
+
+def gemm_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tensor, status: torch.Tensor, bn: int | None = None, pair_min_tokens: int = 129,
+                half: bool | None = None) -> None:
     """act [T, I] bfloat16 = silu(x gate^T) * (x up^T) with w_gate_up [2I, K] = gate rows then up rows."""
     T, K = x.shape
     I = w_gate_up.shape[0] // 2
     ops._check("x", x, torch.bfloat16)
     ops._check("w_gate_up", w_gate_up, torch.bfloat16, (2 * I, K))
     ops._check("act", act, torch.bfloat16, (T, I))
-    if bn is None and T <= 32 and I % 64 == 0:
-        bn = 16 if T <= 16 else 32
+    if bn is None and (half_swiglu(T, I) or (T <= 32 and I % 64 == 0)):
+        bn, half = (16 if T <= 16 else 32 if T <= 32 else 64), True
+    if half is None:
+        half = bn in (16, 32)
     if bn is None and (T >= pair_min_tokens or (T > 32 and -(-I // 256) >= PAIR_SWIGLU_MIN_TILES)):
         L.call("ib_gemm_swiglu_tcgen05_2cta", x.data_ptr(), w_gate_up.data_ptr(), act.data_ptr(), T, I, K, status.data_ptr(), ops._stream())
         return
     if bn is None:
         bn = 64 if T <= 64 else (128 if T <= 128 else 256)
-    L.call("ib_gemm_swiglu_tcgen05", x.data_ptr(), w_gate_up.data_ptr(), act.data_ptr(), T, I, K, bn, status.data_ptr(), ops._stream())
+    L.call("ib_gemm_swiglu_tcgen05", x.data_ptr(), w_gate_up.data_ptr(), act.data_ptr(), T, I, K, bn, 1 if half else 0, status.data_ptr(), ops._stream())

@@ -132,6 +132,9 @@ def test_gemm_swiglu_few_tokens(status, T, I, K):
     finally:
         L.call = real
     assert called == [("ib_gemm_swiglu_tcgen05", 16 if T <= 16 else 32)]
+    act64 = torch.full((T, I), float("nan"), dtype=torch.bfloat16, device=DEV)      # the same form with 64 tokens per CTA
+    G.gemm_swiglu(x, w, act64, status, bn=64, half=True)
+    assert torch.equal(act64, act)
     gu = x.double() @ w.double().T
     g, u = gu[:, :I], gu[:, I:]
     ref = g / (1 + torch.exp(-g)) * u
