@@ -206,6 +206,7 @@ def measure_decode_device(engine, batch: int, steps: int, warmup: int, clocks=No
 LEAVE_OUT = {   # kinds of kernel by the library entry points that launch them
     "attention": ["ib_attention_decode", "ib_attention_decode_stream", "ib_attention_decode_fused", "ib_attention_prefill_ws", "ib_attention_prefill_tc"],
     "head": ["ib_embed", "ib_sample_rows"],
+    "qkv": ["ib_gemm_qkv_tcgen05_2cta"],
     "norm": ["ib_add_rmsnorm"], "silu_mul": ["ib_silu_mul"], "qk": ["ib_qk_norm_rope_kv"], "sampling": ["ib_sample_rows"],
     "gemm": ["ib_gemm_tcgen05", "ib_gemm_swiglu_tcgen05", "ib_gemm_swiglu_tcgen05_2cta", "ib_gemm_tcgen05_2cta", "ib_gemm_tcgen05_2cta_add"],
     "small": ["ib_add_rmsnorm", "ib_silu_mul", "ib_qk_norm_rope_kv", "ib_rope_table", "ib_sample_rows", "ib_embed"],
