@@ -253,3 +253,63 @@ def test_runtime_options_reach_the_engine(model_dirs):
     on16 = _engine(model_dirs, name, "bfloat16")
     a, b = eng16.logits(p), on16.logits(p)
     assert (a - b).abs().max() <= 2e-2 * b.abs().max() and not torch.equal(a, b)      # other kernels, the same model
+
+
+@pytest.mark.parametrize("name,seed", [("B", 0), ("C", 1)])
+def test_random_traffic_matches_plain(model_dirs, name, seed):
+    """Requests that arrive at random steps with random lengths, greedy and seeded sampling, stop tokens, a few cancelled in
+    flight, a pool so small that requests are preempted and recomputed; CUDA graphs and steps kept one ahead. Float32: what
+    every request generated equals what the plain model generates for it alone (a cancelled one: a prefix of it)."""
+    from inference_bench_b200 import SamplingParams
+    from inference_bench_b200.engine.scheduler import Request
+    rng = np.random.default_rng(seed)
+    vocab = CONFIGS[name]["config"]["vocab_size"]
+    page = CONFIGS[name]["page_size"]
+    plain = PlainModel(model_dirs[name])
+    n_req = 18
+    reqs = []
+    for i in range(n_req):
+        p = traces.prompt(1000 + 31 * seed + i, int(rng.integers(1, 12) if rng.random() < 0.6 else rng.integers(12, 60)), vocab)   # short prompts are admitted side by side
+        new = int(rng.integers(1, 40))                                                                                          # ... and then outgrow the pool
+        sp = SamplingParams() if rng.random() < 0.5 else SamplingParams(temperature=float(rng.choice([0.7, 1.1])), seed=int(rng.integers(0, 10 ** 6)), top_k=int(rng.choice([0, 5, 40])))
+        full = plain.greedy(p, new) if sp.temperature == 0 else plain.sample(p, new, sp.temperature, sp.seed, sp.top_k)
+        stop = ()
+        if len(full) > 4 and rng.random() < 0.4:
+            stop = (int(full[int(rng.integers(2, len(full)))]),)
+        want = full[:full.index(stop[0])] if stop and stop[0] in full else full
+        reqs.append(dict(prompt=p, new=new, sp=sp, stop=stop, want=want, arrive=int(rng.integers(0, 40)), cancel=(int(rng.integers(3, 30)) if rng.random() < 0.2 else None)))
+    longest = max(len(r["prompt"]) + r["new"] for r in reqs)
+    eng = _engine(model_dirs, name, "float32", max_ctx=128, num_pages=-(-longest // page) + 2, max_num_seqs=4, prefill_chunk=16, max_batched_tokens=40)
+    got, finish, born = {i: [] for i in range(n_req)}, {}, {}
+    preempted, step = 0, 0
+    while len(finish) < n_req and step < 4000:
+        for i, r in enumerate(reqs):
+            if r["arrive"] == step:
+                eng.scheduler.submit(Request(i, r["prompt"], r["new"], r["sp"], r["stop"]))
+                born[i] = step
+        for i, r in enumerate(reqs):
+            if r["cancel"] is not None and i in born and i not in finish and step == born[i] + r["cancel"]:
+                f = eng.cancel(i)
+                if f is not None:
+                    finish[i] = "cancelled"
+                    got[i] = list(f.tokens)
+        rep = eng.step()
+        preempted += rep.preemptions
+        for rid, tok in rep.emitted:
+            if rid not in finish:
+                got[rid].append(tok)
+        for f in rep.finished:
+            finish[f.id] = f.finish
+            assert got[f.id] == list(f.tokens), f"request {f.id}: the emitted tokens and the finished record differ"
+        eng.cache.check()
+        step += 1
+    assert len(finish) == n_req, f"{n_req - len(finish)} requests never finished"
+    assert preempted > 0, "the pool was meant to be too small"
+    eng.rt.check_status()
+    for i, r in enumerate(reqs):
+        if finish[i] == "cancelled":
+            assert got[i] == r["want"][:len(got[i])], f"request {i} (cancelled)"
+        else:
+            assert got[i] == r["want"], f"request {i} ({finish[i]}; preemptions so far {preempted})"
+            assert finish[i] == ("stop" if r["stop"] and len(r["want"]) < r["new"] else "length")
+    assert eng.cache.used_pages() == [0] * len(eng.cache.groups) and eng.cache.free_slots() == 4
