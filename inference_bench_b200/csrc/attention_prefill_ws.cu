@@ -4,14 +4,19 @@
 //              (64 keys) from tensor memory, keeps the running maximum and sum (float32, base 2), and
 //              writes P = 2^(S - m) as bfloat16 back into tensor memory over the first half of S.
 //   warp 4     issues the MMAs: S_j = Q K_j^T (A = Q, B = K, both from shared memory) one tile ahead,
-//              O += P_j V_j (A = P from tensor memory, B = V from shared memory), and the commits
-//              that free the K and V buffers and tell the softmax threads that S or O is ready.
-//   warp 5     copies: K and V tiles through the block table by TMA box copies (one per page, plane
-//              and 64 values of the head dimension) into two buffers each, as soon as one is free.
+//              O += P_j V_j (A = P from tensor memory, B = V from shared memory), and one commit after each:
+//              the first tells the softmax threads that S is there and the K warp that the K buffer is free,
+//              the second tells the V warp that the V buffer is free and the softmax threads that O has the tile.
+//   warp 5, 6  copy: one the K tiles, one the V tiles, through the block table by TMA box copies (one per page
+//              and 64 values of the head dimension, each issued by a lane of its own) into two and three buffers,
+//              as soon as one is free. A lane looks up the page of one box in 32; the loop divides nothing.
 // Nobody waits at a CTA-wide barrier inside the loop: the roles meet at mbarriers only, so the
 // tensor core works on S_{j+1} while the softmax threads are busy with tile j, and the copies run
 // ahead of both. O is rescaled (in tensor memory, by the softmax threads) only when a row's maximum
-// grows by more than 2^8, so most tiles touch O by MMA alone. Two CTAs share an SM.
+// grows by more than 2^8, so most tiles touch O by MMA alone. Two CTAs share an SM. The warps that issue
+// (MMAs, copies) run one instruction stream each, and the loop is as fast as the slowest of them: what
+// they do per tile is kept to the instructions themselves (descriptors are a constant apart, buffers and
+// parities are counted, a wait that is already over costs one try).
 // Needs the tensor map of the cache pool (ib_make_kv_map): page sizes that are a multiple of 8 and
 // divide 64, or a multiple of 64. Reference design: crates/kir/src/cuda/attention/flash_mma.rs.
 #include <cuda.h>
@@ -23,9 +28,10 @@
 namespace {
 
 constexpr int BM = 128, BN = 64;
-constexpr int kSoftmaxWarps = 4, kThreads = (kSoftmaxWarps + 2) * 32;
+constexpr int kSoftmaxWarps = 4, kThreads = (kSoftmaxWarps + 3) * 32;
 constexpr float kRescaleThreshold = 8.f;  // log2 units
 constexpr int KS = 2, VS = 3;             // buffers for K tiles and for V tiles (what two CTAs per SM leave room for)
+static_assert(KS == 2 && VS >= 2 && VS <= 4, "K buffer j % KS goes with S buffer j & 1; the parity argument for v_empty needs VS >= 2");
 constexpr int kMufu = 4;                  // of every four exponentials, how many the special-function unit computes (0, 2 or 4)
 
 __device__ __forceinline__ uint32_t blk_offset(int rows, int r, int cc) {  // 16-byte chunk cc of row r in [rows][64]-element blocks, 128-byte swizzle
@@ -69,8 +75,8 @@ template <int HD>
 struct Smem {
   static constexpr int kQ = BM * HD * 2, kKV = BN * HD * 2;
   static constexpr int oQ = 0, oK = kQ, oV = kQ + KS * kKV, oBar = kQ + (KS + VS) * kKV;
-  // barriers: k_full[KS] k_empty[KS] v_full[VS] v_empty[VS] s_full[2] p_full[2] o_full q_full; then the tmem slot and the flag
-  static constexpr int kBars = 2 * KS + 2 * VS + 6;
+  // barriers: k_full[KS] v_full[VS] v_empty[VS] s_full[2] p_full[2] q_full; then the tmem slot and the flag
+  static constexpr int kBars = KS + 2 * VS + 5;
   static constexpr int kBytes = oBar + kBars * 8 + 16;
   static_assert(kBytes <= 113 * 1024, "two CTAs must fit one SM");
 };
@@ -91,18 +97,14 @@ __global__ void __launch_bounds__(kThreads, 2)
   }
   const uint32_t q_s = sm100::smem_u32(sm + SM::oQ), k_s = sm100::smem_u32(sm + SM::oK), v_s = sm100::smem_u32(sm + SM::oV);
   uint64_t* bars = (uint64_t*)(sm + SM::oBar);
-  uint64_t *k_full = bars, *k_empty = bars + KS, *v_full = bars + 2 * KS, *v_empty = bars + 2 * KS + VS, *s_full = bars + 2 * KS + 2 * VS,
-           *p_full = s_full + 2, *o_full = s_full + 4, *q_full = s_full + 5;
+  uint64_t *k_full = bars, *v_full = bars + KS, *v_empty = bars + KS + VS, *s_full = bars + KS + 2 * VS, *p_full = s_full + 2, *q_full = s_full + 4;
   uint32_t* tmem_slot = (uint32_t*)(bars + SM::kBars);
   volatile int* gave_up = (volatile int*)(tmem_slot + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   ib::pdl_launch_dependents();
   if (tid == 0) {
-    for (int i = 0; i < KS; i++) {
-      sm100::mbar_init(&k_full[i], 1);
-      sm100::mbar_init(&k_empty[i], 1);
-    }
+    for (int i = 0; i < KS; i++) sm100::mbar_init(&k_full[i], 1);
     for (int i = 0; i < VS; i++) {
       sm100::mbar_init(&v_full[i], 1);
       sm100::mbar_init(&v_empty[i], 1);
@@ -111,7 +113,6 @@ __global__ void __launch_bounds__(kThreads, 2)
       sm100::mbar_init(&s_full[i], 1);
       sm100::mbar_init(&p_full[i], kSoftmaxWarps);
     }
-    sm100::mbar_init(o_full, 1);
     sm100::mbar_init(q_full, 1);
     *gave_up = 0;
     sm100::fence_barrier_init();
@@ -138,103 +139,109 @@ __global__ void __launch_bounds__(kThreads, 2)
   const int n_kt = kt_end - kt_begin;
   // a wait that ran out: say so once, and from then on nobody waits (the results are void, the status says so)
   auto wait = [&](uint64_t* bar, uint32_t parity) {
-    if (*gave_up) return;
+    if (sm100::mbar_try_wait(bar, parity) || *gave_up) return;
     if (!sm100::mbar_wait(bar, parity, wait_ns)) {
       *gave_up = 1;
       atomicOr(status, IB_ERR_WAIT_TIMEOUT);
     }
   };
 
-  if (warp == kSoftmaxWarps + 1) {
-    // ------------------------------------------------------------ the copying warp
+  if (warp > kSoftmaxWarps) {
+    // ------------------------------------------------------------ the copying warps: one for the K tiles, one for the V tiles
+    // One lane owns one box of every tile: box b_pg of the tile's keys (a page, where a page holds fewer than 64 keys) and
+    // the 64-value block b_hb of the head. What does not change from tile to tile is computed once; the row of a box in the
+    // pool is computed when its page is looked up (32 boxes at a time, one per lane), so the loop divides nothing.
     ib::pdl_wait();   // the kernel before wrote this portion's keys and values
     const int box_rows = min(kv.page_size, BN);
-    const int ppt = BN / box_rows;
-    const long long rows_per_page = kv.page_stride / HD, v_rows = kv.v_offset / HD;
-    int held = -2;
+    const int ppt = BN / box_rows, boxes = ppt * HB;
+    const int boxes_per_page = kv.page_size / box_rows;
+    const long long rows_per_page = kv.page_stride / HD;
+    const int v_rows = (int)(kv.v_offset / HD);
+    const int b_pg = lane / HB, b_hb = lane % HB;
+    const bool has_box = lane < boxes;
+    const uint32_t box_bytes = (uint32_t)box_rows * 128;
+    const int plane = warp - kSoftmaxWarps - 1;   // 0: this warp copies K tiles, 1: V tiles
+    const int n_buf = plane ? VS : KS;
+    uint8_t* const dst0 = sm + (plane ? SM::oV : SM::oK) + b_hb * BN * 128 + b_pg * box_bytes;
+    uint64_t* const full0 = plane ? v_full : k_full;
+    int held_row = -1;   // the row in the pool where the K rows of the box that this lane looked up begin, or -1: nothing to copy
+    int st = 0;
+    uint32_t par = 1;   // the parity to wait for before a buffer is filled again: of s_full (K), of v_empty (V)
     for (int j = 0; j < n_kt; j++) {
-      const int kt = kt_begin + j;
       const int rel = j * ppt;
       if ((rel & 31) == 0) {   // the pages of the next 32 boxes, one per lane
-        const int key0 = (kt_begin * ppt + rel + lane) * box_rows;
-        const int col = key0 / kv.page_size;
-        held = -2;
-        if (key0 <= pos_last && key0 + box_rows > key_lo) held = col < kv.table_stride ? kv.block_table[(size_t)seg * kv.table_stride + col] : -1;
-      }
-      const int my = (lane - rel) & 31;
-      const bool mine = my < ppt;
-      const bool valid = mine && held >= 0 && held < kv.num_pages;
-      if (mine && held != -2 && !valid) atomicOr(status, IB_ERR_BAD_PAGE);
-      const unsigned vmask = __ballot_sync(0xffffffffu, valid);
-      const int key0 = kt * BN + my * box_rows;
-      const long long row = (long long)held * rows_per_page + view_row0 + (long long)kvh * kv.page_size + key0 % kv.page_size;
-      const uint32_t bytes = (uint32_t)(__popc(vmask) * box_rows * 128 * HB);
-#pragma unroll 1
-      for (int plane = 0; plane < 2; plane++) {   // K of the tile, then V
-        const int st = plane ? j % VS : j % KS, round = plane ? j / VS : j / KS;
-        uint64_t* full = plane ? &v_full[st] : &k_full[st];
-        uint64_t* empty = plane ? &v_empty[st] : &k_empty[st];
-        uint8_t* dst = sm + (plane ? SM::oV : SM::oK) + st * SM::kKV;
-        if (lane == 0) wait(empty, (round & 1) ^ 1);
-        __syncwarp();
-        bool cleared = false;
-        for (int pg = 0; pg < ppt; pg++) {   // boxes that are not copied (no visible key, or no page) are cleared
-          if ((vmask >> ((rel + pg) & 31)) & 1) continue;
-          cleared = true;
-          for (int idx = lane; idx < box_rows * 8 * HB; idx += 32) {
-            const int hb = idx / (box_rows * 8), r3 = idx % (box_rows * 8);
-            mt::st_shared_zero16(sm100::smem_u32(dst + hb * BN * 128 + pg * box_rows * 128) + r3 * 16);
-          }
-        }
-        if (cleared) sm100::fence_proxy_async();
-        __syncwarp();
-        if (lane == 0) sm100::mbar_arrive_expect_tx(full, bytes);
-        __syncwarp();
-        {   // one box per lane (page, 64-value block), so that the boxes of a tile are issued side by side
-          const int b_pg = lane / HB, b_hb = lane % HB;
-          const int holder = (rel + b_pg) & 31;
-          const int page = __shfl_sync(0xffffffffu, held, holder);
-          if (lane < ppt * HB && ((vmask >> holder) & 1)) {
-            const int bkey0 = kt * BN + b_pg * box_rows;
-            const long long brow = (long long)page * rows_per_page + view_row0 + (long long)kvh * kv.page_size + bkey0 % kv.page_size + (plane ? v_rows : 0);
-            sm100::tma_load_2d(dst + b_hb * BN * 128 + b_pg * box_rows * 128, &kv_map, b_hb * 64, (int)brow, full);
-          }
+        const int box = kt_begin * ppt + rel + lane;
+        const int key0 = box * box_rows;
+        held_row = -1;
+        if (key0 <= pos_last && key0 + box_rows > key_lo) {
+          const int col = boxes_per_page == 1 ? box : box / boxes_per_page;
+          const int page = col < kv.table_stride ? kv.block_table[(size_t)seg * kv.table_stride + col] : -1;
+          if (page >= 0 && page < kv.num_pages)
+            held_row = (int)((long long)page * rows_per_page + view_row0 + (long long)kvh * kv.page_size + (key0 - col * kv.page_size));
+          else
+            atomicOr(status, IB_ERR_BAD_PAGE);
         }
       }
+      const int row = __shfl_sync(0xffffffffu, held_row, (rel + b_pg) & 31);
+      const bool ok = has_box && row >= 0;
+      const unsigned vmask = __ballot_sync(0xffffffffu, ok);
+      const int n_ok = __popc(vmask);
+      const uint32_t bytes = (uint32_t)n_ok * box_bytes;
+      // the K buffer of tile j is free when S of tile j - 2 is there (the MMA warp's commit to s_full says both); the V buffer
+      // when P V of the tile that used it has finished
+      uint64_t* const empty = plane ? &v_empty[st] : j >= KS ? &s_full[st] : nullptr;
+      uint8_t* const dst = dst0 + st * SM::kKV;
+      if (lane == 0 && empty) wait(empty, par);
+      __syncwarp();
+      if (n_ok != boxes) {   // boxes that are not copied (no visible key, or no page) are cleared: the tile's edge, seldom
+        for (int b = 0; b < boxes; b++) {
+          if ((vmask >> b) & 1) continue;
+          const uint32_t d0 = sm100::smem_u32(dst) + ((b % HB) - b_hb) * BN * 128 + ((b / HB) - b_pg) * (int)box_bytes;
+          for (int idx = lane; idx < box_rows * 8; idx += 32) mt::st_shared_zero16(d0 + idx * 16);
+        }
+        sm100::fence_proxy_async();
+        __syncwarp();
+      }
+      if (lane == 0) sm100::mbar_arrive_expect_tx(&full0[st], bytes);
+      if (ok) sm100::tma_load_2d(dst, &kv_map, b_hb * 64, row + plane * v_rows, &full0[st]);
+      if (++st == n_buf) st = 0, par ^= 1;
     }
   } else if (warp == kSoftmaxWarps) {
     // ------------------------------------------------------------ the MMA warp (one lane issues)
     if (lane == 0) {
       constexpr uint32_t idesc_s = sm100::idesc_bf16_f32(BM, BN);
       constexpr uint32_t idesc_o = sm100::idesc_bf16_f32_b_mn(BM, HD);
-      auto issue_s = [&](int j) {  // S_j = Q K_j^T into S buffer j & 1; its commit frees the K buffer
-        wait(&k_full[j % KS], (j / KS) & 1);
+      // Only the address field of a shared-memory descriptor changes from one MMA to the next (16-byte units), so every
+      // operand is the first one's descriptor plus a constant; buffers and parities are counted, not divided.
+      const uint64_t dq0 = sm100::smem_desc_sw128(q_s), dk0 = sm100::smem_desc_sw128(k_s), dv0 = sm100::smem_desc_sw128_mn(v_s, BN * 128);
+      int ks = 0, vs = 0;
+      uint32_t k_par = 0, v_par = 0;
+      auto issue_s = [&](int j) {  // S_j = Q K_j^T into S buffer j & 1 (= K buffer ks); its commit also frees the K buffer
+        wait(&k_full[ks], k_par);
         sm100::tc_fence_after();
-        const uint32_t kb = k_s + (j % KS) * SM::kKV;
+        const uint64_t dk = dk0 + (uint64_t)(ks * (SM::kKV >> 4));
 #pragma unroll
         for (int kk = 0; kk < HD / 16; kk++) {
-          const uint64_t da = sm100::smem_desc_sw128(q_s + (kk >> 2) * BM * 128) + 2 * (kk & 3);
-          const uint64_t db = sm100::smem_desc_sw128(kb + (kk >> 2) * BN * 128) + 2 * (kk & 3);
-          sm100::mma_bf16_ss(tmem + (j & 1) * BN, da, db, idesc_s, kk != 0);
+          const uint64_t step = (uint64_t)(2 * (kk & 3));
+          sm100::mma_bf16_ss(tmem + ks * BN, dq0 + (uint64_t)(((kk >> 2) * BM * 128) >> 4) + step, dk + (uint64_t)(((kk >> 2) * BN * 128) >> 4) + step,
+                             idesc_s, kk != 0);
         }
-        sm100::mma_commit(&s_full[j & 1]);
-        sm100::mma_commit(&k_empty[j % KS]);
+        sm100::mma_commit(&s_full[ks]);
+        if (++ks == KS) ks = 0, k_par ^= 1;
       };
       wait(q_full, 0);
       issue_s(0);
       for (int j = 0; j < n_kt; j++) {
         if (j + 1 < n_kt) issue_s(j + 1);
         wait(&p_full[j & 1], (j >> 1) & 1);
-        wait(&v_full[j % VS], (j / VS) & 1);
+        wait(&v_full[vs], v_par);
         sm100::tc_fence_after();
-        const uint32_t vb = v_s + (j % VS) * SM::kKV;
+        const uint64_t dv = dv0 + (uint64_t)(vs * (SM::kKV >> 4));
 #pragma unroll
-        for (int ks = 0; ks < BN / 16; ks++) {   // O += P_j V_j, P from tensor memory: 16 keys = 8 columns per step
-          const uint64_t db = sm100::smem_desc_sw128_mn(vb + ks * 16 * 128, BN * 128);
-          sm100::mma_bf16_ts(tmem + 2 * BN, tmem + (j & 1) * BN + ks * 8, db, idesc_o, (j | ks) != 0);
-        }
-        sm100::mma_commit(o_full);
-        sm100::mma_commit(&v_empty[j % VS]);
+        for (int kstep = 0; kstep < BN / 16; kstep++)   // O += P_j V_j, P from tensor memory: 16 keys = 8 columns per step
+          sm100::mma_bf16_ts(tmem + 2 * BN, tmem + (j & 1) * BN + kstep * 8, dv + (uint64_t)((kstep * 16 * 128) >> 4), idesc_o, (j | kstep) != 0);
+        sm100::mma_commit(&v_empty[vs]);   // O has tile j, and the V buffer is free
+        if (++vs == VS) vs = 0, v_par ^= 1;
       }
     }
   } else {
@@ -290,7 +297,10 @@ __global__ void __launch_bounds__(kThreads, 2)
       if (j == 0) {
         m_ref = tile_max;
       } else if (__any_sync(0xffffffffu, grow)) {
-        wait(o_full, (j - 1) & 1);   // (S_j is ready, so P V of tile j - 2, issued before it, has finished: the parity means tile j - 1)
+        // P V of tile t commits to v_empty[t % VS]. A parity wait tells a phase from the one before it only; here the barrier
+        // of tile j - 1 has seen tile j - 1 - VS (S_j is ready, and P V of tile j - 2 was issued before it) and cannot have
+        // seen tile j - 1 + VS (its P is not written yet), so the parity of tile j - 1 is not mistaken.
+        wait(&v_empty[(j - 1) % VS], ((j - 1) / VS) & 1);
         sm100::tc_fence_after();
         const float m_new = grow ? fmaxf(m_ref, tile_max) : m_ref;
         const float f = m_new == -INFINITY ? 1.f : ex2(m_ref - m_new);  // 1 for rows that keep their reference, 0 when it was -inf
@@ -329,16 +339,10 @@ __global__ void __launch_bounds__(kThreads, 2)
       sm100::tmem_st_wait();
       sm100::tc_fence_before();
       __syncwarp();
-      if (lane == 0) {
-        // A parity wait tells a phase from the one before it only, so no phase of o_full may go unseen: P V of tile
-        // j - 1 is waited for here, before P_j is handed over (P V of tile j cannot start, so the barrier is in phase
-        // j - 1 or j now). The MMAs run in order anyway: nothing waits here that would not have waited there.
-        if (j > 0) wait(o_full, (j - 1) & 1);
-        sm100::mbar_arrive(&p_full[j & 1]);
-      }
+      if (lane == 0) sm100::mbar_arrive(&p_full[j & 1]);
     }
     // ---- O / l -> out
-    wait(o_full, (n_kt - 1) & 1);
+    wait(&v_empty[(n_kt - 1) % VS], ((n_kt - 1) / VS) & 1);
     sm100::tc_fence_after();
     if (!*gave_up) {
       const float inv = l > 0.f ? 1.f / l : 0.f;
