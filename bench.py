@@ -325,17 +325,19 @@ def run_ours(args) -> dict:
     cfg["num_hidden_layers"] = layers = args.layers or full_layers
     big = max(args.batch, 64)
     page = args.page_size
-    if args.only == "prefill" and args.prefill_after:   # a portion deep in a long context: a cache for one such request
-        engine = make_engine(cfg, page, 1, args.prefill_after + PROMPT)
-        return {"only": "prefill", "layers": layers, "after": args.prefill_after, "ms": measure_prefill(engine, args.steps, 1, args.prefill_after)}
     start = args.context_start
-    if args.only == "decode" and start != PROMPT:   # another context length: a cache for just these requests
+    after = args.prefill_after if args.only == "prefill" else 0
+    if after:   # a portion deep in a long context: a cache for one such request
+        engine = make_engine(cfg, page, 1, after + PROMPT)
+    elif args.only == "decode" and start != PROMPT:   # another context length: a cache for just these requests
         engine = make_engine(cfg, page, max(args.batch, 8), start + CONTEXT - PROMPT)
     else:
         engine = make_engine(cfg, page, big)
     steps, warmup = args.steps, max(args.warmup, 3)
     if args.only == "prefill":   # one part alone, for profiling: a short report, not the benchmark line
-        report = {"only": "prefill", "layers": layers, "ms": measure_prefill(engine, args.steps, 2)}
+        warm = 1 if after else 2
+        report = {"only": "prefill", "layers": layers, "page_size": page, **({"after": after} if after else {}),
+                  "ms": measure_prefill(engine, args.steps, warm, after)}
         if args.leave_out:
             from inference_bench_b200.kernels import lib as L
             real, report["without"] = L.call, {}
@@ -343,7 +345,7 @@ def run_ours(args) -> dict:
                 for kind in args.leave_out.split(","):
                     names = set(sum((LEAVE_OUT[k] for k in kind.split("+")), []))
                     L.call = lambda name, *a, _n=names: None if name in _n else real(name, *a)
-                    report["without"][kind] = measure_prefill(engine, args.steps, 2)
+                    report["without"][kind] = measure_prefill(engine, args.steps, warm, after)
             finally:
                 L.call = real
         return report
