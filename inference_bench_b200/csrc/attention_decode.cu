@@ -447,62 +447,66 @@ __global__ void __launch_bounds__((kWarps + 1) * 32, 2)
 
   if (warp == kWarps) {
     // ---------------- the copying warp
+    // A lane owns one box of every tile: box b_pg of the tile's keys (a page, where a page holds fewer keys than a tile),
+    // plane b_plane and 64-value block b_hb. What does not change from tile to tile is computed once, and the row of a box in
+    // the pool when its page is looked up (32 boxes at a time, one per lane): the loop over the tiles divides nothing.
     const int box_rows = min(kv.page_size, kTile);   // rows of one box: a page, or the tile's part of a larger page
     const int ppt = kTile / box_rows;                // boxes per tile, plane and 64-value block
-    const long long rows_per_page = kv.page_stride / HD, v_rows = kv.v_offset / HD;
+    const int boxes = ppt * HB * 2;
+    const int boxes_per_page = kv.page_size / box_rows;
+    const long long rows_per_page = kv.page_stride / HD;
+    const int v_rows = (int)(kv.v_offset / HD);
+    const int b_pg = lane / (HB * 2), b_plane = (lane / HB) & 1, b_hb = lane % HB;
+    const bool has_box = lane < boxes;
+    const uint32_t box_bytes = (uint32_t)box_rows * 128;
+    const uint32_t dst_lane = b_plane * TILE + b_hb * kTile * 128 + b_pg * box_bytes;
     uint32_t n = 0;        // tiles sent so far
+    int stage = 0;
+    uint32_t parity = 1;   // of the stage's "empty" barrier
     bool waited = false;   // the kernel before this one writes only the rows of the tokens' own positions
     bool ok = true;
     for (int u = next_unit(blockIdx.x); u < n_units && ok; u = next_unit(u + gridDim.x)) {
       const int tile_begin = k_begin / kTile, tile_end = k_begin < k_end ? (k_end - 1) / kTile + 1 : tile_begin;
-      int held = -2;       // page of box (tile_begin * ppt + base + lane), looked up 32 boxes at a time
+      int held_row = -1;   // where in the pool the K rows of box (tile_begin * ppt + rel + lane) begin, or -1: nothing to copy
       for (int tile = tile_begin; tile < tile_end; tile++, n++) {
         const int rel = (tile - tile_begin) * ppt;
         if ((rel & 31) == 0) {
-          const int key0 = (tile_begin * ppt + rel + lane) * box_rows;
-          const int col = key0 / kv.page_size;
-          held = -2;
-          if (key0 < k_end && key0 + box_rows > k_begin) held = col < kv.table_stride ? kv.block_table[(size_t)seg * kv.table_stride + col] : -1;
+          const int box = tile_begin * ppt + rel + lane;
+          const int key0 = box * box_rows;
+          held_row = -1;
+          if (key0 < k_end && key0 + box_rows > k_begin) {
+            const int col = boxes_per_page == 1 ? box : box / boxes_per_page;
+            const int page = col < kv.table_stride ? kv.block_table[(size_t)seg * kv.table_stride + col] : -1;
+            if (page >= 0 && page < kv.num_pages)
+              held_row = (int)((long long)page * rows_per_page + view_row0 + (long long)kvh * kv.page_size + (key0 - col * kv.page_size));
+            else
+              atomicOr(status, IB_ERR_BAD_PAGE);
+          }
         }
-        const int my = (lane - rel) & 31;            // which box of this tile this lane holds, if < ppt
-        const bool mine = my < ppt;
-        const bool valid = mine && held >= 0 && held < kv.num_pages;
-        if (mine && held != -2 && !valid) atomicOr(status, IB_ERR_BAD_PAGE);
-        const unsigned vmask = __ballot_sync(0xffffffffu, valid);
+        const int row = __shfl_sync(0xffffffffu, held_row, (rel + b_pg) & 31);
+        const bool mine = has_box && row >= 0;
+        const unsigned vmask = __ballot_sync(0xffffffffu, mine);
+        const int n_ok = __popc(vmask);
         if (!FUSED && !waited && pos >= tile * kTile && pos < (tile + 1) * kTile) {
           ib::pdl_wait();
           waited = true;
         }
-        const int stage = n % kRing;
-        if (lane == 0) ok = sm100::mbar_wait(&empty[stage], ((n / kRing) & 1) ^ 1, wait_ns);
+        if (lane == 0) ok = sm100::mbar_wait(&empty[stage], parity, wait_ns);
         ok = __shfl_sync(0xffffffffu, ok, 0) && !*gave_up;
         if (!ok) break;
         uint8_t* k_t = ring + stage * 2 * TILE;
-        // boxes that are not copied (no visible key in them, or no page) are cleared: a masked key's value still meets a zero weight
-        bool cleared = false;
-        for (int pg = 0; pg < ppt; pg++) {
-          if ((vmask >> ((rel + pg) & 31)) & 1) continue;
-          cleared = true;
-          for (int idx = lane; idx < box_rows * 8 * HB * 2; idx += 32) {
-            const int plane = idx / (box_rows * 8 * HB), r2 = idx % (box_rows * 8 * HB);
-            const int hb = r2 / (box_rows * 8), r3 = r2 % (box_rows * 8);
-            mt::st_shared_zero16(mt::smem_u32(k_t + plane * TILE + hb * kTile * 128 + pg * box_rows * 128) + r3 * 16);
+        if (n_ok != boxes) {   // boxes that are not copied (no visible key in them, or no page) are cleared: a masked key's value still meets a zero weight
+          for (int b = 0; b < boxes; b++) {
+            if ((vmask >> b) & 1) continue;
+            const uint32_t d0 = mt::smem_u32(k_t) + ((b / HB) & 1) * TILE + (b % HB) * kTile * 128 + (b / (HB * 2)) * box_bytes;
+            for (int idx = lane; idx < box_rows * 8; idx += 32) mt::st_shared_zero16(d0 + idx * 16);
           }
+          sm100::fence_proxy_async();
+          __syncwarp();
         }
-        if (cleared) sm100::fence_proxy_async();
-        __syncwarp();
-        if (lane == 0) sm100::mbar_arrive_expect_tx(&full[stage], (uint32_t)(__popc(vmask) * box_rows * 128 * HB * 2));
-        __syncwarp();
-        {   // one box per lane (page, plane, 64-value block), so that the boxes of a tile are issued side by side
-          const int b_pg = lane / (HB * 2), b_plane = (lane / HB) & 1, b_hb = lane % HB;
-          const int holder = (rel + b_pg) & 31;
-          const int page = __shfl_sync(0xffffffffu, held, holder);
-          if (lane < ppt * HB * 2 && ((vmask >> holder) & 1)) {
-            const int key0 = tile * kTile + b_pg * box_rows;
-            const long long row = (long long)page * rows_per_page + view_row0 + (long long)kvh * kv.page_size + key0 % kv.page_size + b_plane * v_rows;
-            sm100::tma_load_2d(k_t + b_plane * TILE + b_hb * kTile * 128 + b_pg * box_rows * 128, &kv_map, b_hb * 64, (int)row, &full[stage]);
-          }
-        }
+        if (lane == 0) sm100::mbar_arrive_expect_tx(&full[stage], (uint32_t)n_ok * box_bytes);
+        if (mine) sm100::tma_load_2d(k_t + dst_lane, &kv_map, b_hb * 64, row + b_plane * v_rows, &full[stage]);
+        if (++stage == kRing) stage = 0, parity ^= 1;
       }
     }
     if (!ok) {   // a wait ran out: say so, and let the copies in flight land before the shared memory goes
