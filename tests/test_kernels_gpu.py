@@ -377,7 +377,7 @@ def test_attention_generic(status, dtype, window):
     assert (out.cpu().double() - ref).abs().max() <= tol * ref.abs().max()
 
 
-@pytest.mark.parametrize("hd,heads,kvh,page", [(128, 8, 2, 16), (64, 5, 1, 32), (128, 16, 1, 16), (64, 4, 4, 8)])
+@pytest.mark.parametrize("hd,heads,kvh,page", [(128, 8, 2, 16), (64, 5, 1, 32), (128, 16, 1, 16), (64, 4, 4, 8), (128, 8, 2, 128), (64, 4, 2, 64), (128, 4, 1, 192)])
 @pytest.mark.parametrize("window", [None, 100])
 @pytest.mark.parametrize("prefill", ["ws", "tcgen05"])
 def test_attention_tensor_core_kernels(status, hd, heads, kvh, page, window, prefill):
