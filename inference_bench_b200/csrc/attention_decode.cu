@@ -289,8 +289,19 @@ __global__ void __launch_bounds__(kCombineThreads)
   const size_t slot0 = ((size_t)item * heads + h) * max_slices;
   const int sg = threadIdx.x / DQ, dq = threadIdx.x % DQ;
   ib::pdl_wait();
-  float mx = -INFINITY;
-  for (int s = s_begin + sg; s < s_end; s += SG) mx = fmaxf(mx, part_ml[(slot0 + s) * 2]);
+  // the thread's first slice (with up to SG slices, its only one) is requested whole before anything is waited for:
+  // one trip to memory instead of two, one after the other
+  const int s0 = s_begin + sg;
+  const bool have = s0 < s_end;
+  float m0 = -INFINITY, l0 = 0.f;
+  float4 v0 = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (have) {
+    m0 = part_ml[(slot0 + s0) * 2];
+    l0 = part_ml[(slot0 + s0) * 2 + 1];
+    v0 = *(const float4*)&part_o[(slot0 + s0) * HD + 4 * dq];
+  }
+  float mx = m0;
+  for (int s = s0 + SG; s < s_end; s += SG) mx = fmaxf(mx, part_ml[(slot0 + s) * 2]);
   if (dq == 0) m_red[sg] = mx;
   __syncthreads();
   float M = -INFINITY;
@@ -298,7 +309,12 @@ __global__ void __launch_bounds__(kCombineThreads)
   for (int i = 0; i < SG; i++) M = fmaxf(M, m_red[i]);
   float Lp = 0.f;
   float4 Op = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int s = s_begin + sg; s < s_end; s += SG) {
+  if (have) {
+    const float f = exp2f(m0 - M);
+    Lp = l0 * f;
+    Op = make_float4(v0.x * f, v0.y * f, v0.z * f, v0.w * f);
+  }
+  for (int s = s0 + SG; s < s_end; s += SG) {
     const float f = exp2f(part_ml[(slot0 + s) * 2] - M);
     Lp += part_ml[(slot0 + s) * 2 + 1] * f;
     const float4 v = *(const float4*)&part_o[(slot0 + s) * HD + 4 * dq];
