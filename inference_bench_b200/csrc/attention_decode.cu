@@ -567,19 +567,19 @@ __global__ void __launch_bounds__((kWarps + 1) * 32, 2)
       }
     }
   };
-  auto finish_head = [&](const float* norm_w, bool turn, float (&v)[E]) {   // norm and rotation
-    if (norm_w) {
+  // (the norm's weights and the rotation's table entries are requested by the caller beside the partial products,
+  // not here after the sums: one trip to memory, not three one after the other)
+  auto finish_head = [&](bool norm, const float (&nw)[E], bool turn, const float (&c)[E], const float (&sn)[E], float (&v)[E]) {   // norm and rotation
+    if (norm) {
       float ss = 0.f;
 #pragma unroll
       for (int e = 0; e < E; e++) ss += v[e] * v[e];
       ss = ib::warp_sum(ss);
       const float inv = rsqrtf(ss / (float)HD + raw.eps);
 #pragma unroll
-      for (int e = 0; e < E; e++) v[e] = norm_w[lane * E + e] * (v[e] * inv);
+      for (int e = 0; e < E; e++) v[e] = nw[e] * (v[e] * inv);
     }
     if (turn && raw.cos_t) {
-      const float* c = raw.cos_t + (size_t)t * (HD / 2) + (lane & 15) * E;
-      const float* sn = raw.sin_t + (size_t)t * (HD / 2) + (lane & 15) * E;
 #pragma unroll
       for (int e = 0; e < E; e++) {
         const float other = __shfl_xor_sync(0xffffffffu, v[e], 16);
@@ -590,12 +590,19 @@ __global__ void __launch_bounds__((kWarps + 1) * 32, 2)
   auto q_row_addr = [&](int row) { return q_s + mt::tile_offset<HD, 16>(row, lane * E / 8) + (lane * E * 2) % 16; };   // this lane's E values of a Q row
   auto make_unit_inputs = [&]() {   // the opened unit's query rows, and its own key and value if its slice holds them
     const bool own_mine = has_own && warp < 2;   // warp 0: the key (normed and turned); warp 1: the value
-    float vo[E];
+    float vo[E], c[E], sn[E], qw[E], kw[E];
+#pragma unroll
+    for (int e = 0; e < E; e++) {
+      c[e] = raw.cos_t ? raw.cos_t[(size_t)t * (HD / 2) + (lane & 15) * E + e] : 1.f;
+      sn[e] = raw.cos_t ? raw.sin_t[(size_t)t * (HD / 2) + (lane & 15) * E + e] : 0.f;
+      qw[e] = raw.q_norm_w ? raw.q_norm_w[lane * E + e] : 1.f;
+      kw[e] = own_mine && warp == 0 && raw.k_norm_w ? raw.k_norm_w[lane * E + e] : 1.f;
+    }
     if (own_mine) load_head(warp == 0 ? heads + kvh : heads + kv.kv_heads + kvh, vo);   // requested together with the first query row
     for (int row = warp; row < group; row += kWarps) {
       float v[E];
       load_head(kvh * group + row, v);
-      finish_head(raw.q_norm_w, true, v);
+      finish_head(raw.q_norm_w != nullptr, qw, true, c, sn, v);
       if constexpr (E == 4)
         asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(q_row_addr(row)), "r"(mt::pack_bf16(v[0], v[1])), "r"(mt::pack_bf16(v[2], v[3])) : "memory");
       else
@@ -603,7 +610,7 @@ __global__ void __launch_bounds__((kWarps + 1) * 32, 2)
     }
     if (own_mine) {
       float (&v)[E] = vo;
-      finish_head(warp == 0 ? raw.k_norm_w : nullptr, warp == 0, v);
+      finish_head(warp == 0 && raw.k_norm_w != nullptr, kw, warp == 0, c, sn, v);
       __nv_bfloat16 b[E];
       float* own = warp == 0 ? k_own : v_own;
 #pragma unroll
