@@ -60,8 +60,13 @@ __global__ void embed_kernel(const W* __restrict__ table, const int* __restrict_
 // (shuffle tree), then the 32 warp sums (the same tree). sq4 pins the order inside a float4.
 __device__ __forceinline__ float sq4(float4 v) { return __fmaf_rn(v.w, v.w, __fmaf_rn(v.z, v.z, __fmaf_rn(v.y, v.y, __fmul_rn(v.x, v.x)))); }
 
-template <typename O, int VEC>
-__global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, int P, size_t delta_stride,
+// HELD (a few rows only): every partial sum of a thread's four values is requested before the first is used, so that the
+// row costs one trip to memory whatever the number of splits; with more rows the loads of four at a time are the faster
+// form (the rows' requests then stand in one another's way, and in the way of the next product's weights).
+constexpr int kHeld = 9;
+
+template <typename O, int VEC, bool HELD>
+__global__ void __launch_bounds__(1024) add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, int P, size_t delta_stride,
                                    const float* __restrict__ w, O* __restrict__ out, const int* __restrict__ rows, int H, float eps,
                                    int write_x) {
   extern __shared__ __align__(16) float row[];
@@ -77,9 +82,22 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restric
     for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
       float4 v = *(const float4*)(xr + i);
       if (P > 0) {
-        float4 d = *(const float4*)(dr + i);
+        float4 d;
         int p = 1;
-        for (; p + 3 < P; p += 4) {   // four independent loads in flight, added in order
+        if constexpr (HELD) {
+          float4 part[kHeld];
+#pragma unroll
+          for (int q = 0; q < kHeld; q++)
+            if (q < P) part[q] = *(const float4*)(dr + q * delta_stride + i);
+          d = part[0];
+#pragma unroll
+          for (int q = 1; q < kHeld; q++)
+            if (q < P) d.x += part[q].x, d.y += part[q].y, d.z += part[q].z, d.w += part[q].w;
+          p = P < kHeld ? P : kHeld;
+        } else {
+          d = *(const float4*)(dr + i);
+        }
+        for (; !HELD && p + 3 < P; p += 4) {   // four independent loads in flight, added in order
           const float4 a = *(const float4*)(dr + p * delta_stride + i), b = *(const float4*)(dr + (p + 1) * delta_stride + i),
                        c = *(const float4*)(dr + (p + 2) * delta_stride + i), e = *(const float4*)(dr + (p + 3) * delta_stride + i);
           d.x = (((d.x + a.x) + b.x) + c.x) + e.x;
@@ -274,18 +292,19 @@ extern "C" int ib_add_rmsnorm(float* x, const float* delta, int P, long long del
     IB_CHECK_LAUNCH("add_rmsnorm");
     return 0;
   }
-  const int per = vec ? 4 : 1;
+  constexpr int kFewRows = 4;   // up to here the form that requests every partial sum at once (measured: faster for 1 to 4 rows)
   int threads = vec ? 1024 : (H >= 1024 ? 1024 : (H >= 512 ? 512 : (H >= 256 ? 256 : 128)));   // 16-byte form: always 1024, the fixed summation order
   auto go = [&](auto kernel, auto* o) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     ib::launch(kernel, n_rows, threads, smem, stream, x, delta, P, (size_t)delta_stride, w, o, rows, H, eps, write_x);
   };
   if (out_dtype == IB_F32) {
-    if (vec) go(add_rmsnorm_kernel<float, 4>, (float*)out);
-    else go(add_rmsnorm_kernel<float, 1>, (float*)out);
+    if (vec) go(add_rmsnorm_kernel<float, 4, false>, (float*)out);
+    else go(add_rmsnorm_kernel<float, 1, false>, (float*)out);
   } else if (out_dtype == IB_BF16) {
-    if (vec) go(add_rmsnorm_kernel<__nv_bfloat16, 4>, (__nv_bfloat16*)out);
-    else go(add_rmsnorm_kernel<__nv_bfloat16, 1>, (__nv_bfloat16*)out);
+    if (vec && n_rows <= kFewRows) go(add_rmsnorm_kernel<__nv_bfloat16, 4, true>, (__nv_bfloat16*)out);
+    else if (vec) go(add_rmsnorm_kernel<__nv_bfloat16, 4, false>, (__nv_bfloat16*)out);
+    else go(add_rmsnorm_kernel<__nv_bfloat16, 1, false>, (__nv_bfloat16*)out);
   } else {
     return ib_set_error("add_rmsnorm: unknown output dtype %d", out_dtype);
   }
