@@ -105,7 +105,16 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(float* __restrict__ x
           d.z = (((d.z + a.z) + b.z) + c.z) + e.z;
           d.w = (((d.w + a.w) + b.w) + c.w) + e.w;
         }
-        for (; p < P; p++) {
+        if (!HELD && p < P) {   // the one to three that are left: requested together as well, added in order
+          const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+          const float4 a = *(const float4*)(dr + p * delta_stride + i), b = p + 1 < P ? *(const float4*)(dr + (p + 1) * delta_stride + i) : zero,
+                       c = p + 2 < P ? *(const float4*)(dr + (p + 2) * delta_stride + i) : zero;
+          d.x += a.x, d.y += a.y, d.z += a.z, d.w += a.w;
+          if (p + 1 < P) d.x += b.x, d.y += b.y, d.z += b.z, d.w += b.w;
+          if (p + 2 < P) d.x += c.x, d.y += c.y, d.z += c.z, d.w += c.w;
+          p = P;
+        }
+        for (; p < P; p++) {   // (the held form's partial sums beyond what it holds)
           const float4 a = *(const float4*)(dr + p * delta_stride + i);
           d.x += a.x, d.y += a.y, d.z += a.z, d.w += a.w;
         }
