@@ -98,6 +98,25 @@ __global__ void qk_norm_rope_kv_vec_kernel(const float* __restrict__ qkv, int P,
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
   const int j0 = (blockIdx.y * kWarps + warp) * PER;
+  // what every head of the token shares, fetched once per warp with wide loads and requested before the partial products
+  // (one trip to memory for all of it, not one after the other): norm scales, the token's
+  // rotation (the sine with the sign of this lane's half: d < HD/2: v cos - partner sin; d >= HD/2: v cos + partner sin)
+  float qw[E], kw[E], cs[E], sn[E];
+  auto load_vec = [&](const float* src, float (&dst)[E]) {
+    if constexpr (E == 4) {
+      const float4 a = *(const float4*)src;
+      dst[0] = a.x, dst[1] = a.y, dst[2] = a.z, dst[3] = a.w;
+    } else {
+      const float2 a = *(const float2*)src;
+      dst[0] = a.x, dst[1] = a.y;
+    }
+  };
+  if (q_norm_w) load_vec(q_norm_w + lane * E, qw);
+  if (k_norm_w) load_vec(k_norm_w + lane * E, kw);
+  if (cos_t) {
+    load_vec(cos_t + (size_t)t * (HD / 2) + (lane & 15) * E, cs);
+    load_vec(sin_t + (size_t)t * (HD / 2) + (lane & 15) * E, sn);
+  }
   float v[PER][E];
 #pragma unroll
   for (int u = 0; u < PER; u++) {
@@ -116,27 +135,9 @@ __global__ void qk_norm_rope_kv_vec_kernel(const float* __restrict__ qkv, int P,
       }
     }
   }
-  // what every head of the token shares, fetched once per warp with wide loads: norm scales, the token's
-  // rotation (the sine with the sign of this lane's half: d < HD/2: v cos - partner sin; d >= HD/2: v cos + partner sin)
-  float qw[E], kw[E], cs[E], sn[E];
-  auto load_vec = [&](const float* src, float (&dst)[E]) {
-    if constexpr (E == 4) {
-      const float4 a = *(const float4*)src;
-      dst[0] = a.x, dst[1] = a.y, dst[2] = a.z, dst[3] = a.w;
-    } else {
-      const float2 a = *(const float2*)src;
-      dst[0] = a.x, dst[1] = a.y;
-    }
-  };
-  if (q_norm_w) load_vec(q_norm_w + lane * E, qw);
-  if (k_norm_w) load_vec(k_norm_w + lane * E, kw);
-  if (cos_t) {
-    load_vec(cos_t + (size_t)t * (HD / 2) + (lane & 15) * E, cs);
-    load_vec(sin_t + (size_t)t * (HD / 2) + (lane & 15) * E, sn);
-    if (lane < 16) {
+  if (cos_t && lane < 16) {   // (used only now, so that nothing waited for it above)
 #pragma unroll
-      for (int e = 0; e < E; e++) sn[e] = -sn[e];
-    }
+    for (int e = 0; e < E; e++) sn[e] = -sn[e];
   }
 #pragma unroll
   for (int u = 0; u < PER; u++) {
