@@ -567,6 +567,23 @@ __global__ void __launch_bounds__((kWarps + 1) * 32, 2)
       }
     }
   };
+  auto load_two_heads = [&](int j1, float (&v1)[E], int j2, float (&v2)[E]) {   // two heads, their loads side by side
+    const float* s1 = raw.qkv + (size_t)t * R + (size_t)j1 * HD + lane * E;
+    const float* s2 = raw.qkv + (size_t)t * R + (size_t)j2 * HD + lane * E;
+#pragma unroll
+    for (int e = 0; e < E; e++) v1[e] = 0.f, v2[e] = 0.f;
+    for (int p = 0; p < raw.P; p++) {
+      if constexpr (E == 4) {
+        const float4 a = *(const float4*)(s1 + p * raw.stride_p), b = *(const float4*)(s2 + p * raw.stride_p);
+        v1[0] += a.x, v1[1] += a.y, v1[2] += a.z, v1[3] += a.w;
+        v2[0] += b.x, v2[1] += b.y, v2[2] += b.z, v2[3] += b.w;
+      } else {
+        const float2 a = *(const float2*)(s1 + p * raw.stride_p), b = *(const float2*)(s2 + p * raw.stride_p);
+        v1[0] += a.x, v1[1] += a.y;
+        v2[0] += b.x, v2[1] += b.y;
+      }
+    }
+  };
   // (the norm's weights and the rotation's table entries are requested by the caller beside the partial products,
   // not here after the sums: one trip to memory, not three one after the other)
   auto finish_head = [&](bool norm, const float (&nw)[E], bool turn, const float (&c)[E], const float (&sn)[E], float (&v)[E]) {   // norm and rotation
@@ -598,10 +615,15 @@ __global__ void __launch_bounds__((kWarps + 1) * 32, 2)
       qw[e] = raw.q_norm_w ? raw.q_norm_w[lane * E + e] : 1.f;
       kw[e] = own_mine && warp == 0 && raw.k_norm_w ? raw.k_norm_w[lane * E + e] : 1.f;
     }
-    if (own_mine) load_head(warp == 0 ? heads + kvh : heads + kv.kv_heads + kvh, vo);   // requested together with the first query row
+    const int own_j = warp == 0 ? heads + kvh : heads + kv.kv_heads + kvh;
+    const bool together = own_mine && warp < group;   // the own key or value is requested together with the warp's first query row
+    if (own_mine && !together) load_head(own_j, vo);
     for (int row = warp; row < group; row += kWarps) {
       float v[E];
-      load_head(kvh * group + row, v);
+      if (together && row == warp)
+        load_two_heads(own_j, vo, kvh * group + row, v);
+      else
+        load_head(kvh * group + row, v);
       finish_head(raw.q_norm_w != nullptr, qw, true, c, sn, v);
       if constexpr (E == 4)
         asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(q_row_addr(row)), "r"(mt::pack_bf16(v[0], v[1])), "r"(mt::pack_bf16(v[2], v[3])) : "memory");
