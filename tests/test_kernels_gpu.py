@@ -404,6 +404,34 @@ def test_attention_tensor_core_kernels(status, hd, heads, kvh, page, window, pre
     assert (out2.float() - out.float()).abs().max() <= 2e-2 * ref.abs().max()
 
 
+@pytest.mark.parametrize("seed", [0, 1, 2])
+def test_attention_random_shapes(status, seed):
+    """Random mixes of prompt portions and decoded tokens through the dispatch that serving uses (head sizes, groups, page
+    sizes, windows and lengths drawn at random, lengths around tile and page edges included), against the plain reference."""
+    import random
+    from inference_bench_b200.engine.context import Segment, build_context
+    from inference_bench_b200.engine.runtime import Runtime
+    from inference_bench_b200.kernels import attention
+    rng = random.Random(seed)
+    for case in range(8):
+        hd = rng.choice([64, 128])
+        kvh = rng.choice([1, 2, 4])
+        heads = kvh * rng.choice([1, 2, 4, 7])
+        page = rng.choice([8, 16, 32, 64, 128])
+        window = rng.choice([None, None, rng.randint(3, 400)])
+        shapes = []
+        for _ in range(rng.randint(1, 5)):
+            L = rng.choice([1, 2, 63, 64, 65, 127, 128, 129, 191, 192, 193, rng.randint(1, 1100), rng.randint(1500, 3000)])
+            shapes.append((L, rng.choice([1, 1, L, rng.randint(1, L)])))
+        q, view, pos, seg, ref, _ = _attention_case(torch.bfloat16, heads, kvh, hd, page, window, shapes, 1000 * seed + case, needle=True)
+        rt = Runtime(DEV)
+        ctx = build_context(rt, [Segment(i, i, L - n, [0] * n) for i, (L, n) in enumerate(shapes)])
+        out = attention.paged_attention(ctx, q, view, heads, window, 1 / math.sqrt(hd))
+        rt.check_status()
+        err = (out.cpu().double() - ref).abs()
+        assert err.max() <= 1.5e-2 * ref.abs().max(), f"case {case} (hd {hd}, heads {heads}/{kvh}, page {page}, window {window}, {shapes}): row {int(err.max(dim=1).values.argmax())} is off by {err.max():.3e}"
+
+
 @pytest.mark.parametrize("tiles_per_slice", [1, 2, 8])
 @pytest.mark.parametrize("kernel,page,hd", [("stream", 16, 128), ("stream", 64, 64), ("stream", 8, 128), ("stream", 128, 128), ("stream", 32, 64),
                                             ("auto", 24, 64), ("split", 16, 128), ("split", 64, 64), ("split", 8, 128), ("split", 24, 64), ("split", 128, 64)])
